@@ -1,0 +1,671 @@
+// Host side of libfk_w4a16.so: argument checks, launch planning and the extern "C" entry points
+// declared in include/fk_w4a16.h. Nothing here allocates device memory or synchronises, except
+// fk_w4a16_device_status() which is documented to.
+#include "fk_w4a16.h"
+
+#include <cublasLt.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+#include <sstream>
+#include <string>
+
+#include "w4a16_common.cuh"
+#include "w4a16_gemv_stream.cuh"
+#include "w4a16_prep.cuh"
+
+#ifndef FK_W4A16_VERSION
+#define FK_W4A16_VERSION "0.1.0"
+#endif
+
+namespace fk_w4a16 {
+namespace {
+
+__device__ int g_device_status = 0;
+
+thread_local std::string t_last_error;
+
+int fail(int code, const std::string& message) {
+  t_last_error = message;
+  return code;
+}
+
+#define FK_TRY_CUDA(expr)                                                                 \
+  do {                                                                                    \
+    const cudaError_t status__ = (expr);                                                  \
+    if (status__ != cudaSuccess) {                                                        \
+      return fail(FK_W4A16_ERR_CUDA,                                                      \
+                  std::string(#expr) + " failed: " + cudaGetErrorString(status__));       \
+    }                                                                                     \
+  } while (false)
+
+#define FK_TRY_CUBLAS(expr)                                                               \
+  do {                                                                                    \
+    const cublasStatus_t status__ = (expr);                                               \
+    if (status__ != CUBLAS_STATUS_SUCCESS) {                                              \
+      return fail(FK_W4A16_ERR_CUDA,                                                      \
+                  std::string(#expr) + " failed: " + cublasLtGetStatusString(status__));  \
+    }                                                                                     \
+  } while (false)
+
+#define FK_TRY(expr)                  \
+  do {                                \
+    const int rc__ = (expr);          \
+    if (rc__ != FK_W4A16_OK) {        \
+      return rc__;                    \
+    }                                 \
+  } while (false)
+
+// ---- argument checks (same rules and wording as the reference, arc_w4a16.cu:28-57) -----------
+bool group_supported(int group_size) {
+  return group_size == 32 || group_size == 64 || group_size == 128;
+}
+
+int check_group_and_k(int batch, int k, int group_size) {
+  if (batch <= 0 || k <= 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "batch and k must be positive");
+  }
+  if (!group_supported(group_size)) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "group_size must be 32, 64 or 128");
+  }
+  if (k % group_size != 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "k must be divisible by group_size");
+  }
+  return FK_W4A16_OK;
+}
+
+int check_dimensions(int batch, int n, int k, int group_size) {
+  FK_TRY(check_group_and_k(batch, k, group_size));
+  if (n <= 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n must be positive");
+  }
+  if (n % kTileCols != 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n must be a multiple of 128");
+  }
+  return FK_W4A16_OK;
+}
+
+int check_stride(int group_size, int packet_stride_bytes) {
+  const int expected = packet_stride(group_size);
+  if (packet_stride_bytes != expected) {
+    std::ostringstream oss;
+    oss << "packet_stride_bytes=" << packet_stride_bytes << " does not match expected " << expected;
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+  }
+  return FK_W4A16_OK;
+}
+
+int check_dtype(int dtype) {
+  if (dtype != FK_W4A16_DTYPE_F16 && dtype != FK_W4A16_DTYPE_BF16) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "dtype must be FK_W4A16_DTYPE_F16 or _BF16");
+  }
+  return FK_W4A16_OK;
+}
+
+int check_pointer(const void* ptr, const char* name, size_t alignment) {
+  if (ptr == nullptr) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, std::string(name) + " must not be null");
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) % alignment) != 0) {
+    std::ostringstream oss;
+    oss << name << " must be aligned to " << alignment << " bytes";
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+  }
+  return FK_W4A16_OK;
+}
+
+// ---- per-device facts, read once ---------------------------------------------------------
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int* status_word = nullptr;
+};
+
+int device_info(DeviceInfo** out) {
+  static DeviceInfo infos[kMaxDevices];
+  static std::once_flag flags[kMaxDevices];
+  int device = 0;
+  FK_TRY_CUDA(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) {
+    return fail(FK_W4A16_ERR_CUDA, "device index out of range");
+  }
+  cudaError_t err = cudaSuccess;
+  std::call_once(flags[device], [&] {
+    DeviceInfo& info = infos[device];
+    err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (err == cudaSuccess) {
+      err = cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                   device);
+    }
+    if (err == cudaSuccess) {
+      void* addr = nullptr;
+      err = cudaGetSymbolAddress(&addr, g_device_status);
+      info.status_word = static_cast<int*>(addr);
+    }
+  });
+  if (err != cudaSuccess || infos[device].status_word == nullptr) {
+    return fail(FK_W4A16_ERR_CUDA,
+                std::string("device query failed: ") + cudaGetErrorString(err));
+  }
+  *out = &infos[device];
+  return FK_W4A16_OK;
+}
+
+// ---- launch planning for the fused GEMV --------------------------------------------------
+constexpr size_t kTicketBytes = 256 * 1024;  // fixed ticket area at the start of a workspace
+constexpr int kTicketCapacity = static_cast<int>(kTicketBytes / sizeof(int));
+constexpr int kDefaultWarps = 8;
+constexpr int kMaxWarps = 16;
+constexpr int kMaxStages = 8;
+
+struct LaunchConfig {
+  int warps = 0;
+  int stages = 0;
+  int ctas = 0;
+};
+LaunchConfig g_config;
+std::once_flag g_config_env_once;
+
+int env_int(const char* name) {
+  const char* value = std::getenv(name);
+  return value == nullptr ? 0 : std::atoi(value);
+}
+
+const LaunchConfig& launch_config() {
+  std::call_once(g_config_env_once, [] {
+    if (g_config.warps == 0) g_config.warps = env_int("FK_W4A16_WARPS");
+    if (g_config.stages == 0) g_config.stages = env_int("FK_W4A16_STAGES");
+    if (g_config.ctas == 0) g_config.ctas = env_int("FK_W4A16_CTAS");
+  });
+  return g_config;
+}
+
+int m_tile_for_batch(int batch) { return batch <= 1 ? 1 : (batch <= 2 ? 2 : 4); }
+
+struct Plan {
+  int m_tile = 1;
+  int row_tiles = 1;
+  int warps = 1;
+  int stages = 2;
+  int grid_x = 1;
+  int active_warps = 1;
+  size_t smem_bytes = 0;
+  size_t scratch_bytes = 0;
+};
+
+// `sm_count` and `max_smem` describe the device; the plan is a pure function of its arguments
+// so that fk_w4a16_workspace_bytes() and fk_w4a16_gemv() always agree.
+Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
+               const LaunchConfig& cfg) {
+  Plan plan;
+  plan.m_tile = m_tile_for_batch(batch);
+  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
+  const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
+  const int stage_bytes = packet_stride(group_size) + (plan.m_tile * group_size * 2);
+
+  int warps = cfg.warps > 0 ? cfg.warps : kDefaultWarps;
+  warps = warps > kMaxWarps ? kMaxWarps : warps;
+  const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+  long long workers = static_cast<long long>(ctas) * warps;
+  if (workers > total_packets) {
+    workers = total_packets;
+  }
+  // Spread the workers over all CTAs rather than filling the first ones.
+  warps = static_cast<int>((workers + ctas - 1) / ctas);
+  plan.warps = warps;
+  plan.grid_x = static_cast<int>((workers + warps - 1) / warps);
+  plan.active_warps = static_cast<int>(workers);
+
+  const size_t barrier_bytes = ((static_cast<size_t>(warps) * kMaxStages * 8) + 127) & ~size_t{127};
+  int stages = static_cast<int>((static_cast<size_t>(max_smem) - barrier_bytes) /
+                                (static_cast<size_t>(warps) * stage_bytes));
+  const int wanted = cfg.stages > 0 ? cfg.stages : 4;
+  stages = stages > wanted ? wanted : stages;
+  stages = stages > kMaxStages ? kMaxStages : stages;
+  plan.stages = stages;  // < 2 means "does not fit"; the caller reports it
+  plan.smem_bytes = (((static_cast<size_t>(warps) * stages * 8) + 127) & ~size_t{127}) +
+                    (static_cast<size_t>(warps) * stages * stage_bytes);
+  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.active_warps * 2 *
+                       (plan.m_tile * kTileCols) * sizeof(float);
+  return plan;
+}
+
+size_t workspace_bytes_for(const Plan& plan) {
+  return kTicketBytes + ((plan.scratch_bytes + 255) & ~size_t{255});
+}
+
+// cudaFuncSetAttribute is per function and device; raising it to the device limit once covers
+// every later launch shape. `flags` must be distinct per kernel instantiation.
+template <class Kernel>
+int ensure_smem_optin(Kernel kernel, std::once_flag (&flags)[kMaxDevices], size_t bytes,
+                      int max_smem) {
+  int device = 0;
+  FK_TRY_CUDA(cudaGetDevice(&device));
+  cudaError_t err = cudaSuccess;
+  std::call_once(flags[device], [&] {
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+  });
+  if (err != cudaSuccess) {
+    return fail(FK_W4A16_ERR_CUDA,
+                std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(err));
+  }
+  if (bytes > static_cast<size_t>(max_smem)) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch needs more shared memory than the device has");
+  }
+  return FK_W4A16_OK;
+}
+
+template <int G, int M_TILE, class E>
+int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cudaStream_t stream) {
+  auto kernel = w4a16_gemv_stream_kernel<G, M_TILE, E>;
+  static std::once_flag optin_flags[kMaxDevices];
+  FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
+  const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
+  kernel<<<grid, plan.warps * 32, plan.smem_bytes, stream>>>(params);
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+template <int G, int M_TILE, class E>
+int launch_split_k(const SplitKParams& params, int row_tiles, int max_smem, cudaStream_t stream) {
+  auto kernel = w4a16_split_k_kernel<G, M_TILE, E>;
+  constexpr int kWarps = 4;
+  const int stage_bytes = packet_stride(G) + (M_TILE * G * 2);
+  const size_t smem = (((kWarps * params.base.stages * 8) + 127) & ~127) +
+                      (static_cast<size_t>(kWarps) * params.base.stages * stage_bytes);
+  static std::once_flag optin_flags[kMaxDevices];
+  FK_TRY(ensure_smem_optin(kernel, optin_flags, smem, max_smem));
+  const dim3 grid(static_cast<unsigned>(params.base.num_tiles), static_cast<unsigned>(row_tiles),
+                  static_cast<unsigned>(params.slices));
+  kernel<<<grid, kWarps * 32, smem, stream>>>(params);
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+// Compile-time fan-out over (group size, rows per pass, element type).
+template <int G, class E, class Fn>
+int for_m_tile(int m_tile, Fn&& fn) {
+  switch (m_tile) {
+    case 1: return fn(std::integral_constant<int, G>{}, std::integral_constant<int, 1>{}, E{});
+    case 2: return fn(std::integral_constant<int, G>{}, std::integral_constant<int, 2>{}, E{});
+    default: return fn(std::integral_constant<int, G>{}, std::integral_constant<int, 4>{}, E{});
+  }
+}
+template <class E, class Fn>
+int for_group(int group_size, int m_tile, Fn&& fn) {
+  switch (group_size) {
+    case 32: return for_m_tile<32, E>(m_tile, fn);
+    case 64: return for_m_tile<64, E>(m_tile, fn);
+    default: return for_m_tile<128, E>(m_tile, fn);
+  }
+}
+template <class Fn>
+int dispatch(int group_size, int m_tile, int dtype, Fn&& fn) {
+  return dtype == FK_W4A16_DTYPE_BF16 ? for_group<BF16>(group_size, m_tile, fn)
+                                      : for_group<F16>(group_size, m_tile, fn);
+}
+
+int grid_for(long long items, int threads, int sm_count) {
+  const long long blocks = (items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(sm_count) * 32;
+  return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+cublasLtHandle_t g_lt_handle = nullptr;
+std::once_flag g_lt_once;
+
+}  // namespace
+}  // namespace fk_w4a16
+
+using namespace fk_w4a16;
+
+extern "C" {
+
+const char* fk_w4a16_last_error(void) { return t_last_error.c_str(); }
+const char* fk_w4a16_version(void) { return FK_W4A16_VERSION; }
+const char* fk_w4a16_cuda_arch(void) { return "100a"; }
+
+int fk_w4a16_packet_stride_bytes(int group_size) {
+  if (!group_supported(group_size)) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "group_size must be 32, 64 or 128");
+  }
+  return packet_stride(group_size);
+}
+
+int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas) {
+  if (warps_per_cta < 0 || warps_per_cta > kMaxWarps || stages < 0 || stages == 1 ||
+      stages > kMaxStages || ctas < 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config out of range");
+  }
+  (void)launch_config();  // settle the environment defaults first so they cannot override this
+  g_config.warps = warps_per_cta;
+  g_config.stages = stages;
+  g_config.ctas = ctas;
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_pack_packets(const void* q, const void* alpha, const void* beta, void* packets, int n,
+                          int k, int group_size, int packet_stride_bytes, void* stream) {
+  FK_TRY(check_dimensions(1, n, k, group_size));
+  FK_TRY(check_stride(group_size, packet_stride_bytes));
+  FK_TRY(check_pointer(q, "q", 16));
+  FK_TRY(check_pointer(alpha, "alpha", 2));
+  FK_TRY(check_pointer(beta, "beta", 2));
+  FK_TRY(check_pointer(packets, "packets", 16));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  const int num_groups = k / group_size;
+  const long long total = static_cast<long long>(n / kTileCols) * num_groups;
+  const long long cap = static_cast<long long>(info->sm_count) * 16;
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  auto* s = static_cast<cudaStream_t>(stream);
+  auto* qp = static_cast<const uint8_t*>(q);
+  auto* ap = static_cast<const uint16_t*>(alpha);
+  auto* bp = static_cast<const uint16_t*>(beta);
+  auto* pp = static_cast<uint8_t*>(packets);
+  switch (group_size) {
+    case 32: pack_packets_kernel<32><<<grid, 128, 0, s>>>(qp, ap, bp, pp, k, num_groups, total); break;
+    case 64: pack_packets_kernel<64><<<grid, 128, 0, s>>>(qp, ap, bp, pp, k, num_groups, total); break;
+    default: pack_packets_kernel<128><<<grid, 128, 0, s>>>(qp, ap, bp, pp, k, num_groups, total); break;
+  }
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_group_sums(const void* activations, float* sums, int batch, int k, int group_size,
+                        int dtype, void* stream) {
+  FK_TRY(check_group_and_k(batch, k, group_size));
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(activations, "activations", 4));
+  FK_TRY(check_pointer(sums, "sums", 4));
+  const int num_groups = k / group_size;
+  const long long total = static_cast<long long>(batch) * num_groups;
+  const int grid = static_cast<int>((total + 3) / 4);
+  auto* s = static_cast<cudaStream_t>(stream);
+  auto* act = static_cast<const uint16_t*>(activations);
+  const int rc = dispatch(group_size, 1, dtype, [&](auto g, auto, auto e) {
+    using E = decltype(e);
+    group_sums_kernel<decltype(g)::value, E><<<grid, 128, 0, s>>>(act, sums, k, num_groups, total);
+    return FK_W4A16_OK;
+  });
+  FK_TRY(rc);
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+size_t fk_w4a16_workspace_bytes(int batch, int n, int k, int group_size) {
+  if (check_dimensions(batch, n, k, group_size) != FK_W4A16_OK) {
+    return 0;
+  }
+  DeviceInfo* info = nullptr;
+  if (device_info(&info) != FK_W4A16_OK) {
+    return 0;
+  }
+  const Plan plan =
+      make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  return workspace_bytes_for(plan);
+}
+
+int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  FK_TRY(check_pointer(workspace, "workspace", 256));
+  if (workspace_bytes < kTicketBytes) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "workspace is smaller than the ticket area");
+  }
+  FK_TRY_CUDA(cudaMemsetAsync(workspace, 0, kTicketBytes, static_cast<cudaStream_t>(stream)));
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_gemv(const void* activations, const void* packets, void* output, void* workspace,
+                  size_t workspace_bytes, int batch, int n, int k, int group_size,
+                  int packet_stride_bytes, int dtype, void* stream) {
+  FK_TRY(check_dimensions(batch, n, k, group_size));
+  FK_TRY(check_stride(group_size, packet_stride_bytes));
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(activations, "activations", 16));
+  FK_TRY(check_pointer(packets, "packets", 16));
+  FK_TRY(check_pointer(output, "output", 8));
+  FK_TRY(check_pointer(workspace, "workspace", 256));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  const Plan plan =
+      make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  if (plan.stages < 2) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
+  }
+  if (workspace_bytes < workspace_bytes_for(plan)) {
+    std::ostringstream oss;
+    oss << "workspace_bytes=" << workspace_bytes << " is smaller than the required "
+        << workspace_bytes_for(plan);
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+  }
+  const int num_tiles = n / kTileCols;
+  if (static_cast<long long>(plan.row_tiles) * num_tiles > kTicketCapacity) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * batch exceeds the ticket area of a workspace");
+  }
+
+  GemvParams params{};
+  params.act = activations;
+  params.packets = static_cast<const uint8_t*>(packets);
+  params.out = output;
+  params.tickets = static_cast<int*>(workspace);
+  params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
+  params.status = info->status_word;
+  params.m = batch;
+  params.n = n;
+  params.k = k;
+  params.num_groups = k / group_size;
+  params.num_tiles = num_tiles;
+  params.active_warps = plan.active_warps;
+  params.stages = plan.stages;
+  params.total_packets = static_cast<long long>(num_tiles) * params.num_groups;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const int max_smem = info->max_smem_optin;
+  return dispatch(group_size, plan.m_tile, dtype, [&](auto g, auto mt, auto e) {
+    return launch_stream<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
+                                                                                 max_smem, s);
+  });
+}
+
+int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,
+                          int n, int k, int group_size, int packet_stride_bytes,
+                          int split_k_slices, int dtype, void* stream) {
+  FK_TRY(check_dimensions(batch, n, k, group_size));
+  FK_TRY(check_stride(group_size, packet_stride_bytes));
+  FK_TRY(check_dtype(dtype));
+  if (split_k_slices <= 1) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "split_k_slices must be greater than 1");
+  }
+  const int num_groups = k / group_size;
+  if (split_k_slices > num_groups) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                "split_k_slices must not exceed the number of groups");
+  }
+  FK_TRY(check_pointer(activations, "activations", 16));
+  FK_TRY(check_pointer(packets, "packets", 16));
+  FK_TRY(check_pointer(partials, "partials", 4));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+
+  const int m_tile = m_tile_for_batch(batch);
+  SplitKParams params{};
+  params.base.act = activations;
+  params.base.packets = static_cast<const uint8_t*>(packets);
+  params.base.status = info->status_word;
+  params.base.m = batch;
+  params.base.n = n;
+  params.base.k = k;
+  params.base.num_groups = num_groups;
+  params.base.num_tiles = n / kTileCols;
+  params.base.stages = 2;
+  params.base.total_packets = static_cast<long long>(params.base.num_tiles) * num_groups;
+  params.partials = partials;
+  params.slices = split_k_slices;
+  params.groups_per_slice = (num_groups + split_k_slices - 1) / split_k_slices;
+  const int row_tiles = (batch + m_tile - 1) / m_tile;
+  auto* s = static_cast<cudaStream_t>(stream);
+  const int max_smem = info->max_smem_optin;
+  return dispatch(group_size, m_tile, dtype, [&](auto g, auto mt, auto e) {
+    return launch_split_k<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, row_tiles,
+                                                                                  max_smem, s);
+  });
+}
+
+int fk_w4a16_reduce_partials(const float* partials, void* output, int batch, int n,
+                             int split_k_slices, int dtype, void* stream) {
+  if (batch <= 0 || n <= 0 || split_k_slices <= 1) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                "batch, n, and split_k_slices must be positive with split_k_slices > 1");
+  }
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(partials, "partials", 4));
+  FK_TRY(check_pointer(output, "output", 2));
+  const long long total = static_cast<long long>(batch) * n;
+  const int grid = static_cast<int>((total + 255) / 256);
+  auto* s = static_cast<cudaStream_t>(stream);
+  auto* out = static_cast<uint16_t*>(output);
+  if (dtype == FK_W4A16_DTYPE_BF16) {
+    reduce_partials_kernel<BF16><<<grid, 256, 0, s>>>(partials, out, total, split_k_slices);
+  } else {
+    reduce_partials_kernel<F16><<<grid, 256, 0, s>>>(partials, out, total, split_k_slices);
+  }
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_dequant_rowmajor(const void* q, const void* alpha, const void* beta, void* weight,
+                              int n, int k, int group_size, int dtype, void* stream) {
+  FK_TRY(check_dimensions(1, n, k, group_size));
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(q, "q", 4));
+  FK_TRY(check_pointer(alpha, "alpha", 2));
+  FK_TRY(check_pointer(beta, "beta", 2));
+  FK_TRY(check_pointer(weight, "weight", 16));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  const long long total_words = static_cast<long long>(n) * (k / 8);
+  const int grid = grid_for(total_words, 256, info->sm_count);
+  auto* s = static_cast<cudaStream_t>(stream);
+  const int rc = dispatch(group_size, 1, dtype, [&](auto g, auto, auto e) {
+    dequant_rowmajor_kernel<decltype(g)::value, decltype(e)><<<grid, 256, 0, s>>>(
+        static_cast<const uint8_t*>(q), static_cast<const uint16_t*>(alpha),
+        static_cast<const uint16_t*>(beta), static_cast<uint16_t*>(weight), total_words, k,
+        k / group_size);
+    return FK_W4A16_OK;
+  });
+  FK_TRY(rc);
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_dequant_packets(const void* packets, void* weight, int n, int k, int group_size,
+                             int packet_stride_bytes, int dtype, void* stream) {
+  FK_TRY(check_dimensions(1, n, k, group_size));
+  FK_TRY(check_stride(group_size, packet_stride_bytes));
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(packets, "packets", 4));
+  FK_TRY(check_pointer(weight, "weight", 16));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  const long long total_words = static_cast<long long>(n) * (k / 8);
+  const int grid = grid_for(total_words, 256, info->sm_count);
+  auto* s = static_cast<cudaStream_t>(stream);
+  const int rc = dispatch(group_size, 1, dtype, [&](auto g, auto, auto e) {
+    dequant_packets_kernel<decltype(g)::value, decltype(e)><<<grid, 256, 0, s>>>(
+        static_cast<const uint8_t*>(packets), static_cast<uint16_t*>(weight), total_words, k,
+        k / group_size);
+    return FK_W4A16_OK;
+  });
+  FK_TRY(rc);
+  FK_TRY_CUDA(cudaGetLastError());
+  return FK_W4A16_OK;
+}
+
+int fk_w4a16_cublaslt_matmul(const void* activations, const void* weight, void* output,
+                             void* lt_workspace, size_t lt_workspace_bytes, int batch, int n,
+                             int k, int dtype, void* stream) {
+  if (batch <= 0 || n <= 0 || k <= 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "batch, n, and k must be positive");
+  }
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(activations, "activations", 2));
+  FK_TRY(check_pointer(weight, "weight", 2));
+  FK_TRY(check_pointer(output, "output", 2));
+
+  cublasStatus_t create_status = CUBLAS_STATUS_SUCCESS;
+  std::call_once(g_lt_once, [&] { create_status = cublasLtCreate(&g_lt_handle); });
+  if (create_status != CUBLAS_STATUS_SUCCESS || g_lt_handle == nullptr) {
+    return fail(FK_W4A16_ERR_CUDA, "cublasLtCreate failed");
+  }
+
+  // Row-major C[batch, n] = A[batch, k] . B[n, k]^T is, in cuBLAS's column-major terms,
+  // C^T[n, batch] = op_T(B as [k, n], ld k) . (A as [k, batch], ld k).
+  const cudaDataType_t type = dtype == FK_W4A16_DTYPE_BF16 ? CUDA_R_16BF : CUDA_R_16F;
+  cublasLtMatmulDesc_t op = nullptr;
+  cublasLtMatrixLayout_t w_layout = nullptr;
+  cublasLtMatrixLayout_t a_layout = nullptr;
+  cublasLtMatrixLayout_t c_layout = nullptr;
+  cublasLtMatmulPreference_t pref = nullptr;
+  int rc = FK_W4A16_OK;
+  auto cleanup = [&] {
+    if (pref != nullptr) cublasLtMatmulPreferenceDestroy(pref);
+    if (c_layout != nullptr) cublasLtMatrixLayoutDestroy(c_layout);
+    if (a_layout != nullptr) cublasLtMatrixLayoutDestroy(a_layout);
+    if (w_layout != nullptr) cublasLtMatrixLayoutDestroy(w_layout);
+    if (op != nullptr) cublasLtMatmulDescDestroy(op);
+  };
+  auto body = [&]() -> int {
+    const cublasOperation_t transpose = CUBLAS_OP_T;
+    FK_TRY_CUBLAS(cublasLtMatmulDescCreate(&op, CUBLAS_COMPUTE_32F, CUDA_R_32F));
+    FK_TRY_CUBLAS(cublasLtMatmulDescSetAttribute(op, CUBLASLT_MATMUL_DESC_TRANSA, &transpose,
+                                                 sizeof(transpose)));
+    FK_TRY_CUBLAS(cublasLtMatrixLayoutCreate(&w_layout, type, k, n, k));
+    FK_TRY_CUBLAS(cublasLtMatrixLayoutCreate(&a_layout, type, k, batch, k));
+    FK_TRY_CUBLAS(cublasLtMatrixLayoutCreate(&c_layout, type, n, batch, n));
+    FK_TRY_CUBLAS(cublasLtMatmulPreferenceCreate(&pref));
+    size_t ws_bytes = lt_workspace == nullptr ? 0 : lt_workspace_bytes;
+    void* ws = lt_workspace;
+    cublasLtMatmulHeuristicResult_t heuristic{};
+    int found = 0;
+    for (int attempt = 0; attempt < 2 && found == 0; ++attempt) {
+      FK_TRY_CUBLAS(cublasLtMatmulPreferenceSetAttribute(
+          pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes, sizeof(ws_bytes)));
+      FK_TRY_CUBLAS(cublasLtMatmulAlgoGetHeuristic(g_lt_handle, op, w_layout, a_layout, c_layout,
+                                                   c_layout, pref, 1, &heuristic, &found));
+      if (found == 0) {  // retry without workspace, as the reference does
+        ws_bytes = 0;
+        ws = nullptr;
+      }
+    }
+    if (found == 0) {
+      return fail(FK_W4A16_ERR_CUDA, "cublasLtMatmulAlgoGetHeuristic returned no usable algorithm");
+    }
+    const float one = 1.0f;
+    const float zero = 0.0f;
+    FK_TRY_CUBLAS(cublasLtMatmul(g_lt_handle, op, &one, weight, w_layout, activations, a_layout,
+                                 &zero, output, c_layout, output, c_layout, &heuristic.algo, ws,
+                                 ws_bytes, static_cast<cudaStream_t>(stream)));
+    return FK_W4A16_OK;
+  };
+  rc = body();
+  cleanup();
+  return rc;
+}
+
+int fk_w4a16_device_status(int* status) {
+  if (status == nullptr) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "status must not be null");
+  }
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  FK_TRY_CUDA(cudaDeviceSynchronize());
+  FK_TRY_CUDA(cudaMemcpy(status, info->status_word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status != 0) {
+    FK_TRY_CUDA(cudaMemset(info->status_word, 0, sizeof(int)));
+  }
+  return FK_W4A16_OK;
+}
+
+}  // extern "C"

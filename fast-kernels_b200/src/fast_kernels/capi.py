@@ -1,0 +1,116 @@
+"""ctypes binding of libfk_w4a16.so -- the C ABI declared in include/fk_w4a16.h.
+
+This is the thinnest way into the CUDA library: every function takes raw device addresses
+(``tensor.data_ptr()``) and a stream handle. The parity tests and ``bench.py`` go through here;
+``fast_kernels.ops`` (the reference-compatible Python API) reaches the same entry points through
+the pybind11 module instead.
+
+There is no CPU fallback: if the shared library is missing, loading raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+from pathlib import Path
+
+OK = 0
+ERR_INVALID_ARGUMENT = -1
+ERR_CUDA = -2
+ERR_DEVICE_STATUS = -3
+
+DTYPE_F16 = 0
+DTYPE_BF16 = 1
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfk_w4a16.so"
+
+_c_void_p = ctypes.c_void_p
+_c_int = ctypes.c_int
+_c_size_t = ctypes.c_size_t
+
+# name -> (restype, argtypes); mirrors include/fk_w4a16.h one to one.
+SIGNATURES: dict[str, tuple[object, list[object]]] = {
+    "fk_w4a16_last_error": (ctypes.c_char_p, []),
+    "fk_w4a16_version": (ctypes.c_char_p, []),
+    "fk_w4a16_cuda_arch": (ctypes.c_char_p, []),
+    "fk_w4a16_packet_stride_bytes": (_c_int, [_c_int]),
+    "fk_w4a16_pack_packets": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
+    "fk_w4a16_group_sums": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
+    "fk_w4a16_workspace_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
+    "fk_w4a16_workspace_init": (_c_int, [_c_void_p, _c_size_t, _c_void_p]),
+    "fk_w4a16_gemv": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
+         _c_int, _c_int, _c_void_p],
+    ),
+    "fk_w4a16_gemv_split_k": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+         _c_void_p],
+    ),
+    "fk_w4a16_reduce_partials": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p]),
+    "fk_w4a16_dequant_rowmajor": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
+    "fk_w4a16_dequant_packets": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
+    "fk_w4a16_cublaslt_matmul": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
+         _c_void_p],
+    ),
+    "fk_w4a16_device_status": (_c_int, [ctypes.POINTER(_c_int)]),
+    "fk_w4a16_set_launch_config": (_c_int, [_c_int, _c_int, _c_int]),
+}
+
+
+class FkError(RuntimeError):
+    """A C-ABI call returned an error code."""
+
+    def __init__(self, code: int, message: str) -> None:
+        super().__init__(message)
+        self.code = code
+
+
+@lru_cache(maxsize=1)
+def load_library() -> ctypes.CDLL:
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python fast-kernels_b200/build.py` "
+            "(there is no CPU fallback for the W4A16 kernels)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def check(code: int) -> None:
+    """Raise ValueError / FkError for a non-zero return code, as the C++ launchers do."""
+    if code == OK:
+        return
+    message = (load_library().fk_w4a16_last_error() or b"").decode()
+    if code == ERR_INVALID_ARGUMENT:
+        raise ValueError(message)
+    raise FkError(code, message)
+
+
+def packet_stride_bytes(group_size: int) -> int:
+    value = load_library().fk_w4a16_packet_stride_bytes(group_size)
+    if value < 0:
+        check(value)
+    return int(value)
+
+
+def device_status() -> int:
+    status = _c_int(0)
+    check(load_library().fk_w4a16_device_status(ctypes.byref(status)))
+    return int(status.value)

@@ -1,0 +1,125 @@
+/*
+ * fk_w4a16.h -- C ABI of the sm_100a W4A16 decode-GEMV library (libfk_w4a16.so).
+ *
+ * This is the boundary a host program binds to: plain pointers and sizes, no C++ or torch types,
+ * no exceptions. Every pointer is a DEVICE address unless the comment says otherwise; `stream` is
+ * a cudaStream_t passed as void* (NULL = the default stream). All work is enqueued on `stream`
+ * and nothing synchronises the host. Functions return FK_W4A16_OK or a negative error code;
+ * fk_w4a16_last_error() gives the message for the calling thread.
+ *
+ * Each entry point names the function of the reference (SamMausberg/fast-kernels) that it
+ * replaces, as file:line in that project.
+ *
+ * Data layout ("ARC packets", csrc/kernels/decode_quant_linear/arc_w4a16.cu:87-122): the weight
+ * matrix W[n, k] is cut into tiles of 128 output columns and groups of `group_size` input
+ * features. Packet (tile t, group g) starts at byte (t * k/group_size + g) * stride and holds
+ *   uint32 words[group_size/8][128]  word (r, c): nibble i (bits 4i..4i+3) = q[128t + c, g*G + 8r + i]
+ *   16-bit alpha[128]                scale of column 128t + c in group g
+ *   16-bit beta[128]                 offset, beta = -(alpha * zero_point) rounded in the 16-bit type
+ * with stride = 64 * group_size + 512 bytes, and W[n, k] = alpha * q + beta.
+ */
+#ifndef FK_W4A16_H_
+#define FK_W4A16_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FK_W4A16_API __attribute__((visibility("default")))
+#else
+#define FK_W4A16_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FK_W4A16_OK 0
+#define FK_W4A16_ERR_INVALID_ARGUMENT (-1) /* maps to std::invalid_argument / ValueError */
+#define FK_W4A16_ERR_CUDA (-2)             /* a CUDA or cuBLAS call failed: std::runtime_error */
+#define FK_W4A16_ERR_DEVICE_STATUS (-3)    /* a bounded device-side wait gave up */
+
+/* 16-bit element type of activations, scales, offsets and outputs. */
+#define FK_W4A16_DTYPE_F16 0
+#define FK_W4A16_DTYPE_BF16 1
+
+/* Message for the last error on the calling thread ("" if none). Host pointer, valid until the
+ * thread's next failing call. */
+FK_W4A16_API const char* fk_w4a16_last_error(void);
+
+/* Library version string and the CUDA architecture it was compiled for ("100a"). Host pointers. */
+FK_W4A16_API const char* fk_w4a16_version(void);
+FK_W4A16_API const char* fk_w4a16_cuda_arch(void);
+
+/* Packet stride in bytes for a group size (32, 64 or 128), or a negative error code.
+ * Reference: expected_packet_stride_bytes, arc_w4a16.cu:23-26. */
+FK_W4A16_API int fk_w4a16_packet_stride_bytes(int group_size);
+
+/* q_u8[n, k/2] (low nibble = even k), alpha/beta[n, k/group_size] -> packets.
+ * Reference: pack_arc_w4a16_packets, arc_w4a16.cu:649-669 (kernel :87-122). */
+FK_W4A16_API int fk_w4a16_pack_packets(const void* q, const void* alpha, const void* beta, void* packets, int n,
+                          int k, int group_size, int packet_stride_bytes, void* stream);
+
+/* sums[batch, k/group_size] (fp32) = per-group sums of the activations.
+ * Reference: compute_arc_w4a16_group_sums, arc_w4a16.cu:671-685 (kernel :124-158). */
+FK_W4A16_API int fk_w4a16_group_sums(const void* activations, float* sums, int batch, int k, int group_size,
+                        int dtype, void* stream);
+
+/* Scratch the fused GEMV needs for a problem, in bytes (a multiple of 256; never 0). The caller
+ * allocates it on the device, zero-fills it ONCE (fk_w4a16_workspace_init or cudaMemset) and may
+ * then reuse it for any number of calls whose requirement is not larger. Calls that run
+ * concurrently on the GPU need separate workspaces. */
+FK_W4A16_API size_t fk_w4a16_workspace_bytes(int batch, int n, int k, int group_size);
+FK_W4A16_API int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* The hot path: out[batch, n] = activations[batch, k] . W^T in ONE launch -- activation group
+ * sums, int4 unpack, scale/offset, fp32 accumulation, split-K finish and the 16-bit rounding of
+ * the output all happen inside it. batch <= 4 streams on CUDA cores; larger batches are
+ * processed 4 rows at a time.
+ * Reference: arc_w4a16_forward, arc_w4a16.cu:687-707, together with the group-sum prepass
+ * (:671-685) and the split-K pair (:709-751) that its Python caller chains around it
+ * (src/fast_kernels/ops/decode_quant_linear.py:383-439). */
+FK_W4A16_API int fk_w4a16_gemv(const void* activations, const void* packets, void* output, void* workspace,
+                  size_t workspace_bytes, int batch, int n, int k, int group_size,
+                  int packet_stride_bytes, int dtype, void* stream);
+
+/* Caller-visible split-K: partials[split_k_slices, batch, n] (fp32), slice s covering groups
+ * [s * ceil(NG/S), ...). Reference: arc_w4a16_forward_split_k, arc_w4a16.cu:709-737. */
+FK_W4A16_API int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,
+                          int n, int k, int group_size, int packet_stride_bytes,
+                          int split_k_slices, int dtype, void* stream);
+
+/* output[batch, n] = round16(sum over slices, in slice order).
+ * Reference: reduce_arc_w4a16_split_k_partials, arc_w4a16.cu:739-751. */
+FK_W4A16_API int fk_w4a16_reduce_partials(const float* partials, void* output, int batch, int n,
+                             int split_k_slices, int dtype, void* stream);
+
+/* weight[n, k] (16-bit) = alpha * q + beta, bit-exact with the reference.
+ * Reference: dequant_w4a16_to_fp16, arc_w4a16.cu:753-770. */
+FK_W4A16_API int fk_w4a16_dequant_rowmajor(const void* q, const void* alpha, const void* beta, void* weight,
+                              int n, int k, int group_size, int dtype, void* stream);
+
+/* The same from packets. Reference: dequant_arc_w4a16_packets_to_fp16, arc_w4a16.cu:772-789. */
+FK_W4A16_API int fk_w4a16_dequant_packets(const void* packets, void* weight, int n, int k, int group_size,
+                             int packet_stride_bytes, int dtype, void* stream);
+
+/* Vendor baseline subject: output[batch, n] = activations[batch, k] . weight[n, k]^T through
+ * cuBLASLt with fp32 compute. `lt_workspace` may be NULL when lt_workspace_bytes is 0.
+ * Reference: cublaslt_fp16_with_weight, arc_w4a16.cu:791-803 (run_cublaslt_matmul :577-645). */
+FK_W4A16_API int fk_w4a16_cublaslt_matmul(const void* activations, const void* weight, void* output,
+                             void* lt_workspace, size_t lt_workspace_bytes, int batch, int n,
+                             int k, int dtype, void* stream);
+
+/* Reads (and clears) the device status word of the current device into *status (host pointer):
+ * 0 = no device-side wait ever timed out. Synchronises the device. */
+FK_W4A16_API int fk_w4a16_device_status(int* status);
+
+/* Launch-shape knobs of the fused GEMV, for tuning and tests: warps per CTA (1..16, 0 = auto),
+ * ring stages per warp (2..8, 0 = auto) and CTAs in the grid (0 = one per SM). Process-wide. */
+FK_W4A16_API int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FK_W4A16_H_ */

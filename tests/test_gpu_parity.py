@@ -1,0 +1,248 @@
+"""GPU parity: the CUDA library, called through its C ABI, against the CPU oracle.
+
+Bars: bit-exact for pack / dequant / group sums (integer and byte work, plus the fixed-order fp32
+sums); for the GEMV, max relative error <= 1e-2 against the fp64 dequant-matvec oracle (floor on
+the denominator: 1e-3 of the row's largest |y|), and the reference tests' own
+assert_close(atol=1e-2, rtol=1e-2) against the golden outputs.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+from fast_kernels import capi
+from fast_kernels.workloads import LayerShape, make_problem
+from oracle import w4a16_oracle as oracle
+from w4a16_testlib import (
+    Workspace,
+    capi_gemv,
+    capi_pack,
+    dev_bits,
+    golden_case_names,
+    host_bits,
+    load_golden,
+    stream_ptr,
+)
+
+pytestmark = pytest.mark.gpu
+
+GEMV_REL_TOL = 1e-2
+WS = Workspace()
+
+
+@pytest.fixture(autouse=True)
+def _device_status_is_clean():
+    yield
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0, "a bounded device-side wait timed out"
+
+
+def _check_gemv(problem: dict, shape: LayerShape, code: int) -> None:
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, shape.group_size)
+    out = capi_gemv(capi, WS, act, packets, shape.n, shape.k, shape.group_size, code)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all(), "some outputs were never written"
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
+                          oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]),
+                          shape.group_size, code)
+    err = oracle.max_rel_err(got, y64)
+    assert err <= GEMV_REL_TOL, f"max relative error {err:.3e} for {shape}"
+    # a second call on the same workspace must give the same bits (tickets reset themselves)
+    again = capi_gemv(capi, WS, act, packets, shape.n, shape.k, shape.group_size, code)
+    torch.cuda.synchronize()
+    assert torch.equal(again.view(torch.int16), out.view(torch.int16))
+
+
+@pytest.mark.parametrize("name", golden_case_names())
+def test_gemv_matches_reference_golden_outputs(name: str) -> None:
+    case = load_golden(name)
+    if case is None:
+        pytest.skip("this torch build does not reproduce the fixture's seeded inputs")
+    meta = case["meta"]
+    group, n, k = meta["group_size"], meta["n"], meta["k"]
+    q = torch.from_numpy(case["q_u8"]).cuda()
+    alpha, beta, act = (dev_bits(case[key], 0) for key in ("alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, group)
+    out = capi_gemv(capi, WS, act, packets, n, k, group, 0)
+    expected = dev_bits(case["output"], 0)
+    # the reference's own bar (tests/gpu/test_decode_quant_linear.py:102)
+    torch.testing.assert_close(out, expected, atol=1e-2, rtol=1e-2)
+    y64 = oracle.gemv_f64(case["activations"], case["q_u8"], case["alpha"], case["beta"], group, 0)
+    assert oracle.max_rel_err(out.float().cpu().numpy(), y64) <= GEMV_REL_TOL
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_pack_and_dequant_are_bit_exact(group: int, dtype: str) -> None:
+    code = oracle.dtype_code(dtype)
+    shape = LayerShape("t", 384, group * 6, group_size=group, dtype=dtype, zero_point=None,
+                       scale_range=(0.001, 0.05))
+    problem = make_problem(shape, seed=100 + group)
+    q, alpha, beta = (problem[k].cuda() for k in ("q_u8", "alpha", "beta"))
+    lib = capi.load_library()
+    packets = capi_pack(capi, q, alpha, beta, group)
+    want_packets = oracle.pack_packets(problem["q_u8"].numpy(), oracle.bits_of(problem["alpha"]),
+                                       oracle.bits_of(problem["beta"]), group)
+    assert np.array_equal(packets.cpu().numpy(), want_packets)
+
+    want_weight = oracle.dequant_rowmajor(problem["q_u8"].numpy(), oracle.bits_of(problem["alpha"]),
+                                          oracle.bits_of(problem["beta"]), group, code)
+    weight = torch.empty((shape.n, shape.k), dtype=alpha.dtype, device="cuda")
+    capi.check(lib.fk_w4a16_dequant_rowmajor(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(),
+                                             weight.data_ptr(), shape.n, shape.k, group, code, stream_ptr()))
+    assert np.array_equal(host_bits(weight), want_weight)
+    weight.zero_()
+    capi.check(lib.fk_w4a16_dequant_packets(packets.data_ptr(), weight.data_ptr(), shape.n, shape.k,
+                                            group, capi.packet_stride_bytes(group), code, stream_ptr()))
+    assert np.array_equal(host_bits(weight), want_weight)
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_group_sums_are_bit_exact(group: int, dtype: str) -> None:
+    code = oracle.dtype_code(dtype)
+    gen = torch.Generator().manual_seed(5 + group)
+    act = torch.randn((5, group * 9), generator=gen).to(torch.float16 if code == 0 else torch.bfloat16)
+    dev = act.cuda()
+    sums = torch.empty((5, 9), dtype=torch.float32, device="cuda")
+    capi.check(capi.load_library().fk_w4a16_group_sums(dev.data_ptr(), sums.data_ptr(), 5, group * 9,
+                                                       group, code, stream_ptr()))
+    want = oracle.group_sums(oracle.bits_of(act), group, code)
+    assert np.array_equal(sums.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 7])
+def test_gemv_small_shapes(group: int, batch: int, dtype: str) -> None:
+    # odd tile/group counts so that warp runs start and end inside tiles
+    shape = LayerShape("t", 128 * 5, group * 7, group_size=group, batch=batch, dtype=dtype,
+                       zero_point=None, scale_range=(0.001, 0.05))
+    _check_gemv(make_problem(shape, seed=7 * group + batch), shape, oracle.dtype_code(dtype))
+
+
+@pytest.mark.parametrize(
+    ("n", "k", "group", "dtype"),
+    [
+        (128, 128, 128, "fp16"),      # a single packet
+        (128, 64, 32, "bf16"),        # two tiny packets
+        (4096, 4096, 128, "fp16"),    # the reference case: fewer packets than resident warps
+        (6144, 4096, 128, "bf16"),    # Llama-3-8B qkv
+        (4096, 14336, 128, "bf16"),   # down_proj: long K, runs shorter than a tile
+        (13824, 5120, 32, "fp16"),    # 13B MLP, smallest group
+        (13824, 5120, 64, "fp16"),
+    ],
+)
+def test_gemv_layer_shapes(n: int, k: int, group: int, dtype: str) -> None:
+    shape = LayerShape("t", n, k, group_size=group, dtype=dtype, zero_point=None)
+    _check_gemv(make_problem(shape), shape, oracle.dtype_code(dtype))
+
+
+@pytest.mark.parametrize(("warps", "stages", "ctas"), [(1, 2, 3), (3, 2, 0), (8, 3, 0), (16, 2, 0), (5, 4, 11)])
+def test_gemv_is_independent_of_launch_shape(warps: int, stages: int, ctas: int) -> None:
+    lib = capi.load_library()
+    shape = LayerShape("t", 128 * 9, 128 * 11, batch=2, dtype="fp16", zero_point=None)
+    problem = make_problem(shape, seed=99)
+    try:
+        capi.check(lib.fk_w4a16_set_launch_config(warps, stages, ctas))
+        _check_gemv(problem, shape, 0)
+    finally:
+        capi.check(lib.fk_w4a16_set_launch_config(0, 0, 0))
+
+
+def test_gemv_full_size_properties() -> None:
+    """At a size the CPU oracle would take too long on: linearity in the activations and
+    agreement between the fused path and the caller-visible split-K path."""
+    lib = capi.load_library()
+    shape = LayerShape("mlp_up", 28672, 8192, dtype="bf16")
+    problem = make_problem(shape)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    del q
+    y1 = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1).float()
+    y2 = capi_gemv(capi, WS, (act * 2).contiguous(), packets, shape.n, shape.k, 128, 1).float()
+    scale = y1.abs().max().item()
+    assert (y2 - 2 * y1).abs().max().item() <= 2e-2 * scale  # doubling is exact up to bf16 rounding of y
+    partials = torch.empty((4, 1, shape.n), dtype=torch.float32, device="cuda")
+    capi.check(lib.fk_w4a16_gemv_split_k(act.data_ptr(), packets.data_ptr(), partials.data_ptr(), 1,
+                                         shape.n, shape.k, 128, 8704, 4, 1, stream_ptr()))
+    via_split = partials.sum(0)
+    assert (via_split - y1).abs().max().item() <= 1e-2 * scale
+    # and a sample of rows against the fp64 oracle
+    rows = slice(0, 512)
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"][rows].numpy(),
+                          oracle.bits_of(problem["alpha"][rows]), oracle.bits_of(problem["beta"][rows]), 128, 1)
+    assert oracle.max_rel_err(y1[:, rows].cpu().numpy(), y64) <= GEMV_REL_TOL
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize(("batch", "slices"), [(1, 2), (8, 4), (3, 7)])
+def test_split_k_and_reduce(batch: int, slices: int, dtype: str) -> None:
+    """The caller-visible split-K pair (reference: arc_w4a16.cu:709-751; its test :171-207)."""
+    code = oracle.dtype_code(dtype)
+    lib = capi.load_library()
+    shape = LayerShape("t", 256, 128 * 7, batch=batch, dtype=dtype, zero_point=None)
+    problem = make_problem(shape, seed=4242)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    partials = torch.full((slices, batch, shape.n), float("nan"), dtype=torch.float32, device="cuda")
+    capi.check(lib.fk_w4a16_gemv_split_k(act.data_ptr(), packets.data_ptr(), partials.data_ptr(), batch,
+                                         shape.n, shape.k, 128, 8704, slices, code, stream_ptr()))
+    out = torch.empty((batch, shape.n), dtype=act.dtype, device="cuda")
+    capi.check(lib.fk_w4a16_reduce_partials(partials.data_ptr(), out.data_ptr(), batch, shape.n, slices,
+                                            code, stream_ptr()))
+    torch.cuda.synchronize()
+    # reduce: slices added in index order, one rounding
+    want = partials[0].clone()
+    for s in range(1, slices):
+        want = want + partials[s]
+    assert torch.equal(out, want.to(act.dtype))
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
+                          oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]), 128, code)
+    assert oracle.max_rel_err(out.float().cpu().numpy(), y64) <= GEMV_REL_TOL
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_cublaslt_subject_matches_oracle(dtype: str) -> None:
+    code = oracle.dtype_code(dtype)
+    lib = capi.load_library()
+    shape = LayerShape("t", 512, 1024, batch=4, dtype=dtype, zero_point=None)
+    problem = make_problem(shape, seed=17)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    weight = torch.empty((shape.n, shape.k), dtype=act.dtype, device="cuda")
+    capi.check(lib.fk_w4a16_dequant_rowmajor(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(),
+                                             weight.data_ptr(), shape.n, shape.k, 128, code, stream_ptr()))
+    out = torch.empty((4, shape.n), dtype=act.dtype, device="cuda")
+    lt_ws = torch.empty(8 << 20, dtype=torch.uint8, device="cuda")
+    capi.check(lib.fk_w4a16_cublaslt_matmul(act.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                                            lt_ws.data_ptr(), lt_ws.numel(), 4, shape.n, shape.k, code,
+                                            stream_ptr()))
+    torch.cuda.synchronize()
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
+                          oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]), 128, code)
+    # the weight is rounded to 16 bits before the GEMM here, hence the looser bar (reference: 1e-2 abs/rel)
+    assert np.allclose(out.float().cpu().numpy(), y64, rtol=2e-2, atol=2e-2)
+
+
+def test_gemv_respects_the_stream() -> None:
+    """Work is enqueued on the stream it is given (reference test :248-281)."""
+    shape = LayerShape("t", 128, 256, dtype="fp16", zero_point=None)
+    problem = make_problem(shape, seed=2112)
+    q, alpha, beta = (problem[k].cuda() for k in ("q_u8", "alpha", "beta"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    expected_act = problem["activations"].cuda()
+    act = torch.zeros_like(expected_act)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        torch.cuda._sleep(50_000_000)
+        act.copy_(expected_act)
+        out = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 0)
+    side.synchronize()
+    torch.cuda.synchronize()
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
+                          oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]), 128, 0)
+    assert oracle.max_rel_err(out.float().cpu().numpy(), y64) <= GEMV_REL_TOL
