@@ -11,6 +11,7 @@
 #include <mutex>
 #include <sstream>
 #include <string>
+#include <type_traits>
 
 #include "w4a16_common.cuh"
 #include "w4a16_gemv_stream.cuh"
@@ -83,6 +84,9 @@ int check_dimensions(int batch, int n, int k, int group_size) {
   }
   if (n % kTileCols != 0) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n must be a multiple of 128");
+  }
+  if (static_cast<long long>(n / kTileCols) * (k / group_size) > (1LL << 30)) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * k is too large: more than 2^30 packets");
   }
   return FK_W4A16_OK;
 }
@@ -157,7 +161,6 @@ int device_info(DeviceInfo** out) {
 // ---- launch planning for the fused GEMV --------------------------------------------------
 constexpr size_t kTicketBytes = 256 * 1024;  // fixed ticket area at the start of a workspace
 constexpr int kTicketCapacity = static_cast<int>(kTicketBytes / sizeof(int));
-constexpr int kDefaultWarps = 8;
 constexpr int kMaxWarps = 16;
 constexpr int kMaxStages = 8;
 
@@ -189,9 +192,10 @@ struct Plan {
   int m_tile = 1;
   int row_tiles = 1;
   int warps = 1;
-  int stages = 2;
+  int stages = 0;  // < 2 means the configuration does not fit in shared memory
   int grid_x = 1;
   int active_warps = 1;
+  uint32_t total_packets = 0;
   size_t smem_bytes = 0;
   size_t scratch_bytes = 0;
 };
@@ -204,9 +208,17 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.m_tile = m_tile_for_batch(batch);
   plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
+  plan.total_packets = static_cast<uint32_t>(total_packets);
   const int stage_bytes = packet_stride(group_size) + (plan.m_tile * group_size * 2);
 
-  int warps = cfg.warps > 0 ? cfg.warps : kDefaultWarps;
+  // Default: as many warps as fit with a two-deep ring each (more warps hide more latency than
+  // deeper rings do), at most 16.
+  int warps = cfg.warps;
+  if (warps <= 0) {
+    const int per_warp = (2 * stage_bytes) + (2 * plan.m_tile * kTileCols * 4) + 16;
+    warps = (max_smem - 256) / per_warp;
+    warps = warps > kMaxWarps ? kMaxWarps : (warps < 1 ? 1 : warps);
+  }
   warps = warps > kMaxWarps ? kMaxWarps : warps;
   const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
   long long workers = static_cast<long long>(ctas) * warps;
@@ -219,16 +231,18 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.grid_x = static_cast<int>((workers + warps - 1) / warps);
   plan.active_warps = static_cast<int>(workers);
 
-  const size_t barrier_bytes = ((static_cast<size_t>(warps) * kMaxStages * 8) + 127) & ~size_t{127};
-  int stages = static_cast<int>((static_cast<size_t>(max_smem) - barrier_bytes) /
-                                (static_cast<size_t>(warps) * stage_bytes));
   const int wanted = cfg.stages > 0 ? cfg.stages : 4;
-  stages = stages > wanted ? wanted : stages;
-  stages = stages > kMaxStages ? kMaxStages : stages;
-  plan.stages = stages;  // < 2 means "does not fit"; the caller reports it
-  plan.smem_bytes = (((static_cast<size_t>(warps) * stages * 8) + 127) & ~size_t{127}) +
-                    (static_cast<size_t>(warps) * stages * stage_bytes);
-  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.active_warps * 2 *
+  int stages = 0;
+  for (int candidate = kMaxStages < wanted ? kMaxStages : wanted; candidate >= 2; --candidate) {
+    if (stream_smem_plan(warps, candidate, stage_bytes, plan.m_tile).total <=
+        static_cast<uint32_t>(max_smem)) {
+      stages = candidate;
+      break;
+    }
+  }
+  plan.stages = stages;
+  plan.smem_bytes = stream_smem_plan(warps, stages < 2 ? 2 : stages, stage_bytes, plan.m_tile).total;
+  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
                        (plan.m_tile * kTileCols) * sizeof(float);
   return plan;
 }
@@ -237,8 +251,8 @@ size_t workspace_bytes_for(const Plan& plan) {
   return kTicketBytes + ((plan.scratch_bytes + 255) & ~size_t{255});
 }
 
-// cudaFuncSetAttribute is per function and device; raising it to the device limit once covers
-// every later launch shape. `flags` must be distinct per kernel instantiation.
+// Opts a kernel in to the device's full dynamic shared memory, once per function and device
+// (minus whatever the kernel declares statically). `flags` must be distinct per instantiation.
 template <class Kernel>
 int ensure_smem_optin(Kernel kernel, std::once_flag (&flags)[kMaxDevices], size_t bytes,
                       int max_smem) {
@@ -246,7 +260,12 @@ int ensure_smem_optin(Kernel kernel, std::once_flag (&flags)[kMaxDevices], size_
   FK_TRY_CUDA(cudaGetDevice(&device));
   cudaError_t err = cudaSuccess;
   std::call_once(flags[device], [&] {
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncAttributes attrs{};
+    err = cudaFuncGetAttributes(&attrs, kernel);
+    if (err == cudaSuccess) {
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 max_smem - static_cast<int>(attrs.sharedSizeBytes));
+    }
   });
   if (err != cudaSuccess) {
     return fail(FK_W4A16_ERR_CUDA,
@@ -258,9 +277,12 @@ int ensure_smem_optin(Kernel kernel, std::once_flag (&flags)[kMaxDevices], size_
   return FK_W4A16_OK;
 }
 
+template <class E>
+using UnpackModeFor = std::conditional_t<std::is_same<E, BF16>::value, UnpackBF16, UnpackF16>;
+
 template <int G, int M_TILE, class E>
 int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cudaStream_t stream) {
-  auto kernel = w4a16_gemv_stream_kernel<G, M_TILE, E>;
+  auto kernel = w4a16_gemv_stream_kernel<G, M_TILE, UnpackModeFor<E>>;
   static std::once_flag optin_flags[kMaxDevices];
   FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
@@ -271,7 +293,7 @@ int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cuda
 
 template <int G, int M_TILE, class E>
 int launch_split_k(const SplitKParams& params, int row_tiles, int max_smem, cudaStream_t stream) {
-  auto kernel = w4a16_split_k_kernel<G, M_TILE, E>;
+  auto kernel = w4a16_split_k_kernel<G, M_TILE, UnpackModeFor<E>>;
   constexpr int kWarps = 4;
   const int stage_bytes = packet_stride(G) + (M_TILE * G * 2);
   const size_t smem = (((kWarps * params.base.stages * 8) + 127) & ~127) +
@@ -460,7 +482,9 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
   params.num_tiles = num_tiles;
   params.active_warps = plan.active_warps;
   params.stages = plan.stages;
-  params.total_packets = static_cast<long long>(num_tiles) * params.num_groups;
+  params.total_packets = plan.total_packets;
+  params.run_base = plan.total_packets / static_cast<uint32_t>(plan.active_warps);
+  params.run_rem = plan.total_packets % static_cast<uint32_t>(plan.active_warps);
   auto* s = static_cast<cudaStream_t>(stream);
   const int max_smem = info->max_smem_optin;
   return dispatch(group_size, plan.m_tile, dtype, [&](auto g, auto mt, auto e) {
@@ -500,7 +524,7 @@ int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* p
   params.base.num_groups = num_groups;
   params.base.num_tiles = n / kTileCols;
   params.base.stages = 2;
-  params.base.total_packets = static_cast<long long>(params.base.num_tiles) * num_groups;
+  params.base.total_packets = static_cast<uint32_t>(params.base.num_tiles) * num_groups;
   params.partials = partials;
   params.slices = split_k_slices;
   params.groups_per_slice = (num_groups + split_k_slices - 1) / split_k_slices;

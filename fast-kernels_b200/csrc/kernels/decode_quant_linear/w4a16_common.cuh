@@ -148,35 +148,30 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint2 v) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Nibble unpack. One LOP3 per pair: (w & mask) | 0x6400 puts a nibble into the low mantissa bits
-// of an fp16 whose exponent makes the mantissa LSB worth 1, i.e. the half value 1024 + q (nibble
-// in bits 0-3) or 1024 + 16 q (nibble in bits 4-7). The four results pair nibbles (0,4), (1,5),
-// (2,6), (3,7) as (low half, high half).
+// Nibble unpack and multiply-accumulate.
+//
+// One LOP3, (w & mask) | magic, drops a nibble into the low mantissa bits of a 16-bit float whose
+// exponent makes the result an exact small integer plus a constant:
+//     fp16  magic 0x6400, nibble in bits 4-7  ->  1024 + 16 q     ("high" placement)
+//     fp16  magic 0x6400, nibble in bits 0-3  ->  1024 + q        ("low" placement)
+//     bf16  magic 0x4300, nibble in bits 0-3  ->   128 + q        (bf16 has 7 mantissa bits)
+// Each 32-bit result is a pair (low half, high half) = nibbles (i, i+4) of the word. The constant
+// rides along as constant * activation and is removed once per group in fp32, so its size sets the
+// rounding error of the fp32 accumulation: relative to q it is 64 for the high placement (the
+// activation is pre-divided by 16), 128 for bf16-low and 1024 for fp16-low. The two unpack modes
+// below therefore avoid fp16-low:
+//     UnpackF16   all four pairs in high placement            (3 shifts + 4 LOP3 per word)
+//     UnpackBF16  pairs (0,4),(2,6) bf16-low, (1,5),(3,7) fp16-high   (1 shift + 4 LOP3 per word)
+// Products of two 16-bit floats are exact in fp32 and the sm_100 mixed-precision FMA
+// (fma.rn.f32.f16 / .bf16) adds them to an fp32 accumulator without conversion instructions.
 // ---------------------------------------------------------------------------------------------
-template <uint32_t kMask>
-__device__ __forceinline__ uint32_t nibble_pair_to_biased_half2(uint32_t w) {
+template <uint32_t kMask, uint32_t kMagic>
+__device__ __forceinline__ uint32_t mask_or(uint32_t w) {
   uint32_t r;
-  // LUT 0xEA = (a & b) | c
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "n"(kMask), "n"(0x64006400u));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "n"(kMask), "n"(kMagic));  // (a&b)|c
   return r;
 }
 
-struct BiasedNibbles {
-  uint32_t p04, p15, p26, p37;  // half2 bit patterns; p15 and p37 carry 16*q
-};
-__device__ __forceinline__ BiasedNibbles unpack_word(uint32_t w) {
-  BiasedNibbles u;
-  u.p04 = nibble_pair_to_biased_half2<0x000f000fu>(w);
-  u.p15 = nibble_pair_to_biased_half2<0x00f000f0u>(w);
-  const uint32_t w8 = w >> 8;
-  u.p26 = nibble_pair_to_biased_half2<0x000f000fu>(w8);
-  u.p37 = nibble_pair_to_biased_half2<0x00f000f0u>(w8);
-  return u;
-}
-constexpr float kNibbleBias = 1024.0f;  // every unpacked half carries +1024 (times its activation)
-
-// acc_lo += q.lo * a.lo ; acc_hi += q.hi * a.hi with fp16 operands, exact fp32 products and
-// fp32 accumulation (the sm_100 mixed-precision FMA: no conversion instructions).
 __device__ __forceinline__ void fma2_f32_f16(float& acc_lo, float& acc_hi, uint32_t q2,
                                              uint32_t a2) {
   asm("{\n"
@@ -189,6 +184,79 @@ __device__ __forceinline__ void fma2_f32_f16(float& acc_lo, float& acc_hi, uint3
       : "+f"(acc_lo), "+f"(acc_hi)
       : "r"(q2), "r"(a2));
 }
+__device__ __forceinline__ void fma2_f32_bf16(float& acc_lo, float& acc_hi, uint32_t q2,
+                                              uint32_t a2) {
+  asm("{\n"
+      ".reg .b16 ql, qh, al, ah;\n"
+      "mov.b32 {ql, qh}, %2;\n"
+      "mov.b32 {al, ah}, %3;\n"
+      "fma.rn.f32.bf16 %0, ql, al, %0;\n"
+      "fma.rn.f32.bf16 %1, qh, ah, %1;\n"
+      "}\n"
+      : "+f"(acc_lo), "+f"(acc_hi)
+      : "r"(q2), "r"(a2));
+}
+
+struct NibblePairs {
+  uint32_t p04, p15, p26, p37;
+};
+
+// What the staging step must put in shared memory for one word-row of one batch row: four 32-bit
+// pairs (a0,a4) (a1,a5) (a2,a6) (a3,a7) in the formats the mode multiplies with, and the constant
+// term B such that sum_i pair_i * staged_i = sum_k q_k a_k + B.
+struct UnpackF16 {
+  using Elem = F16;
+  static __device__ __forceinline__ NibblePairs unpack(uint32_t w) {
+    NibblePairs u;
+    u.p04 = mask_or<0x00f000f0u, 0x64006400u>(w << 4);
+    u.p15 = mask_or<0x00f000f0u, 0x64006400u>(w);
+    u.p26 = mask_or<0x00f000f0u, 0x64006400u>(w >> 4);
+    u.p37 = mask_or<0x00f000f0u, 0x64006400u>(w >> 8);
+    return u;
+  }
+  static __device__ __forceinline__ void mac(float& lo, float& hi, const NibblePairs& u,
+                                             const uint4& a) {
+    fma2_f32_f16(lo, hi, u.p04, a.x);
+    fma2_f32_f16(lo, hi, u.p15, a.y);
+    fma2_f32_f16(lo, hi, u.p26, a.z);
+    fma2_f32_f16(lo, hi, u.p37, a.w);
+  }
+  // Staged value and bias contribution of activation `f` sitting at an even / odd nibble.
+  static __device__ __forceinline__ unsigned short stage(float f, bool /*odd*/, float& bias) {
+    const __half h = __float2half_rn(f * 0.0625f);
+    bias += 1024.0f * __half2float(h);
+    return __half_as_ushort(h);
+  }
+};
+
+struct UnpackBF16 {
+  using Elem = BF16;
+  static __device__ __forceinline__ NibblePairs unpack(uint32_t w) {
+    NibblePairs u;
+    const uint32_t w8 = w >> 8;
+    u.p04 = mask_or<0x000f000fu, 0x43004300u>(w);
+    u.p15 = mask_or<0x00f000f0u, 0x64006400u>(w);
+    u.p26 = mask_or<0x000f000fu, 0x43004300u>(w8);
+    u.p37 = mask_or<0x00f000f0u, 0x64006400u>(w8);
+    return u;
+  }
+  static __device__ __forceinline__ void mac(float& lo, float& hi, const NibblePairs& u,
+                                             const uint4& a) {
+    fma2_f32_bf16(lo, hi, u.p04, a.x);
+    fma2_f32_f16(lo, hi, u.p15, a.y);
+    fma2_f32_bf16(lo, hi, u.p26, a.z);
+    fma2_f32_f16(lo, hi, u.p37, a.w);
+  }
+  static __device__ __forceinline__ unsigned short stage(float f, bool odd, float& bias) {
+    if (odd) {
+      const __half h = __float2half_rn(f * 0.0625f);
+      bias += 1024.0f * __half2float(h);
+      return __half_as_ushort(h);
+    }
+    bias += 128.0f * f;  // f is a bf16 value: kept as is, exactly
+    return static_cast<unsigned short>(__float_as_uint(f) >> 16);
+  }
+};
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -5,26 +5,28 @@
 // :124-158, :222-402) with ONE persistent launch whose unit of work is a whole packet.
 //
 // Work split. The T*NG packets of a layer are one contiguous byte stream (tile-major,
-// group-minor). The stream is cut into V nearly equal contiguous runs, one per warp, V = warps
-// resident on the GPU (or fewer for small layers). A warp is an independent worker: it owns a
-// private ring of `stages` shared-memory buffers, lane 0 refills a buffer with one bulk
-// asynchronous copy per packet (plus one small copy per batch row for that group's activations)
-// as soon as the warp has consumed it, and all 32 lanes wait on the buffer's mbarrier. There is
-// no CTA-wide barrier anywhere, so warps never stall on each other.
+// group-minor). The stream is cut into V contiguous runs whose lengths differ by at most one
+// packet, one run per warp, V = warps resident on the GPU (or fewer for small layers); warps of a
+// CTA hold neighbouring runs. A warp is an independent worker: it owns a private ring of `stages`
+// shared-memory buffers, lane 0 refills a buffer with one bulk asynchronous copy per packet (plus
+// one small copy per batch row for that group's activations) as soon as the warp has consumed it,
+// and all 32 lanes wait on the buffer's mbarrier. No warp waits for another until its run is done.
 //
 // Inside a packet each lane owns 4 adjacent output columns: one 128-bit shared-memory load per
-// word-row brings 4 columns x 8 nibbles, five integer instructions per word turn the nibbles
-// into fp16 values 1024 + q (or 1024 + 16 q), and eight mixed-precision FMAs per word multiply
-// them with the fp16 activations into fp32 accumulators. The +1024 bias, the per-group scale and
-// the per-group offset are settled once per group in fp32:
-//     y += alpha * (acc - B_g) + beta * S_g,  S_g = sum_k a_k,  B_g = 1024 * sum_k a'_k
-// where a' are the staged activations (odd nibbles pre-divided by 16). Products are exact in
-// fp32, so the only roundings are the fp32 additions.
+// word-row brings 4 columns x 8 nibbles, a handful of integer instructions per word turn the
+// nibbles into 16-bit floats "constant + q", and eight mixed-precision FMAs per word multiply them
+// with the staged activations into fp32 accumulators (see w4a16_common.cuh). The constant, the
+// per-group scale and the per-group offset are settled once per group in fp32:
+//     y += alpha * (acc - B_g) + beta * S_g,    S_g = sum_k a_k,   B_g = sum_k constant_k * a'_k
 //
-// Split tiles. A run may start or end inside a tile. Such a warp writes its 128 partial sums to
-// a scratch slot that only it owns and takes a ticket for the tile; the warp that draws the last
-// ticket adds the slots in run order (a fixed order, so results are reproducible bit for bit)
-// and stores the output. Tiles that one warp covers alone never touch scratch.
+// Finishing a tile (split-K, two levels, fixed summation order => bit-reproducible results):
+//   1. a warp whose run covers all groups of a tile stores that tile's outputs itself;
+//   2. otherwise the warp leaves its partial sums in a shared-memory slot; after one CTA-wide
+//      barrier at the end of the runs, the CTA adds the slots of each tile in warp order and
+//      stores tiles that lie wholly inside the CTA's packet range;
+//   3. a tile shared with a neighbouring CTA is written to a global scratch slot that only this
+//      CTA owns, followed by a ticket; the CTA that draws the tile's last ticket adds the slots in
+//      CTA order and stores the outputs, then resets the ticket for the next call.
 #pragma once
 
 #include "w4a16_common.cuh"
@@ -35,32 +37,35 @@ struct GemvParams {
   const void* act;         // [m, k] 16-bit, row-major
   const uint8_t* packets;  // [num_tiles * num_groups, stride]
   void* out;               // [m, n] 16-bit, row-major
-  float* scratch;          // [row_tiles][active_warps][2][M_TILE * 128] fp32
+  float* scratch;          // [row_tiles][ctas][2][M_TILE * 128] fp32
   int* tickets;            // [row_tiles][num_tiles], zero between calls
   int* status;             // device status word
   int m, n, k;
   int num_groups;          // k / G
   int num_tiles;           // n / 128
-  int active_warps;        // V
+  int active_warps;        // V: number of runs
   int stages;              // ring depth per warp
-  long long total_packets; // num_tiles * num_groups
+  uint32_t total_packets;  // num_tiles * num_groups
+  uint32_t run_base;       // total_packets / V
+  uint32_t run_rem;        // total_packets % V: the first run_rem runs hold run_base + 1 packets
 };
 
-// First packet of worker v's run.
-__device__ __forceinline__ long long run_begin(long long v, long long total, int workers) {
-  return (v * total) / workers;
+__device__ __forceinline__ uint32_t run_begin(uint32_t v, const GemvParams& p) {
+  return (v * p.run_base) + (v < p.run_rem ? v : p.run_rem);
 }
-// Worker whose run holds packet p: the largest v with run_begin(v) <= p.
-__device__ __forceinline__ int run_owner(long long p, long long total, int workers) {
-  return static_cast<int>((((p + 1) * workers) - 1) / total);
+// Run that holds packet `pkt`.
+__device__ __forceinline__ uint32_t run_owner(uint32_t pkt, const GemvParams& p) {
+  const uint32_t split = p.run_rem * (p.run_base + 1);
+  return pkt < split ? pkt / (p.run_base + 1) : p.run_rem + ((pkt - split) / p.run_base);
 }
 
 // Rewrites one group's raw activations (G 16-bit values, row `m` of the stage) in place into the
-// order the unpack produces -- per word-row the four half2 (a0,a4) (a1/16,a5/16) (a2,a6)
-// (a3/16,a7/16) -- converting to fp16, and returns S = sum a and B = 1024 * sum a'.
-template <int G, class E>
+// order and formats the unpack mode multiplies with -- per word-row the four pairs (a0,a4)
+// (a1,a5) (a2,a6) (a3,a7) -- and returns S = sum a and the constant term B.
+template <int G, class Mode>
 __device__ __forceinline__ void stage_activations(uint32_t act_addr, int lane, float& s_out,
                                                   float& b_out) {
+  using E = typename Mode::Elem;
   constexpr int kActiveLanes = G / 4;
   float s = 0.0f;
   float b = 0.0f;
@@ -73,33 +78,31 @@ __device__ __forceinline__ void stage_activations(uint32_t act_addr, int lane, f
     const float f2 = E::to_float(static_cast<unsigned short>(raw.y & 0xffffu));
     const float f3 = E::to_float(static_cast<unsigned short>(raw.y >> 16));
     s = (f0 + f1) + (f2 + f3);
-    const __half h0 = __float2half_rn(f0);
-    const __half h1 = __float2half_rn(f1 * 0.0625f);
-    const __half h2 = __float2half_rn(f2);
-    const __half h3 = __float2half_rn(f3 * 0.0625f);
-    b = (__half2float(h0) + __half2float(h1)) + (__half2float(h2) + __half2float(h3));
-    p01 = static_cast<uint32_t>(__half_as_ushort(h0)) |
-          (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
-    p23 = static_cast<uint32_t>(__half_as_ushort(h2)) |
-          (static_cast<uint32_t>(__half_as_ushort(h3)) << 16);
+    // This lane holds nibbles 4*(lane&1) + {0,1,2,3} of a word-row: positions 1 and 3 are odd.
+    const uint32_t h0 = Mode::stage(f0, false, b);
+    const uint32_t h1 = Mode::stage(f1, true, b);
+    const uint32_t h2 = Mode::stage(f2, false, b);
+    const uint32_t h3 = Mode::stage(f3, true, b);
+    p01 = h0 | (h1 << 16);
+    p23 = h2 | (h3 << 16);
   }
   // Even lanes hold nibbles 0-3 of a word-row, odd lanes nibbles 4-7. Swap one register with
-  // the neighbour so each lane can write two finished (low nibble, high nibble) pairs.
-  const bool odd = (lane & 1) != 0;
-  const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd ? p01 : p23, 1);
+  // the neighbour so each lane can write two finished (nibble i, nibble i+4) pairs.
+  const bool odd_lane = (lane & 1) != 0;
+  const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd_lane ? p01 : p23, 1);
   if (lane < kActiveLanes) {
     uint2 staged;
-    if (!odd) {
+    if (!odd_lane) {
       staged.x = __byte_perm(p01, recv, 0x5410);  // (a0, a4)
-      staged.y = __byte_perm(p01, recv, 0x7632);  // (a1', a5')
+      staged.y = __byte_perm(p01, recv, 0x7632);  // (a1, a5)
     } else {
       staged.x = __byte_perm(recv, p23, 0x5410);  // (a2, a6)
-      staged.y = __byte_perm(recv, p23, 0x7632);  // (a3', a7')
+      staged.y = __byte_perm(recv, p23, 0x7632);  // (a3, a7)
     }
     sts64(act_addr + lane * 8, staged);
   }
   s_out = warp_sum(s);
-  b_out = kNibbleBias * warp_sum(b);
+  b_out = warp_sum(b);
 }
 
 template <class E>
@@ -114,13 +117,15 @@ __device__ __forceinline__ void store_tile_row(void* out, long long elem_offset,
   *dst = packed;
 }
 
-// One warp's pass over packets [p_begin, p_end) of one tile-major packet stream, accumulating
-// `y` per tile and handing every finished tile run to `on_tile_done(tile, first_pkt, last_pkt)`.
-template <int G, int M_TILE, class E, class TileDone>
+// One warp's pass over packets [p_begin, p_end) of the tile-major packet stream, accumulating
+// `y` per tile and handing every finished tile run to on_tile_done(tile, first_pkt, end_pkt).
+// Returns false if a copy never arrived (the status word is set).
+template <int G, int M_TILE, class Mode, class TileDone>
 __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t ring_addr,
                                                    uint32_t bar_addr, int row0, int m_act,
-                                                   long long p_begin, long long p_end, int lane,
+                                                   uint32_t p_begin, uint32_t p_end, int lane,
                                                    float (&y)[M_TILE][4], TileDone&& on_tile_done) {
+  using E = typename Mode::Elem;
   constexpr int kStride = packet_stride(G);
   constexpr int kQBytes = packet_q_bytes(G);
   constexpr int kActBytes = G * 2;
@@ -128,43 +133,50 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
   constexpr int kWordRows = G / 8;
 
   const int stages = p.stages;
-  const long long count = p_end - p_begin;
+  const uint32_t count = p_end - p_begin;
   const uint64_t weight_policy = l2_evict_first_policy();
   const uint64_t act_policy = l2_evict_last_policy();
   const auto* act_bytes = static_cast<const uint8_t*>(p.act);
+  const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
 
-  auto issue = [&](long long j) {
-    const int slot = static_cast<int>(j % stages);
-    const long long pkt = p_begin + j;
-    const int group = static_cast<int>(pkt % p.num_groups);
-    const uint32_t bar = bar_addr + (slot * 8);
-    const uint32_t dst = ring_addr + (slot * kStageBytes);
+  uint32_t tile = p_begin / num_groups;
+  const uint32_t first_group = p_begin - (tile * num_groups);
+
+  // Issue side (lane 0 only acts; the counters are cheap enough to keep in every lane).
+  uint32_t issue_idx = 0;
+  uint32_t issue_group = first_group;
+  int issue_slot = 0;
+  auto issue_next = [&]() {
+    const uint32_t bar = bar_addr + (issue_slot * 8);
+    const uint32_t dst = ring_addr + (issue_slot * kStageBytes);
     mbar_expect_tx(bar, static_cast<uint32_t>(kStride + (m_act * kActBytes)));
-    bulk_copy_g2s(dst, p.packets + (pkt * kStride), kStride, bar, weight_policy);
+    bulk_copy_g2s(dst, p.packets + (static_cast<size_t>(p_begin + issue_idx) * kStride), kStride,
+                  bar, weight_policy);
     for (int m = 0; m < m_act; ++m) {
-      const long long elem = (static_cast<long long>(row0 + m) * p.k) +
-                             (static_cast<long long>(group) * G);
+      const size_t elem = (static_cast<size_t>(row0 + m) * p.k) + (issue_group * G);
       bulk_copy_g2s(dst + kStride + (m * kActBytes), act_bytes + (elem * 2), kActBytes, bar,
                     act_policy);
     }
+    ++issue_idx;
+    issue_group = (issue_group + 1 == num_groups) ? 0 : issue_group + 1;
+    issue_slot = (issue_slot + 1 == stages) ? 0 : issue_slot + 1;
   };
 
   if (lane == 0) {
-    const long long prefill = count < stages ? count : stages;
-    for (long long j = 0; j < prefill; ++j) {
-      issue(j);
+    const uint32_t prefill = count < static_cast<uint32_t>(stages) ? count : stages;
+    for (uint32_t j = 0; j < prefill; ++j) {
+      issue_next();
     }
   }
 
-  long long pkt = p_begin;
-  int tile = static_cast<int>(p_begin / p.num_groups);
-  long long tile_end = static_cast<long long>(tile + 1) * p.num_groups;
-  long long tile_first = p_begin;
+  uint32_t pkt = p_begin;
+  uint32_t tile_end = (tile + 1) * num_groups;
+  uint32_t tile_first = p_begin;
   int slot = 0;
   uint32_t parity = 0;
   bool ok = true;
 
-  for (long long j = 0; j < count; ++j, ++pkt) {
+  for (uint32_t j = 0; j < count; ++j, ++pkt) {
     if (pkt == tile_end) {
       on_tile_done(tile, tile_first, pkt);
 #pragma unroll
@@ -176,7 +188,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       }
       ++tile;
       tile_first = pkt;
-      tile_end += p.num_groups;
+      tile_end += num_groups;
     }
 
     const uint32_t bar = bar_addr + (slot * 8);
@@ -193,7 +205,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       float bias = 0.0f;
       group_sum[m] = 0.0f;
       if (m < m_act) {
-        stage_activations<G, E>(stage + kStride + (m * kActBytes), lane, group_sum[m], bias);
+        stage_activations<G, Mode>(stage + kStride + (m * kActBytes), lane, group_sum[m], bias);
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -206,29 +218,17 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 #pragma unroll 4
     for (int r = 0; r < kWordRows; ++r) {
       const uint4 wq = lds128(stage + (r * (kTileCols * 4)) + (lane * 16));
-      BiasedNibbles u[4];
-      u[0] = unpack_word(wq.x);
-      u[1] = unpack_word(wq.y);
-      u[2] = unpack_word(wq.z);
-      u[3] = unpack_word(wq.w);
+      NibblePairs u[4];
+      u[0] = Mode::unpack(wq.x);
+      u[1] = Mode::unpack(wq.y);
+      u[2] = Mode::unpack(wq.z);
+      u[3] = Mode::unpack(wq.w);
 #pragma unroll
       for (int m = 0; m < M_TILE; ++m) {
         const uint4 a = lds128(stage + kStride + (m * kActBytes) + (r * 16));
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          fma2_f32_f16(acc[m][c][0], acc[m][c][1], u[c].p04, a.x);
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          fma2_f32_f16(acc[m][c][0], acc[m][c][1], u[c].p15, a.y);
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          fma2_f32_f16(acc[m][c][0], acc[m][c][1], u[c].p26, a.z);
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          fma2_f32_f16(acc[m][c][0], acc[m][c][1], u[c].p37, a.w);
+          Mode::mac(acc[m][c][0], acc[m][c][1], u[c], a);
         }
       }
     }
@@ -259,9 +259,9 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 
     // The whole warp is done reading this buffer: hand it back to the copy engine.
     __syncwarp();
-    if (lane == 0 && (j + stages) < count) {
+    if (lane == 0 && issue_idx < count) {
       proxy_fence_async();
-      issue(j + stages);
+      issue_next();
     }
     if (++slot == stages) {
       slot = 0;
@@ -276,13 +276,12 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 
   // A copy never landed. Record it, then give the copies still in flight a bounded chance to
   // finish before this warp's shared memory can be handed to another CTA.
+  issue_idx = __shfl_sync(0xffffffffu, issue_idx, 0);
   if (lane == 0) {
     atomicExch(p.status, static_cast<int>(kStatusCopyWaitTimeout));
   }
-  const long long issued_end = (pkt - p_begin) + stages < count ? (pkt - p_begin) + stages : count;
-  for (long long j = pkt - p_begin; j < issued_end; ++j) {
-    const uint32_t bar = bar_addr + (slot * 8);
-    (void)mbar_wait_bounded(bar, parity);
+  for (uint32_t j = pkt - p_begin; j < issue_idx; ++j) {
+    (void)mbar_wait_bounded(bar_addr + (slot * 8), parity);
     if (++slot == stages) {
       slot = 0;
       parity ^= 1u;
@@ -291,133 +290,229 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
   return false;
 }
 
-template <int G, int M_TILE, class E>
-__global__ void __launch_bounds__(512, 1) w4a16_gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+// Shared-memory plan of the stream kernel, used by host and device alike.
+struct StreamSmem {
+  uint32_t barriers;  // offset of warp 0's barriers
+  uint32_t slots;     // offset of the per-warp partial-sum slots
+  uint32_t rings;     // offset of warp 0's ring
+  uint32_t total;
+};
+__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int stages, int stage_bytes,
+                                                       int m_tile) {
+  StreamSmem plan;
+  plan.barriers = 0;
+  plan.slots = ((static_cast<uint32_t>(warps) * stages * 8) + 127u) & ~127u;
+  plan.rings = plan.slots + (static_cast<uint32_t>(warps) * 2 * m_tile * kTileCols * 4);
+  plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * stage_bytes);
+  return plan;
+}
+
+template <int G, int M_TILE, class Mode>
+__global__ void __launch_bounds__(512, 1)
+    w4a16_gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+  using E = typename Mode::Elem;
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kStageBytes = packet_stride(G) + (M_TILE * G * 2);
+  constexpr int kSlotFloats = M_TILE * kTileCols;
 
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int warp = static_cast<int>(threadIdx.x) >> 5;
   const int warps_per_cta = static_cast<int>(blockDim.x) >> 5;
-  const int v = (static_cast<int>(blockIdx.x) * warps_per_cta) + warp;
-  if (v >= p.active_warps) {
-    return;  // whole warps leave; nothing below uses a CTA-wide barrier
-  }
+  const uint32_t cta = blockIdx.x;
+  const uint32_t v = (cta * warps_per_cta) + warp;
+  const uint32_t workers = static_cast<uint32_t>(p.active_warps);
+  const bool active = v < workers;
   const int row_tile = static_cast<int>(blockIdx.y);
   const int row0 = row_tile * M_TILE;
   const int m_act = (p.m - row0) < M_TILE ? (p.m - row0) : M_TILE;
+  const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
 
-  // Shared memory: all warps' barriers first (8 bytes each), then the rings.
   const int stages = p.stages;
+  const StreamSmem plan = stream_smem_plan(warps_per_cta, stages, kStageBytes, M_TILE);
   const uint32_t smem_base = smem_addr(smem);
-  const uint32_t bar_addr = smem_base + (warp * stages * 8);
-  const uint32_t ring_base = smem_base + (((warps_per_cta * stages * 8) + 127) & ~127);
-  const uint32_t ring_addr = ring_base + (warp * stages * kStageBytes);
-  if (lane == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_addr + (s * 8), 1);
+  const uint32_t bar_addr = smem_base + plan.barriers + (warp * stages * 8);
+  const uint32_t ring_addr = smem_base + plan.rings + (warp * stages * kStageBytes);
+  float* slots = reinterpret_cast<float*>(smem + plan.slots);  // [warp][2][kSlotFloats]
+
+  const uint32_t p_begin = active ? run_begin(v, p) : 0;
+  const uint32_t p_end = active ? run_begin(v + 1, p) : 0;
+  const uint32_t first_tile = p_begin / num_groups;
+
+  if (active) {
+    if (lane == 0) {
+      for (int s = 0; s < stages; ++s) {
+        mbar_init(bar_addr + (s * 8), 1);
+      }
+      mbar_init_fence();
     }
-    mbar_init_fence();
+    __syncwarp();
+
+    float y[M_TILE][4];
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        y[m][c] = 0.0f;
+      }
+    }
+    auto on_tile_done = [&](uint32_t tile, uint32_t first_pkt, uint32_t end_pkt) {
+      if ((end_pkt - first_pkt) == num_groups) {
+        const long long out_col = static_cast<long long>(tile) * kTileCols;
+#pragma unroll
+        for (int m = 0; m < M_TILE; ++m) {
+          if (m < m_act) {
+            store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane,
+                              y[m]);
+          }
+        }
+        return;
+      }
+      float* slot = slots + (((warp * 2) + (tile == first_tile ? 0 : 1)) * kSlotFloats);
+#pragma unroll
+      for (int m = 0; m < M_TILE; ++m) {
+        reinterpret_cast<float4*>(slot + (m * kTileCols))[lane] =
+            make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
+      }
+    };
+    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, row0, m_act, p_begin, p_end,
+                                              lane, y, on_tile_done);
   }
-  __syncwarp();
+  __syncthreads();
 
-  const long long total = p.total_packets;
-  const int workers = p.active_warps;
-  const long long p_begin = run_begin(v, total, workers);
-  const long long p_end = run_begin(v + 1, total, workers);
-  const int first_tile = static_cast<int>(p_begin / p.num_groups);
-
-  float* scratch = p.scratch + (static_cast<size_t>(row_tile) * workers * 2 * (M_TILE * kTileCols));
+  // ---- CTA-level finish ---------------------------------------------------------------------
+  const uint32_t cta_first_run = cta * warps_per_cta;
+  uint32_t cta_end_run = cta_first_run + warps_per_cta;
+  cta_end_run = cta_end_run < workers ? cta_end_run : workers;
+  const uint32_t cta_begin = run_begin(cta_first_run, p);
+  const uint32_t cta_end = run_begin(cta_end_run, p);
+  const uint32_t cta_first_tile = cta_begin / num_groups;
+  const uint32_t cta_last_tile = (cta_end - 1) / num_groups;
+  float* scratch = p.scratch + (static_cast<size_t>(row_tile) * gridDim.x * 2 * kSlotFloats);
   int* tickets = p.tickets + (static_cast<size_t>(row_tile) * p.num_tiles);
 
-  float y[M_TILE][4];
-#pragma unroll
-  for (int m = 0; m < M_TILE; ++m) {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      y[m][c] = 0.0f;
+  for (uint32_t tile = cta_first_tile + warp; tile <= cta_last_tile; tile += warps_per_cta) {
+    const uint32_t tile_lo = tile * num_groups;
+    const uint32_t tile_hi = tile_lo + num_groups;
+    const uint32_t lo = tile_lo > cta_begin ? tile_lo : cta_begin;
+    const uint32_t hi = tile_hi < cta_end ? tile_hi : cta_end;
+    const uint32_t run_a = run_owner(lo, p);
+    const uint32_t run_b = run_owner(hi - 1, p);
+    if (run_a == run_b && run_begin(run_a, p) <= tile_lo && run_begin(run_a + 1, p) >= tile_hi) {
+      continue;  // one warp saw the whole tile and stored it
     }
-  }
 
-  auto on_tile_done = [&](int tile, long long first_pkt, long long end_pkt) {
+    float sum[M_TILE][4];
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        sum[m][c] = 0.0f;
+      }
+    }
+    for (uint32_t u = run_a; u <= run_b; ++u) {
+      // the tile is run u's first tile exactly when the run starts inside it
+      const int which = run_begin(u, p) >= tile_lo ? 0 : 1;
+      const float* slot = slots + ((((u - cta_first_run) * 2) + which) * kSlotFloats);
+#pragma unroll
+      for (int m = 0; m < M_TILE; ++m) {
+        const float4 part = reinterpret_cast<const float4*>(slot + (m * kTileCols))[lane];
+        sum[m][0] += part.x;
+        sum[m][1] += part.y;
+        sum[m][2] += part.z;
+        sum[m][3] += part.w;
+      }
+    }
+
     const long long out_col = static_cast<long long>(tile) * kTileCols;
-    if ((end_pkt - first_pkt) == p.num_groups) {
-      // This warp saw every group of the tile: the sums are final.
+    if (cta_begin <= tile_lo && cta_end >= tile_hi) {
 #pragma unroll
       for (int m = 0; m < M_TILE; ++m) {
         if (m < m_act) {
-          store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane, y[m]);
+          store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane,
+                            sum[m]);
         }
       }
-      return;
+      continue;
     }
 
-    // Partial tile: publish, take a ticket, and let the last arrival finish the tile.
-    float* my_slot = scratch + ((static_cast<size_t>(v) * 2 + (tile == first_tile ? 0 : 1)) *
-                                (M_TILE * kTileCols));
+    // The tile continues in a neighbouring CTA: publish, take a ticket, last one finishes.
+    float* mine = scratch + (((static_cast<size_t>(cta) * 2) + (cta_begin >= tile_lo ? 0 : 1)) *
+                             kSlotFloats);
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
-      reinterpret_cast<float4*>(my_slot + (m * kTileCols))[lane] =
-          make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
+      __stcg(reinterpret_cast<float4*>(mine + (m * kTileCols)) + lane,
+             make_float4(sum[m][0], sum[m][1], sum[m][2], sum[m][3]));
     }
     __threadfence();
     __syncwarp();
-
-    const long long tile_first_pkt = static_cast<long long>(tile) * p.num_groups;
-    const int v_first = run_owner(tile_first_pkt, total, workers);
-    const int v_last = run_owner(tile_first_pkt + p.num_groups - 1, total, workers);
+    const uint32_t cta_a = run_owner(tile_lo, p) / warps_per_cta;
+    const uint32_t cta_b = run_owner(tile_hi - 1, p) / warps_per_cta;
     int ticket = 0;
     if (lane == 0) {
       ticket = atomicAdd(&tickets[tile], 1);
     }
     ticket = __shfl_sync(0xffffffffu, ticket, 0);
-    if (ticket != (v_last - v_first)) {
-      return;
+    if (ticket != static_cast<int>(cta_b - cta_a)) {
+      continue;
     }
     __threadfence();
 
-    float total_y[M_TILE][4];
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        total_y[m][c] = 0.0f;
+        sum[m][c] = 0.0f;
       }
     }
-    for (int u = v_first; u <= v_last; ++u) {
-      const int u_first_tile = static_cast<int>(run_begin(u, total, workers) / p.num_groups);
-      const float* slot = scratch + ((static_cast<size_t>(u) * 2 + (tile == u_first_tile ? 0 : 1)) *
-                                     (M_TILE * kTileCols));
+    constexpr int kBatch = 4;  // independent loads in flight per step; order of addition is fixed
+    for (uint32_t base = cta_a; base <= cta_b; base += kBatch) {
+      float4 part[kBatch][M_TILE];
 #pragma unroll
-      for (int m = 0; m < M_TILE; ++m) {
-        const float4 part = __ldcg(reinterpret_cast<const float4*>(slot + (m * kTileCols)) + lane);
-        total_y[m][0] += part.x;
-        total_y[m][1] += part.y;
-        total_y[m][2] += part.z;
-        total_y[m][3] += part.w;
+      for (int i = 0; i < kBatch; ++i) {
+        const uint32_t cc = base + i;
+        if (cc <= cta_b) {
+          const int which = run_begin(cc * warps_per_cta, p) >= tile_lo ? 0 : 1;
+          const float* theirs =
+              scratch + (((static_cast<size_t>(cc) * 2) + which) * kSlotFloats);
+#pragma unroll
+          for (int m = 0; m < M_TILE; ++m) {
+            part[i][m] = __ldcg(reinterpret_cast<const float4*>(theirs + (m * kTileCols)) + lane);
+          }
+        } else {
+#pragma unroll
+          for (int m = 0; m < M_TILE; ++m) {
+            part[i][m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+#pragma unroll
+        for (int m = 0; m < M_TILE; ++m) {
+          sum[m][0] += part[i][m].x;
+          sum[m][1] += part[i][m].y;
+          sum[m][2] += part[i][m].z;
+          sum[m][3] += part[i][m].w;
+        }
       }
     }
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
       if (m < m_act) {
-        store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane,
-                          total_y[m]);
+        store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane, sum[m]);
       }
     }
     if (lane == 0) {
       tickets[tile] = 0;  // ready for the next call on this workspace
     }
-  };
-
-  (void)consume_packet_run<G, M_TILE, E>(p, ring_addr, bar_addr, row0, m_act, p_begin, p_end, lane,
-                                         y, on_tile_done);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
 // Caller-visible split-K (the reference's arc_w4a16_forward_split_k + reduce, arc_w4a16.cu
 // :341-402): slice s covers groups [s*gps, min((s+1)*gps, NG)), gps = ceil(NG / S), and writes
-// fp32 partials[s, m, n]. One CTA per (tile, slice); its warps take the slice's packets
-// round-robin and add their sums through shared memory in warp order.
+// fp32 partials[s, m, n]. One CTA per (tile, slice); its warps take contiguous shares of the
+// slice's packets and add their sums through shared memory in warp order.
 // ---------------------------------------------------------------------------------------------
 struct SplitKParams {
   GemvParams base;
@@ -426,8 +521,9 @@ struct SplitKParams {
   int groups_per_slice;
 };
 
-template <int G, int M_TILE, class E>
-__global__ void __launch_bounds__(128, 1) w4a16_split_k_kernel(const __grid_constant__ SplitKParams sp) {
+template <int G, int M_TILE, class Mode>
+__global__ void __launch_bounds__(128, 1)
+    w4a16_split_k_kernel(const __grid_constant__ SplitKParams sp) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kStageBytes = packet_stride(G) + (M_TILE * G * 2);
   constexpr int kWarps = 4;
@@ -445,7 +541,6 @@ __global__ void __launch_bounds__(128, 1) w4a16_split_k_kernel(const __grid_cons
   int g_end = g_begin + sp.groups_per_slice;
   g_end = g_end < p.num_groups ? g_end : p.num_groups;
   const int slice_groups = g_end > g_begin ? g_end - g_begin : 0;
-  // Warp w takes a contiguous share of the slice.
   const int w_begin = g_begin + ((slice_groups * warp) / kWarps);
   const int w_end = g_begin + ((slice_groups * (warp + 1)) / kWarps);
 
@@ -471,10 +566,10 @@ __global__ void __launch_bounds__(128, 1) w4a16_split_k_kernel(const __grid_cons
     }
   }
   if (w_end > w_begin) {
-    const long long base_pkt = static_cast<long long>(tile) * p.num_groups;
-    auto keep = [](int, long long, long long) {};
-    (void)consume_packet_run<G, M_TILE, E>(p, ring_addr, bar_addr, row0, m_act, base_pkt + w_begin,
-                                           base_pkt + w_end, lane, y, keep);
+    const uint32_t base_pkt = static_cast<uint32_t>(tile) * p.num_groups;
+    auto keep = [](uint32_t, uint32_t, uint32_t) {};
+    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, row0, m_act,
+                                              base_pkt + w_begin, base_pkt + w_end, lane, y, keep);
   }
 #pragma unroll
   for (int m = 0; m < M_TILE; ++m) {
