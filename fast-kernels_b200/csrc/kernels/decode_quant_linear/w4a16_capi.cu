@@ -26,6 +26,10 @@ namespace {
 
 __device__ int g_device_status = 0;
 
+// Scratch of fk_w4a16_gemv_static. In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels are given the address that call returns.
+static __device__ __align__(256) unsigned char g_static_scratch[FK_W4A16_STATIC_SCRATCH_BYTES];
+
 thread_local std::string t_last_error;
 
 int fail(int code, const std::string& message) {
@@ -491,6 +495,53 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
     return launch_stream<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
                                                                                  max_smem, s);
   });
+}
+
+int fk_w4a16_gemv_static(const void* activations, const void* packets, void* output, int batch,
+                         int n, int k, int group_size, int packet_stride_bytes, int dtype,
+                         void* stream) {
+  FK_TRY(check_dimensions(batch, n, k, group_size));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+
+  // Once per device, with that device current: the device address of the static array.
+  static void* scratch_address[kMaxDevices] = {};
+  static std::once_flag scratch_once[kMaxDevices];
+  int device = 0;
+  FK_TRY_CUDA(cudaGetDevice(&device));
+  cudaError_t lookup = cudaSuccess;
+  std::call_once(scratch_once[device], [&] {
+    void* address = nullptr;
+    lookup = cudaGetSymbolAddress(&address, g_static_scratch);
+    if (lookup == cudaSuccess) {
+      scratch_address[device] = address;
+    }
+  });
+  if (lookup != cudaSuccess || scratch_address[device] == nullptr) {
+    return fail(FK_W4A16_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch) failed: ") +
+                                       cudaGetErrorString(lookup));
+  }
+
+  const Plan plan =
+      make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  const size_t need = workspace_bytes_for(plan);
+  if (need > static_cast<size_t>(FK_W4A16_STATIC_SCRATCH_BYTES)) {
+    std::ostringstream oss;
+    oss << "this problem needs " << need << " bytes of scratch but the static array holds "
+        << FK_W4A16_STATIC_SCRATCH_BYTES << "; use fk_w4a16_gemv with a caller-owned workspace";
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+  }
+  // The tickets this call will use must start at zero whatever an earlier call left behind.
+  const size_t ticket_bytes =
+      static_cast<size_t>(plan.row_tiles) * static_cast<size_t>(n / kTileCols) * sizeof(int);
+  if (ticket_bytes > kTicketBytes) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * batch exceeds the ticket area of a workspace");
+  }
+  FK_TRY_CUDA(cudaMemsetAsync(scratch_address[device], 0, ticket_bytes,
+                              static_cast<cudaStream_t>(stream)));
+  return fk_w4a16_gemv(activations, packets, output, scratch_address[device],
+                       FK_W4A16_STATIC_SCRATCH_BYTES, batch, n, k, group_size, packet_stride_bytes,
+                       dtype, stream);
 }
 
 int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,

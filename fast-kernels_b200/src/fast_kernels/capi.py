@@ -46,6 +46,10 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
          _c_int, _c_int, _c_void_p],
     ),
+    "fk_w4a16_gemv_static": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
     "fk_w4a16_gemv_split_k": (
         _c_int,
         [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,

@@ -83,6 +83,28 @@ FK_W4A16_API int fk_w4a16_gemv(const void* activations, const void* packets, voi
                   size_t workspace_bytes, int batch, int n, int k, int group_size,
                   int packet_stride_bytes, int dtype, void* stream);
 
+/* fk_w4a16_gemv for callers that cannot hand over scratch memory. This entry point has no
+ * counterpart in the reference. It is meant for hosts where device allocation is off the table
+ * once start-up is over: a serving process that has already handed all free device memory to its
+ * own pools (so a later cudaMalloc fails or has to be carved out of someone else's budget), and
+ * decode loops that cannot afford the device-wide stall an allocation implies. The scratch is a
+ * fixed array of FK_W4A16_STATIC_SCRATCH_BYTES inside the library's device image; every GPU that
+ * loads the library holds that much until the process exits, whether or not this function is used.
+ *
+ * Same arguments and results as fk_w4a16_gemv minus the workspace. Problems whose scratch need
+ * exceeds the array (in practice batch > 4, or devices with far more SMs than a B200) are refused
+ * with FK_W4A16_ERR_INVALID_ARGUMENT and a message that states both sizes. The function calls no
+ * allocator of any kind. The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call outside stream capture.
+ * All calls on a device share the one array: the part a call depends on being zero is cleared on
+ * `stream` before each launch, but two calls that overlap on the GPU (different streams, no
+ * ordering between them) would race on it -- serialise them or use fk_w4a16_gemv with separate
+ * workspaces. */
+#define FK_W4A16_STATIC_SCRATCH_BYTES (1024 * 1024)
+FK_W4A16_API int fk_w4a16_gemv_static(const void* activations, const void* packets, void* output, int batch,
+                         int n, int k, int group_size, int packet_stride_bytes, int dtype,
+                         void* stream);
+
 /* Caller-visible split-K: partials[split_k_slices, batch, n] (fp32), slice s covering groups
  * [s * ceil(NG/S), ...). Reference: arc_w4a16_forward_split_k, arc_w4a16.cu:709-737. */
 FK_W4A16_API int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,
