@@ -196,7 +196,7 @@ struct Plan {
   int m_tile = 1;
   int row_tiles = 1;
   int warps = 1;
-  int stages = 0;  // < 2 means the configuration does not fit in shared memory
+  int stages = 0;  // 0 means the configuration does not fit in shared memory
   int grid_x = 1;
   int active_warps = 1;
   uint32_t total_packets = 0;
@@ -213,13 +213,14 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
-  const int stage_bytes = packet_stride(group_size) + (plan.m_tile * group_size * 2);
+  const int stage_bytes = packet_stride(group_size);
 
   // Default: as many warps as fit with a two-deep ring each (more warps hide more latency than
   // deeper rings do), at most 16.
   int warps = cfg.warps;
   if (warps <= 0) {
-    const int per_warp = (2 * stage_bytes) + (2 * plan.m_tile * kTileCols * 4) + 16;
+    const int per_warp = (2 * stage_bytes) + (2 * plan.m_tile * kTileCols * 4) +
+                         (plan.m_tile * group_size * 2) + 16;
     warps = (max_smem - 256) / per_warp;
     warps = warps > kMaxWarps ? kMaxWarps : (warps < 1 ? 1 : warps);
   }
@@ -235,17 +236,24 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.grid_x = static_cast<int>((workers + warps - 1) / warps);
   plan.active_warps = static_cast<int>(workers);
 
-  const int wanted = cfg.stages > 0 ? cfg.stages : 4;
+  // A ring deeper than the longest run is wasted shared memory -- and a small footprint is what
+  // lets the next launch's CTAs move in early under programmatic dependent launch.
+  const long long longest_run = (total_packets + workers - 1) / workers;
+  int wanted = cfg.stages > 0 ? cfg.stages : 4;
+  wanted = wanted > kMaxStages ? kMaxStages : wanted;
+  if (wanted > longest_run) {
+    wanted = static_cast<int>(longest_run);
+  }
   int stages = 0;
-  for (int candidate = kMaxStages < wanted ? kMaxStages : wanted; candidate >= 2; --candidate) {
-    if (stream_smem_plan(warps, candidate, stage_bytes, plan.m_tile).total <=
+  for (int candidate = wanted; candidate >= (longest_run < 2 ? 1 : 2); --candidate) {
+    if (stream_smem_plan(warps, candidate, group_size, plan.m_tile).total <=
         static_cast<uint32_t>(max_smem)) {
       stages = candidate;
       break;
     }
   }
   plan.stages = stages;
-  plan.smem_bytes = stream_smem_plan(warps, stages < 2 ? 2 : stages, stage_bytes, plan.m_tile).total;
+  plan.smem_bytes = stream_smem_plan(warps, stages < 1 ? 1 : stages, group_size, plan.m_tile).total;
   plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
                        (plan.m_tile * kTileCols) * sizeof(float);
   return plan;
@@ -281,6 +289,33 @@ int ensure_smem_optin(Kernel kernel, std::once_flag (&flags)[kMaxDevices], size_
   return FK_W4A16_OK;
 }
 
+// Launches with programmatic stream serialisation: the kernel may begin (and prefetch weights)
+// while its predecessor in the stream drains; it orders itself with griddepcontrol.wait before it
+// reads activations or writes anything. FK_W4A16_PDL=0 turns the attribute off.
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char* value = std::getenv("FK_W4A16_PDL");
+    return value == nullptr || std::atoi(value) != 0;
+  }();
+  return enabled;
+}
+
+template <class Params>
+cudaError_t launch_kernel(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, const Params& params) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, params);
+}
+
 template <class E>
 using UnpackModeFor = std::conditional_t<std::is_same<E, BF16>::value, UnpackBF16, UnpackF16>;
 
@@ -290,8 +325,7 @@ int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cuda
   static std::once_flag optin_flags[kMaxDevices];
   FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
-  kernel<<<grid, plan.warps * 32, plan.smem_bytes, stream>>>(params);
-  FK_TRY_CUDA(cudaGetLastError());
+  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params));
   return FK_W4A16_OK;
 }
 
@@ -299,15 +333,14 @@ template <int G, int M_TILE, class E>
 int launch_split_k(const SplitKParams& params, int row_tiles, int max_smem, cudaStream_t stream) {
   auto kernel = w4a16_split_k_kernel<G, M_TILE, UnpackModeFor<E>>;
   constexpr int kWarps = 4;
-  const int stage_bytes = packet_stride(G) + (M_TILE * G * 2);
+  const int stage_bytes = packet_stride(G);
   const size_t smem = (((kWarps * params.base.stages * 8) + 127) & ~127) +
                       (static_cast<size_t>(kWarps) * params.base.stages * stage_bytes);
   static std::once_flag optin_flags[kMaxDevices];
   FK_TRY(ensure_smem_optin(kernel, optin_flags, smem, max_smem));
   const dim3 grid(static_cast<unsigned>(params.base.num_tiles), static_cast<unsigned>(row_tiles),
                   static_cast<unsigned>(params.slices));
-  kernel<<<grid, kWarps * 32, smem, stream>>>(params);
-  FK_TRY_CUDA(cudaGetLastError());
+  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(kWarps * 32), smem, stream, params));
   return FK_W4A16_OK;
 }
 
@@ -362,8 +395,8 @@ int fk_w4a16_packet_stride_bytes(int group_size) {
 }
 
 int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas) {
-  if (warps_per_cta < 0 || warps_per_cta > kMaxWarps || stages < 0 || stages == 1 ||
-      stages > kMaxStages || ctas < 0) {
+  if (warps_per_cta < 0 || warps_per_cta > kMaxWarps || stages < 0 || stages > kMaxStages ||
+      ctas < 0) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config out of range");
   }
   (void)launch_config();  // settle the environment defaults first so they cannot override this
@@ -458,7 +491,7 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
   FK_TRY(device_info(&info));
   const Plan plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  if (plan.stages < 2) {
+  if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
   if (workspace_bytes < workspace_bytes_for(plan)) {
@@ -728,6 +761,15 @@ int fk_w4a16_cublaslt_matmul(const void* activations, const void* weight, void* 
   cleanup();
   return rc;
 }
+
+#ifdef FK_W4A16_TRACE
+// Tuning builds only: copies the timeline marks (148 x 16 x 8 timestamps) to a host buffer.
+__attribute__((visibility("default"))) int fk_w4a16_trace_read(unsigned long long* host) {
+  FK_TRY_CUDA(cudaDeviceSynchronize());
+  FK_TRY_CUDA(cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * 148 * 16 * kTraceSlots));
+  return FK_W4A16_OK;
+}
+#endif
 
 int fk_w4a16_device_status(int* status) {
   if (status == nullptr) {

@@ -70,7 +70,15 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t arrivals) {
 // Makes freshly initialised barriers visible to the asynchronous (TMA) proxy.
 __device__ __forceinline__ void mbar_init_fence() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Programmatic dependent launch (griddepcontrol). Both are no-ops when the kernel was launched
+// without the programmatic-serialisation attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait_for_prerequisites() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // Orders this thread's earlier generic-proxy shared-memory accesses before later

@@ -33,6 +33,27 @@
 
 namespace fk_w4a16 {
 
+// Optional timeline instrumentation for tuning builds (-DFK_W4A16_TRACE): lane 0 of every warp
+// records the global timer at a few milestones. Compiled out of the shipped library.
+#ifdef FK_W4A16_TRACE
+constexpr int kTraceSlots = 8;
+__device__ unsigned long long g_trace[148 * 16 * kTraceSlots];  // this header is one TU's
+__device__ __forceinline__ void trace_mark(int slot) {
+  if ((threadIdx.x & 31) == 0 && blockIdx.x < 148 && (threadIdx.x >> 5) < 16) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_trace[((blockIdx.x * 16) + (threadIdx.x >> 5)) * kTraceSlots + slot] = t;
+    if (slot == 0) {
+      unsigned int smid;
+      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+      g_trace[((blockIdx.x * 16) + (threadIdx.x >> 5)) * kTraceSlots + 6] = smid;
+    }
+  }
+}
+#else
+__device__ __forceinline__ void trace_mark(int) {}
+#endif
+
 struct GemvParams {
   const void* act;         // [m, k] 16-bit, row-major
   const uint8_t* packets;  // [num_tiles * num_groups, stride]
@@ -59,12 +80,13 @@ __device__ __forceinline__ uint32_t run_owner(uint32_t pkt, const GemvParams& p)
   return pkt < split ? pkt / (p.run_base + 1) : p.run_rem + ((pkt - split) / p.run_base);
 }
 
-// Rewrites one group's raw activations (G 16-bit values, row `m` of the stage) in place into the
-// order and formats the unpack mode multiplies with -- per word-row the four pairs (a0,a4)
-// (a1,a5) (a2,a6) (a3,a7) -- and returns S = sum a and the constant term B.
+// Turns one group's raw activations (this lane's 4 consecutive 16-bit values, `raw`) into the order
+// and formats the unpack mode multiplies with -- per word-row the four pairs (a0,a4) (a1,a5)
+// (a2,a6) (a3,a7) -- writes them to the warp's activation buffer and returns S = sum a and the
+// constant term B.
 template <int G, class Mode>
-__device__ __forceinline__ void stage_activations(uint32_t act_addr, int lane, float& s_out,
-                                                  float& b_out) {
+__device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, int lane,
+                                                  float& s_out, float& b_out) {
   using E = typename Mode::Elem;
   constexpr int kActiveLanes = G / 4;
   float s = 0.0f;
@@ -72,7 +94,6 @@ __device__ __forceinline__ void stage_activations(uint32_t act_addr, int lane, f
   uint32_t p01 = 0;
   uint32_t p23 = 0;
   if (lane < kActiveLanes) {
-    const uint2 raw = lds64(act_addr + lane * 8);
     const float f0 = E::to_float(static_cast<unsigned short>(raw.x & 0xffffu));
     const float f1 = E::to_float(static_cast<unsigned short>(raw.x >> 16));
     const float f2 = E::to_float(static_cast<unsigned short>(raw.y & 0xffffu));
@@ -122,43 +143,37 @@ __device__ __forceinline__ void store_tile_row(void* out, long long elem_offset,
 // Returns false if a copy never arrived (the status word is set).
 template <int G, int M_TILE, class Mode, class TileDone>
 __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t ring_addr,
-                                                   uint32_t bar_addr, int row0, int m_act,
+                                                   uint32_t bar_addr, uint32_t act_addr, int row0,
+                                                   int m_act,
                                                    uint32_t p_begin, uint32_t p_end, int lane,
                                                    float (&y)[M_TILE][4], TileDone&& on_tile_done) {
   using E = typename Mode::Elem;
   constexpr int kStride = packet_stride(G);
   constexpr int kQBytes = packet_q_bytes(G);
   constexpr int kActBytes = G * 2;
-  constexpr int kStageBytes = kStride + (M_TILE * kActBytes);
+  constexpr int kStageBytes = kStride;
   constexpr int kWordRows = G / 8;
+  constexpr int kActLanes = G / 4;
 
   const int stages = p.stages;
   const uint32_t count = p_end - p_begin;
   const uint64_t weight_policy = l2_evict_first_policy();
-  const uint64_t act_policy = l2_evict_last_policy();
   const auto* act_bytes = static_cast<const uint8_t*>(p.act);
   const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
 
   uint32_t tile = p_begin / num_groups;
   const uint32_t first_group = p_begin - (tile * num_groups);
 
-  // Issue side (lane 0 only acts; the counters are cheap enough to keep in every lane).
+  // Issue side: lane 0 alone issues copies; the counters are cheap enough to keep in every lane.
   uint32_t issue_idx = 0;
-  uint32_t issue_group = first_group;
   int issue_slot = 0;
   auto issue_next = [&]() {
     const uint32_t bar = bar_addr + (issue_slot * 8);
-    const uint32_t dst = ring_addr + (issue_slot * kStageBytes);
-    mbar_expect_tx(bar, static_cast<uint32_t>(kStride + (m_act * kActBytes)));
-    bulk_copy_g2s(dst, p.packets + (static_cast<size_t>(p_begin + issue_idx) * kStride), kStride,
-                  bar, weight_policy);
-    for (int m = 0; m < m_act; ++m) {
-      const size_t elem = (static_cast<size_t>(row0 + m) * p.k) + (issue_group * G);
-      bulk_copy_g2s(dst + kStride + (m * kActBytes), act_bytes + (elem * 2), kActBytes, bar,
-                    act_policy);
-    }
+    mbar_expect_tx(bar, static_cast<uint32_t>(kStride));
+    bulk_copy_g2s(ring_addr + (issue_slot * kStageBytes),
+                  p.packets + (static_cast<size_t>(p_begin + issue_idx) * kStride), kStride, bar,
+                  weight_policy);
     ++issue_idx;
-    issue_group = (issue_group + 1 == num_groups) ? 0 : issue_group + 1;
     issue_slot = (issue_slot + 1 == stages) ? 0 : issue_slot + 1;
   };
 
@@ -168,6 +183,30 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       issue_next();
     }
   }
+  trace_mark(1);
+
+  // Programmatic dependent launch: the weight copies above do not depend on the kernel before
+  // this one in the stream, so they are already in flight; let the kernel after this one start
+  // its own prologue, then wait for the one before us before touching activations, outputs or
+  // scratch (all of which it may have written).
+  pdl_launch_dependents();
+  pdl_wait_for_prerequisites();
+
+  // Activations: plain global loads (they stay in L2), one packet ahead, straight to registers.
+  uint32_t act_group = first_group;
+  auto load_activations = [&](uint2 (&dst)[M_TILE]) {
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+      dst[m] = make_uint2(0u, 0u);
+      if (m < m_act && lane < kActLanes) {
+        const size_t elem = (static_cast<size_t>(row0 + m) * p.k) + (act_group * G);
+        dst[m] = __ldg(reinterpret_cast<const uint2*>(act_bytes + (elem * 2)) + lane);
+      }
+    }
+    act_group = (act_group + 1 == num_groups) ? 0 : act_group + 1;
+  };
+  uint2 next_raw[M_TILE];
+  load_activations(next_raw);
 
   uint32_t pkt = p_begin;
   uint32_t tile_end = (tile + 1) * num_groups;
@@ -197,6 +236,18 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       ok = false;
       break;
     }
+    if (j == 0) {
+      trace_mark(2);
+    }
+
+    uint2 raw[M_TILE];
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+      raw[m] = next_raw[m];
+    }
+    if (j + 1 < count) {
+      load_activations(next_raw);
+    }
 
     float group_sum[M_TILE];
     float acc[M_TILE][4][2];
@@ -205,7 +256,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       float bias = 0.0f;
       group_sum[m] = 0.0f;
       if (m < m_act) {
-        stage_activations<G, Mode>(stage + kStride + (m * kActBytes), lane, group_sum[m], bias);
+        stage_activations<G, Mode>(raw[m], act_addr + (m * kActBytes), lane, group_sum[m], bias);
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -225,7 +276,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       u[3] = Mode::unpack(wq.w);
 #pragma unroll
       for (int m = 0; m < M_TILE; ++m) {
-        const uint4 a = lds128(stage + kStride + (m * kActBytes) + (r * 16));
+        const uint4 a = lds128(act_addr + (m * kActBytes) + (r * 16));
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           Mode::mac(acc[m][c][0], acc[m][c][1], u[c], a);
@@ -292,18 +343,20 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 
 // Shared-memory plan of the stream kernel, used by host and device alike.
 struct StreamSmem {
-  uint32_t barriers;  // offset of warp 0's barriers
-  uint32_t slots;     // offset of the per-warp partial-sum slots
-  uint32_t rings;     // offset of warp 0's ring
+  uint32_t barriers;  // offset of warp 0's barriers (8 bytes per stage)
+  uint32_t slots;     // offset of the per-warp partial-sum slots (2 x M_TILE x 128 floats each)
+  uint32_t acts;      // offset of the per-warp staged activations (M_TILE x G 16-bit values each)
+  uint32_t rings;     // offset of warp 0's ring (stages x packet)
   uint32_t total;
 };
-__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int stages, int stage_bytes,
+__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int stages, int group,
                                                        int m_tile) {
   StreamSmem plan;
   plan.barriers = 0;
   plan.slots = ((static_cast<uint32_t>(warps) * stages * 8) + 127u) & ~127u;
-  plan.rings = plan.slots + (static_cast<uint32_t>(warps) * 2 * m_tile * kTileCols * 4);
-  plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * stage_bytes);
+  plan.acts = plan.slots + (static_cast<uint32_t>(warps) * 2 * m_tile * kTileCols * 4);
+  plan.rings = plan.acts + (static_cast<uint32_t>(warps) * m_tile * group * 2);
+  plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * packet_stride(group));
   return plan;
 }
 
@@ -312,7 +365,7 @@ __global__ void __launch_bounds__(512, 1)
     w4a16_gemv_stream_kernel(const __grid_constant__ GemvParams p) {
   using E = typename Mode::Elem;
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kStageBytes = packet_stride(G) + (M_TILE * G * 2);
+  constexpr int kStageBytes = packet_stride(G);
   constexpr int kSlotFloats = M_TILE * kTileCols;
 
   const int lane = static_cast<int>(threadIdx.x) & 31;
@@ -328,9 +381,10 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
 
   const int stages = p.stages;
-  const StreamSmem plan = stream_smem_plan(warps_per_cta, stages, kStageBytes, M_TILE);
+  const StreamSmem plan = stream_smem_plan(warps_per_cta, stages, G, M_TILE);
   const uint32_t smem_base = smem_addr(smem);
   const uint32_t bar_addr = smem_base + plan.barriers + (warp * stages * 8);
+  const uint32_t act_addr = smem_base + plan.acts + (warp * M_TILE * G * 2);
   const uint32_t ring_addr = smem_base + plan.rings + (warp * stages * kStageBytes);
   float* slots = reinterpret_cast<float*>(smem + plan.slots);  // [warp][2][kSlotFloats]
 
@@ -338,6 +392,7 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t p_end = active ? run_begin(v + 1, p) : 0;
   const uint32_t first_tile = p_begin / num_groups;
 
+  trace_mark(0);
   if (active) {
     if (lane == 0) {
       for (int s = 0; s < stages; ++s) {
@@ -374,10 +429,15 @@ __global__ void __launch_bounds__(512, 1)
             make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
       }
     };
-    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, row0, m_act, p_begin, p_end,
-                                              lane, y, on_tile_done);
+    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, act_addr, row0, m_act,
+                                              p_begin, p_end, lane, y, on_tile_done);
+  } else {
+    pdl_launch_dependents();
+    pdl_wait_for_prerequisites();
   }
+  trace_mark(3);
   __syncthreads();
+  trace_mark(4);
 
   // ---- CTA-level finish ---------------------------------------------------------------------
   const uint32_t cta_first_run = cta * warps_per_cta;
@@ -506,6 +566,7 @@ __global__ void __launch_bounds__(512, 1)
       tickets[tile] = 0;  // ready for the next call on this workspace
     }
   }
+  trace_mark(5);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -525,9 +586,10 @@ template <int G, int M_TILE, class Mode>
 __global__ void __launch_bounds__(128, 1)
     w4a16_split_k_kernel(const __grid_constant__ SplitKParams sp) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kStageBytes = packet_stride(G) + (M_TILE * G * 2);
+  constexpr int kStageBytes = packet_stride(G);
   constexpr int kWarps = 4;
   __shared__ float reduce_buf[kWarps][M_TILE][kTileCols];
+  __shared__ __align__(16) unsigned short act_buf[kWarps][M_TILE][G];
 
   const GemvParams& p = sp.base;
   const int lane = static_cast<int>(threadIdx.x) & 31;
@@ -568,8 +630,12 @@ __global__ void __launch_bounds__(128, 1)
   if (w_end > w_begin) {
     const uint32_t base_pkt = static_cast<uint32_t>(tile) * p.num_groups;
     auto keep = [](uint32_t, uint32_t, uint32_t) {};
-    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, row0, m_act,
+    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr,
+                                              smem_addr(&act_buf[warp][0][0]), row0, m_act,
                                               base_pkt + w_begin, base_pkt + w_end, lane, y, keep);
+  } else {
+    pdl_launch_dependents();
+    pdl_wait_for_prerequisites();
   }
 #pragma unroll
   for (int m = 0; m < M_TILE; ++m) {

@@ -137,7 +137,7 @@ FK_W4A16_API int fk_w4a16_cublaslt_matmul(const void* activations, const void* w
 FK_W4A16_API int fk_w4a16_device_status(int* status);
 
 /* Launch-shape knobs of the fused GEMV, for tuning and tests: warps per CTA (1..16, 0 = auto),
- * ring stages per warp (2..8, 0 = auto) and CTAs in the grid (0 = one per SM). Process-wide. */
+ * ring stages per warp (1..8, 0 = auto) and CTAs in the grid (0 = one per SM). Process-wide. */
 FK_W4A16_API int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas);
 
 #ifdef __cplusplus
