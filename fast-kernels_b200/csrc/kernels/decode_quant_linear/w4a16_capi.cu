@@ -477,16 +477,40 @@ int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* strea
   return FK_W4A16_OK;
 }
 
-int fk_w4a16_gemv(const void* activations, const void* packets, void* output, void* workspace,
-                  size_t workspace_bytes, int batch, int n, int k, int group_size,
-                  int packet_stride_bytes, int dtype, void* stream) {
+int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
+  if (args == nullptr) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "args must not be null");
+  }
+  const int batch = args->batch;
+  const int n = args->n;
+  const int k = args->k;
+  const int group_size = args->group_size;
   FK_TRY(check_dimensions(batch, n, k, group_size));
-  FK_TRY(check_stride(group_size, packet_stride_bytes));
-  FK_TRY(check_dtype(dtype));
-  FK_TRY(check_pointer(activations, "activations", 16));
-  FK_TRY(check_pointer(packets, "packets", 16));
-  FK_TRY(check_pointer(output, "output", 8));
-  FK_TRY(check_pointer(workspace, "workspace", 256));
+  FK_TRY(check_stride(group_size, args->packet_stride_bytes));
+  FK_TRY(check_dtype(args->dtype));
+  FK_TRY(check_pointer(args->activations, "activations", 16));
+  FK_TRY(check_pointer(args->packets, "packets", 16));
+  FK_TRY(check_pointer(args->output, "output", args->output_f32 != 0 ? 16 : 8));
+  FK_TRY(check_pointer(args->workspace, "workspace", 256));
+  const long long out_ld = args->output_ld == 0 ? n : args->output_ld;
+  if (out_ld < n || args->output_col0 < 0 || args->output_col0 + n > out_ld ||
+      (out_ld % 4) != 0 || (args->output_col0 % 4) != 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                "output_ld / output_col0 must place n columns inside a row, in multiples of 4");
+  }
+  if (args->num_peers < 0 || args->num_peers > FK_W4A16_MAX_PEERS) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "num_peers must be between 0 and 7");
+  }
+  for (int peer = 0; peer < args->num_peers; ++peer) {
+    FK_TRY(check_pointer(args->peer_outputs[peer], "peer_outputs[i]", args->output_f32 != 0 ? 16 : 8));
+    if (args->local_signal != nullptr) {
+      FK_TRY(check_pointer(args->peer_signals[peer], "peer_signals[i]", 4));
+    }
+  }
+  if (args->local_signal != nullptr) {
+    FK_TRY(check_pointer(args->local_signal, "local_signal", 4));
+  }
+
   DeviceInfo* info = nullptr;
   FK_TRY(device_info(&info));
   const Plan plan =
@@ -494,24 +518,35 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
-  if (workspace_bytes < workspace_bytes_for(plan)) {
+  if (args->workspace_bytes < workspace_bytes_for(plan)) {
     std::ostringstream oss;
-    oss << "workspace_bytes=" << workspace_bytes << " is smaller than the required "
+    oss << "workspace_bytes=" << args->workspace_bytes << " is smaller than the required "
         << workspace_bytes_for(plan);
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
   }
   const int num_tiles = n / kTileCols;
-  if (static_cast<long long>(plan.row_tiles) * num_tiles > kTicketCapacity) {
+  if (static_cast<long long>(plan.row_tiles) * num_tiles > kTicketCapacity - 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * batch exceeds the ticket area of a workspace");
   }
 
   GemvParams params{};
-  params.act = activations;
-  params.packets = static_cast<const uint8_t*>(packets);
-  params.out = output;
-  params.tickets = static_cast<int*>(workspace);
-  params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
+  params.act = args->activations;
+  params.packets = static_cast<const uint8_t*>(args->packets);
+  params.out = args->output;
+  params.tickets = static_cast<int*>(args->workspace);
+  params.exit_count = static_cast<int*>(args->workspace) + (kTicketCapacity - 1);
+  params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(args->workspace) + kTicketBytes);
   params.status = info->status_word;
+  params.out_ld = out_ld;
+  params.out_col0 = args->output_col0;
+  params.out_f32 = args->output_f32 != 0 ? 1 : 0;
+  params.num_peers = args->num_peers;
+  for (int peer = 0; peer < args->num_peers; ++peer) {
+    params.peer_out[peer] = args->peer_outputs[peer];
+    params.peer_signal[peer] = args->peer_signals[peer];
+  }
+  params.local_signal = args->local_signal;
+  params.wait_value = args->wait_value;
   params.m = batch;
   params.n = n;
   params.k = k;
@@ -522,12 +557,31 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
   params.total_packets = plan.total_packets;
   params.run_base = plan.total_packets / static_cast<uint32_t>(plan.active_warps);
   params.run_rem = plan.total_packets % static_cast<uint32_t>(plan.active_warps);
-  auto* s = static_cast<cudaStream_t>(stream);
+  auto* s = static_cast<cudaStream_t>(args->stream);
   const int max_smem = info->max_smem_optin;
-  return dispatch(group_size, plan.m_tile, dtype, [&](auto g, auto mt, auto e) {
+  return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
     return launch_stream<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
                                                                                  max_smem, s);
   });
+}
+
+int fk_w4a16_gemv(const void* activations, const void* packets, void* output, void* workspace,
+                  size_t workspace_bytes, int batch, int n, int k, int group_size,
+                  int packet_stride_bytes, int dtype, void* stream) {
+  fk_w4a16_gemv_args args{};
+  args.activations = activations;
+  args.packets = packets;
+  args.output = output;
+  args.workspace = workspace;
+  args.workspace_bytes = workspace_bytes;
+  args.batch = batch;
+  args.n = n;
+  args.k = k;
+  args.group_size = group_size;
+  args.packet_stride_bytes = packet_stride_bytes;
+  args.dtype = dtype;
+  args.stream = stream;
+  return fk_w4a16_gemv_ex(&args);
 }
 
 int fk_w4a16_gemv_static(const void* activations, const void* packets, void* output, int batch,

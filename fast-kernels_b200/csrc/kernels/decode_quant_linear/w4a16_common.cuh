@@ -128,6 +128,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+constexpr uint32_t kPeerWaitLimit = 8u << 20;  // polls of >= 200 ns each while waiting for peers
+
 // Bounded wait: returns false when the limit is hit instead of spinning forever.
 constexpr uint32_t kCopyWaitLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {

@@ -54,6 +54,8 @@ __device__ __forceinline__ void trace_mark(int slot) {
 __device__ __forceinline__ void trace_mark(int) {}
 #endif
 
+constexpr int kMaxPeers = 7;
+
 struct GemvParams {
   const void* act;         // [m, k] 16-bit, row-major
   const uint8_t* packets;  // [num_tiles * num_groups, stride]
@@ -61,6 +63,21 @@ struct GemvParams {
   float* scratch;          // [row_tiles][ctas][2][M_TILE * 128] fp32
   int* tickets;            // [row_tiles][num_tiles], zero between calls
   int* status;             // device status word
+  // Output placement. Element (row, col) of the result goes to out[row * out_ld + out_col0 + col]
+  // and to the same offset in each of peer_out[0 .. num_peers) -- buffers of other GPUs mapped
+  // into this process (plain stores over NVLink). out_f32 selects unrounded fp32 outputs.
+  long long out_ld;
+  long long out_col0;
+  int out_f32;
+  int num_peers;
+  void* peer_out[kMaxPeers];
+  // Exchange completion. When local_signal is set, the last CTA to leave adds 1 (system scope,
+  // after all of this GPU's stores) to local_signal and to every peer_signal, then stays until
+  // local_signal has reached wait_value -- i.e. until every GPU of the group has delivered.
+  unsigned int* peer_signal[kMaxPeers];
+  unsigned int* local_signal;
+  unsigned int wait_value;
+  int* exit_count;         // zero between calls; counts CTAs that have finished
   int m, n, k;
   int num_groups;          // k / G
   int num_tiles;           // n / 128
@@ -127,8 +144,13 @@ __device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, 
 }
 
 template <class E>
-__device__ __forceinline__ void store_tile_row(void* out, long long elem_offset, int lane,
-                                               const float (&y)[4]) {
+__device__ __forceinline__ void store_tile_row_to(void* out, int out_f32, long long elem_offset,
+                                                  int lane, const float (&y)[4]) {
+  if (out_f32 != 0) {
+    auto* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + elem_offset) + lane;
+    *dst = make_float4(y[0], y[1], y[2], y[3]);
+    return;
+  }
   uint2 packed;
   packed.x = static_cast<uint32_t>(E::from_float(y[0])) |
              (static_cast<uint32_t>(E::from_float(y[1])) << 16);
@@ -136,6 +158,18 @@ __device__ __forceinline__ void store_tile_row(void* out, long long elem_offset,
              (static_cast<uint32_t>(E::from_float(y[3])) << 16);
   auto* dst = reinterpret_cast<uint2*>(static_cast<unsigned short*>(out) + elem_offset) + lane;
   *dst = packed;
+}
+
+// Stores one row of a finished tile (this lane's 4 columns) locally and on every peer.
+template <class E>
+__device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uint32_t tile, int lane,
+                                               const float (&y)[4]) {
+  const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
+                           (static_cast<long long>(tile) * kTileCols);
+  store_tile_row_to<E>(p.out, p.out_f32, offset, lane, y);
+  for (int peer = 0; peer < p.num_peers; ++peer) {
+    store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, y);
+  }
 }
 
 // One warp's pass over packets [p_begin, p_end) of the tile-major packet stream, accumulating
@@ -412,12 +446,10 @@ __global__ void __launch_bounds__(512, 1)
     }
     auto on_tile_done = [&](uint32_t tile, uint32_t first_pkt, uint32_t end_pkt) {
       if ((end_pkt - first_pkt) == num_groups) {
-        const long long out_col = static_cast<long long>(tile) * kTileCols;
 #pragma unroll
         for (int m = 0; m < M_TILE; ++m) {
           if (m < m_act) {
-            store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane,
-                              y[m]);
+            store_tile_row<E>(p, row0 + m, tile, lane, y[m]);
           }
         }
         return;
@@ -483,13 +515,11 @@ __global__ void __launch_bounds__(512, 1)
       }
     }
 
-    const long long out_col = static_cast<long long>(tile) * kTileCols;
     if (cta_begin <= tile_lo && cta_end >= tile_hi) {
 #pragma unroll
       for (int m = 0; m < M_TILE; ++m) {
         if (m < m_act) {
-          store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane,
-                            sum[m]);
+          store_tile_row<E>(p, row0 + m, tile, lane, sum[m]);
         }
       }
       continue;
@@ -559,11 +589,43 @@ __global__ void __launch_bounds__(512, 1)
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
       if (m < m_act) {
-        store_tile_row<E>(p.out, (static_cast<long long>(row0 + m) * p.n) + out_col, lane, sum[m]);
+        store_tile_row<E>(p, row0 + m, tile, lane, sum[m]);
       }
     }
     if (lane == 0) {
       tickets[tile] = 0;  // ready for the next call on this workspace
+    }
+  }
+
+  // ---- exchange completion (multi-GPU calls only) ------------------------------------------
+  if (p.local_signal != nullptr) {
+    __threadfence_system();  // this thread's peer stores are performed before it counts as done
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int ctas_total = gridDim.x * gridDim.y;
+      const int finished = atomicAdd(p.exit_count, 1);
+      if (finished == static_cast<int>(ctas_total) - 1) {
+        __threadfence_system();
+        *p.exit_count = 0;
+        for (int peer = 0; peer < p.num_peers; ++peer) {
+          atomicAdd_system(p.peer_signal[peer], 1u);
+        }
+        atomicAdd_system(p.local_signal, 1u);
+        // Bounded wait for the other GPUs' deliveries (about two seconds at most).
+        bool arrived = false;
+        for (uint32_t spin = 0; spin < kPeerWaitLimit; ++spin) {
+          const unsigned int seen = *reinterpret_cast<volatile unsigned int*>(p.local_signal);
+          if (static_cast<int>(seen - p.wait_value) >= 0) {
+            arrived = true;
+            break;
+          }
+          __nanosleep(200);
+        }
+        if (!arrived) {
+          atomicExch(p.status, static_cast<int>(kStatusPeerWaitTimeout));
+        }
+        __threadfence_system();
+      }
     }
   }
   trace_mark(5);

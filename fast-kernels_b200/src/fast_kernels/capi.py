@@ -28,6 +28,36 @@ _c_void_p = ctypes.c_void_p
 _c_int = ctypes.c_int
 _c_size_t = ctypes.c_size_t
 
+MAX_PEERS = 7
+
+
+class GemvArgs(ctypes.Structure):
+    """``fk_w4a16_gemv_args`` of include/fk_w4a16.h (zero-initialised on construction)."""
+
+    _fields_ = [
+        ("activations", _c_void_p),
+        ("packets", _c_void_p),
+        ("output", _c_void_p),
+        ("workspace", _c_void_p),
+        ("workspace_bytes", _c_size_t),
+        ("batch", _c_int),
+        ("n", _c_int),
+        ("k", _c_int),
+        ("group_size", _c_int),
+        ("packet_stride_bytes", _c_int),
+        ("dtype", _c_int),
+        ("output_f32", _c_int),
+        ("output_ld", ctypes.c_longlong),
+        ("output_col0", ctypes.c_longlong),
+        ("num_peers", _c_int),
+        ("peer_outputs", _c_void_p * MAX_PEERS),
+        ("peer_signals", _c_void_p * MAX_PEERS),
+        ("local_signal", _c_void_p),
+        ("wait_value", ctypes.c_uint),
+        ("stream", _c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); mirrors include/fk_w4a16.h one to one.
 SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "fk_w4a16_last_error": (ctypes.c_char_p, []),
@@ -46,6 +76,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
          _c_int, _c_int, _c_void_p],
     ),
+    "fk_w4a16_gemv_ex": (_c_int, [ctypes.POINTER(GemvArgs)]),
     "fk_w4a16_gemv_static": (
         _c_int,
         [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],

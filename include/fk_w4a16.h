@@ -83,6 +83,42 @@ FK_W4A16_API int fk_w4a16_gemv(const void* activations, const void* packets, voi
                   size_t workspace_bytes, int batch, int n, int k, int group_size,
                   int packet_stride_bytes, int dtype, void* stream);
 
+/* The same GEMV with every option spelled out; fk_w4a16_gemv(...) is this call with the options
+ * at their defaults. The options exist for layers that are sharded over the GPUs of one node
+ * (no counterpart in the reference, which is single-GPU):
+ *   - output_f32: write unrounded fp32 sums instead of 16-bit outputs (a K-shard's partial result);
+ *   - output_ld / output_col0: place the n local columns inside a wider row-major matrix
+ *     (an N-shard's slice of the full output);
+ *   - peer_outputs: up to 7 more buffers -- other GPUs' memory mapped into this process -- that
+ *     receive the same tiles by plain stores over NVLink while the kernel runs, so the exchange
+ *     overlaps the computation tile by tile;
+ *   - local_signal / peer_signals / wait_value: 32-bit counters in device memory, one per GPU of
+ *     the group. When the call's last output has been written everywhere, each counter is
+ *     incremented once (system scope), and the kernel does not complete before local_signal has
+ *     reached wait_value (bounded: after about two seconds it gives up and sets the device status
+ *     word). With wait_value = calls_so_far * group_size, kernels queued after this call on the
+ *     same stream see every GPU's contribution. Leave local_signal NULL for single-GPU use.
+ * Zero-initialise the struct; unset fields then mean "default". */
+#define FK_W4A16_MAX_PEERS 7
+typedef struct fk_w4a16_gemv_args {
+  const void* activations;
+  const void* packets;
+  void* output;
+  void* workspace;
+  size_t workspace_bytes;
+  int batch, n, k, group_size, packet_stride_bytes, dtype;
+  int output_f32;
+  long long output_ld;   /* elements between rows of `output`; 0 means n */
+  long long output_col0; /* column of `output` that receives local column 0 */
+  int num_peers;
+  void* peer_outputs[FK_W4A16_MAX_PEERS];
+  unsigned int* peer_signals[FK_W4A16_MAX_PEERS];
+  unsigned int* local_signal;
+  unsigned int wait_value;
+  void* stream;
+} fk_w4a16_gemv_args;
+FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
+
 /* fk_w4a16_gemv for callers that cannot hand over scratch memory. This entry point has no
  * counterpart in the reference. It is meant for hosts where device allocation is off the table
  * once start-up is over: a serving process that has already handed all free device memory to its

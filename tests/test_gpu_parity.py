@@ -246,3 +246,47 @@ def test_gemv_respects_the_stream() -> None:
     y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
                           oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]), 128, 0)
     assert oracle.max_rel_err(out.float().cpu().numpy(), y64) <= GEMV_REL_TOL
+
+
+def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
+    """fk_w4a16_gemv_ex: fp32 partial outputs, a slice of a wider matrix, a second destination
+    and the completion counters -- here with both destinations on this GPU."""
+    lib = capi.load_library()
+    shape = LayerShape("t", 128 * 6, 128 * 5, batch=2, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=808)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    plain = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    ld, col0 = shape.n * 3, shape.n
+    signals = torch.zeros(64, dtype=torch.int32, device="cuda")
+    for want_f32 in (0, 1):
+        dtype = torch.float32 if want_f32 else torch.bfloat16
+        wide = torch.full((2, ld), -7.0, dtype=dtype, device="cuda")
+        mirror = torch.full((2, ld), -7.0, dtype=dtype, device="cuda")
+        args = capi.GemvArgs()
+        ws = WS.get(capi, 2, shape.n, shape.k, 128)
+        args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), wide.data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = 2, shape.n, shape.k, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.output_f32, args.output_ld, args.output_col0 = want_f32, ld, col0
+        args.num_peers = 1
+        args.peer_outputs[0] = mirror.data_ptr()
+        args.peer_signals[0] = signals.data_ptr() + 4
+        args.local_signal = signals.data_ptr()
+        args.wait_value = want_f32 + 1  # the counter after this call's own increment
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+        torch.cuda.synchronize()
+        assert signals[0].item() == want_f32 + 1 and signals[1].item() == want_f32 + 1
+        for buf in (wide, mirror):
+            assert (buf[:, :col0] == -7.0).all() and (buf[:, col0 + shape.n:] == -7.0).all()
+        assert torch.equal(wide, mirror)
+        got = wide[:, col0:col0 + shape.n]
+        if want_f32:
+            assert torch.equal(got.to(torch.bfloat16), plain)  # same sums, rounded once
+        else:
+            assert torch.equal(got, plain)
+    with pytest.raises(ValueError, match="output_ld"):
+        args.output_col0 = ld
+        capi.check(lib.fk_w4a16_gemv_ex(args))
