@@ -354,6 +354,81 @@ def _cpu_baseline_leg() -> dict:
     }
 
 
+def _sharded_layers(torch, dist, capi, device, world: int, rank: int, peak_gbs: float) -> list[dict]:
+    """The two layers that are large enough to be split over the GPUs of a node (70B-style fused
+    gate+up, N-split; down_proj, K-split), each with the NCCL exchange and with the exchange done
+    by the GEMV kernel itself through peer memory. Per-call device time over a CUDA graph that
+    cycles through several weight copies (so shards that would fit in L2 still come from HBM)."""
+    from fast_kernels.dist import ShardedW4A16Linear, column_shard_packets, row_shard_packets
+    from fast_kernels.workloads import SHARDED_COLUMN, SHARDED_ROW, make_problem
+
+    lib = capi.load_library()
+    results = []
+    for shape, mode in ((SHARDED_COLUMN, "column"), (SHARDED_ROW, "row")):
+        prob = make_problem(shape)
+        q, alpha, beta = (prob[key].to(device) for key in ("q_u8", "alpha", "beta"))
+        act = prob["activations"].to(device)
+        stride = capi.packet_stride_bytes(128)
+        packets = torch.empty(((shape.n // 128) * (shape.k // 128), stride), dtype=torch.uint8, device=device)
+        capi.check(lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(), packets.data_ptr(),
+                                             shape.n, shape.k, 128, stride,
+                                             int(torch.cuda.current_stream(device).cuda_stream)))
+        shard = (column_shard_packets if mode == "column" else row_shard_packets)(
+            packets, n=shape.n, k=shape.k, group_size=128, rank=rank, world=world).contiguous()
+        del q, alpha, beta, packets
+        copies = max(2, min(8, int(400e6 // shard.numel()) + 1))
+        gen = torch.Generator().manual_seed(7)
+        shards = [shard] + [shard[torch.randperm(shard.shape[0], generator=gen).to(device)].contiguous()
+                            for _ in range(copies - 1)]
+        for exchange in ("nccl", "peer"):
+            layers = [ShardedW4A16Linear(s, n=shape.n, k=shape.k, group_size=128, mode=mode,
+                                         dtype=torch.bfloat16, exchange=exchange, packets_are_local=True,
+                                         max_batch=1) for s in shards]
+            for layer in layers:  # eager warm-up (function attributes, communicators)
+                layer(act)
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            mode_used = "cuda graph"
+            try:
+                graph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream(device=device)
+                side.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+                    for layer in layers:
+                        layer(act)
+                torch.cuda.current_stream(device).wait_stream(side)
+                run = graph.replay
+            except RuntimeError:
+                mode_used = "eager"
+
+                def run() -> None:
+                    for layer in layers:
+                        layer(act)
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            reps = 20
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(reps):
+                run()
+            stop.record()
+            torch.cuda.synchronize(device)
+            t = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item()) * 1e3 / (reps * len(layers))
+            total_gbs = shape.algorithmic_bytes() / (us * 1e-6) / 1e9
+            results.append({"layer": shape.name, "n": shape.n, "k": shape.k, "split": mode, "exchange": exchange,
+                            "us_per_call": us, "aggregate_gbs": total_gbs,
+                            "frac_of_n_gpu_peak": total_gbs / (peak_gbs * world), "launch": mode_used,
+                            "weight_copies": len(layers)})
+            del layers
+        del shards, shard
+        torch.cuda.empty_cache()
+    return results
+
+
 def run_ours(args) -> int:
     import torch
     import torch.distributed as dist
@@ -422,6 +497,10 @@ def run_ours(args) -> int:
         e2e_seconds = float(t.item())
     e2e_value = step_bytes * world * e2e_steps / e2e_seconds / 1e12
 
+    sharded = None
+    if world > 1 and not args.no_sharded:
+        sharded = _sharded_layers(torch, dist, capi, device, world, rank, peak_gbs)
+
     if rank == 0:
         achieved_gbs = step_bytes * args.steps / seconds / 1e9  # this rank's kernels, gaps included
         line = {
@@ -464,6 +543,12 @@ def run_ours(args) -> int:
             "gpu_launches": calls_per_step * args.steps,
             "clocks": clocks.summary(),
         }
+        if sharded is not None:
+            line["sharded_layers"] = {
+                "note": "strong scaling of single large layers over this run's GPUs (N-split + gather, "
+                        "K-split + reduce); us_per_call is the max over ranks",
+                "results": sharded,
+            }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = _cpu_baseline_leg()
         print(json.dumps(line), flush=True)
@@ -480,6 +565,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=None)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~10 s CPU baseline leg")
+    parser.add_argument("--no-sharded", action="store_true", help="N > 1: skip the sharded-layer measurements")
     args = parser.parse_args()
     if args.impl == "reference":
         args.steps = 10 if args.steps is None else args.steps

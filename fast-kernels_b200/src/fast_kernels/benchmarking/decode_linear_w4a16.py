@@ -5,7 +5,7 @@ Follows the flow of the reference's runner (src/fast_kernels/benchmarking/decode
 agreement with an explicit fp32 torch expression under the suite's tolerances, then times the two
 baselines (``baselines.ids[0]`` = torch reference, ``[1]`` = vendor GEMM, by position) and every
 kernel id. Differences: device time comes from CUDA events and is what ``latency_us_*`` reports
-(the wall clock, 4 warm-up + 12 timed calls as in the reference, is kept beside it); weights rotate
+(the wall clock, 4 warm-up + 12 timed calls as in the reference, is kept beside it) and is taken over CUDA-graph replays; weights rotate
 over enough copies to exceed L2 so the figures are HBM figures; ``metrics`` carries the achieved
 bandwidth. Without a GPU every case is emitted as ``skipped`` with the reason.
 """
@@ -65,10 +65,33 @@ def _explicit_reference(torch: Any, act: Any, q_u8: Any, alpha: Any, beta: Any, 
 
 
 def _time_device(torch: Any, calls: list[Callable[[], Any]], iters: int) -> list[float]:
-    """One CUDA-event pair per call, cycling through ``calls`` (distinct weight copies)."""
+    """Device time per call in microseconds, one sample per replay of a CUDA graph that holds one
+    launch per entry of ``calls`` (distinct weight copies), so that host launch overhead is not in
+    the figure. Falls back to one event pair per eager call if capture is refused."""
     for fn in calls[: max(1, min(len(calls), WARMUP_ITERS))]:
         fn()
     torch.cuda.synchronize()
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+            for fn in calls:
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(iters):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            samples.append(start.elapsed_time(stop) * 1e3 / len(calls))
+        return samples
+    except RuntimeError:
+        torch.cuda.synchronize()
     pairs = []
     for i in range(iters):
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -120,6 +120,10 @@ def load_library() -> ctypes.CDLL:
             f"{LIB_PATH} is missing: build it with `python fast-kernels_b200/build.py` "
             "(there is no CPU fallback for the W4A16 kernels)"
         )
+    try:
+        import torch  # noqa: F401  (its bundled cuBLASLt must be the one this library binds to)
+    except ImportError:
+        pass
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here means header and library disagree

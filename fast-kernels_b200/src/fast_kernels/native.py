@@ -11,6 +11,14 @@ _native: ModuleType | None
 _native_import_error: ImportError | None
 
 try:
+    # PyTorch bundles its own cuBLAS / cuBLASLt pair. Load it first so that the native library's
+    # dependency on libcublasLt.so.12 binds to that copy; letting the toolkit's copy in first
+    # would leave torch's cuBLAS talking to a cuBLASLt of a different release.
+    import torch  # noqa: F401
+except ImportError:  # the library also works without torch (C / ctypes callers)
+    pass
+
+try:
     _native = import_module("fast_kernels._native")
 except ImportError as exc:  # the extension has not been built
     _native = None
