@@ -15,6 +15,7 @@
 
 #include "w4a16_common.cuh"
 #include "w4a16_gemv_stream.cuh"
+#include "w4a16_gemm_mma.cuh"
 #include "w4a16_prep.cuh"
 
 #ifndef FK_W4A16_VERSION
@@ -202,17 +203,58 @@ struct Plan {
   uint32_t total_packets = 0;
   size_t smem_bytes = 0;
   size_t scratch_bytes = 0;
+  bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
+  size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
+
+// Shared memory of the tensor-core kernel: barriers | one slot per warp | rings.
+size_t mma_smem_bytes(int warps, int stages, int group, int mt) {
+  const size_t stage = (3 * ((group / 32) * 512 + 32)) + ((group / 32) * 512) + kScaleBytes +
+                       (static_cast<size_t>(mt) * mma_act_pitch(group));
+  return (((static_cast<size_t>(warps) * stages * 8) + 127) & ~size_t{127}) +
+         (static_cast<size_t>(warps) * mt * kTileCols * 4) + (static_cast<size_t>(warps) * stages * stage);
+}
 
 // `sm_count` and `max_smem` describe the device; the plan is a pure function of its arguments
 // so that fk_w4a16_workspace_bytes() and fk_w4a16_gemv() always agree.
 Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
                const LaunchConfig& cfg) {
   Plan plan;
-  plan.m_tile = m_tile_for_batch(batch);
-  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
+  if (batch > 4) {
+    plan.tensor_cores = true;
+    plan.m_tile = batch <= 8 ? 8 : 16;
+    plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
+    // Register budget (accumulators for 8 tiles x rows) caps the CTA at 256 threads.
+    int warps = cfg.warps > 0 ? cfg.warps : (plan.m_tile == 8 ? 8 : 6);
+    warps = warps > 8 ? 8 : warps;
+    const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+    long long workers = static_cast<long long>(ctas) * warps;
+    workers = workers > total_packets ? total_packets : workers;
+    warps = static_cast<int>((workers + ctas - 1) / ctas);
+    plan.warps = warps;
+    plan.grid_x = static_cast<int>((workers + warps - 1) / warps);
+    plan.active_warps = static_cast<int>(workers);
+    const long long longest_run = (total_packets + workers - 1) / workers;
+    int wanted = cfg.stages > 0 ? cfg.stages : 3;
+    wanted = wanted > longest_run ? static_cast<int>(longest_run) : wanted;
+    plan.stages = 0;
+    for (int candidate = wanted; candidate >= 1; --candidate) {
+      if (mma_smem_bytes(warps, candidate, group_size, plan.m_tile) <= static_cast<size_t>(max_smem)) {
+        plan.stages = candidate;
+        break;
+      }
+    }
+    plan.smem_bytes = mma_smem_bytes(warps, plan.stages < 1 ? 1 : plan.stages, group_size, plan.m_tile);
+    plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
+                         (plan.m_tile * kTileCols) * sizeof(float);
+    plan.staged_bytes = static_cast<size_t>(plan.row_tiles) * (k / group_size) * plan.m_tile *
+                        mma_act_pitch(group_size);
+    return plan;
+  }
+  plan.m_tile = m_tile_for_batch(batch);
+  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const int stage_bytes = packet_stride(group_size);
 
   // Default: as many warps as fit with a two-deep ring each (more warps hide more latency than
@@ -260,7 +302,8 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
 }
 
 size_t workspace_bytes_for(const Plan& plan) {
-  return kTicketBytes + ((plan.scratch_bytes + 255) & ~size_t{255});
+  return kTicketBytes + ((plan.scratch_bytes + 255) & ~size_t{255}) +
+         ((plan.staged_bytes + 255) & ~size_t{255});
 }
 
 // Opts a kernel in to the device's full dynamic shared memory, once per function and device
@@ -327,6 +370,39 @@ int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cuda
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
   FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params));
   return FK_W4A16_OK;
+}
+
+template <int G, int MT, class E>
+int launch_mma(const GemvParams& params, const Plan& plan, uint8_t* staged, int max_smem,
+               cudaStream_t stream) {
+  using Mode = UnpackModeFor<E>;
+  auto kernel = w4a16_gemm_mma_kernel<G, MT, Mode>;
+  static std::once_flag optin_flags[kMaxDevices];
+  FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
+  // Prepass (ordinary launch: it must not start before earlier work on the stream is done with
+  // the staging area), then the GEMM with programmatic serialisation behind it.
+  const long long items = static_cast<long long>(plan.row_tiles) * params.num_groups * MT;
+  stage_activations_mma_kernel<G, Mode><<<static_cast<unsigned>((items + 3) / 4), 128, 0, stream>>>(
+      static_cast<const uint16_t*>(params.act), staged, params.m, params.k, params.num_groups, MT, items);
+  FK_TRY_CUDA(cudaGetLastError());
+  MmaParams mma_params{};
+  mma_params.base = params;
+  mma_params.staged = staged;
+  const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
+  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, mma_params));
+  return FK_W4A16_OK;
+}
+
+template <class E, class Fn>
+int for_group_mt(int group_size, int mt, Fn&& fn) {
+  switch (group_size) {
+    case 32: return mt == 8 ? fn(std::integral_constant<int, 32>{}, std::integral_constant<int, 8>{}, E{})
+                            : fn(std::integral_constant<int, 32>{}, std::integral_constant<int, 16>{}, E{});
+    case 64: return mt == 8 ? fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 8>{}, E{})
+                            : fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 16>{}, E{});
+    default: return mt == 8 ? fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 8>{}, E{})
+                            : fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 16>{}, E{});
+  }
 }
 
 template <int G, int M_TILE, class E>
@@ -559,6 +635,16 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
   params.run_rem = plan.total_packets % static_cast<uint32_t>(plan.active_warps);
   auto* s = static_cast<cudaStream_t>(args->stream);
   const int max_smem = info->max_smem_optin;
+  if (plan.tensor_cores) {
+    uint8_t* staged = static_cast<uint8_t*>(args->workspace) + kTicketBytes +
+                      ((plan.scratch_bytes + 255) & ~size_t{255});
+    auto run = [&](auto g, auto mt, auto e) {
+      return launch_mma<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan, staged,
+                                                                               max_smem, s);
+    };
+    return args->dtype == FK_W4A16_DTYPE_BF16 ? for_group_mt<BF16>(group_size, plan.m_tile, run)
+                                              : for_group_mt<F16>(group_size, plan.m_tile, run);
+  }
   return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
     return launch_stream<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
                                                                                  max_smem, s);

@@ -216,6 +216,13 @@ struct NibblePairs {
 // term B such that sum_i pair_i * staged_i = sum_k q_k a_k + B.
 struct UnpackF16 {
   using Elem = F16;
+  // Tensor-core variant: both k-steps of a word multiply fp16 pairs. A constant-valued weight
+  // row (all kConstB / all kConstS) makes the MMA itself deliver B and S for every batch row.
+  static constexpr bool kEvenNibblesBf16 = false;
+  static constexpr uint32_t kEvenConstB = 0x64006400u;  // 1024 : sum 1024 * a' = B
+  static constexpr uint32_t kEvenConstS = 0x4C004C00u;  // 16   : sum 16 * (a / 16) = S
+  static constexpr uint32_t kOddConstB = 0x64006400u;
+  static constexpr uint32_t kOddConstS = 0x4C004C00u;
   static __device__ __forceinline__ NibblePairs unpack(uint32_t w) {
     NibblePairs u;
     u.p04 = mask_or<0x00f000f0u, 0x64006400u>(w << 4);
@@ -241,6 +248,11 @@ struct UnpackF16 {
 
 struct UnpackBF16 {
   using Elem = BF16;
+  static constexpr bool kEvenNibblesBf16 = true;
+  static constexpr uint32_t kEvenConstB = 0x43004300u;  // bf16 128 : sum 128 * a
+  static constexpr uint32_t kEvenConstS = 0x3F803F80u;  // bf16 1   : sum a
+  static constexpr uint32_t kOddConstB = 0x64006400u;   // fp16 1024
+  static constexpr uint32_t kOddConstS = 0x4C004C00u;   // fp16 16
   static __device__ __forceinline__ NibblePairs unpack(uint32_t w) {
     NibblePairs u;
     const uint32_t w8 = w >> 8;
@@ -267,6 +279,24 @@ struct UnpackBF16 {
     return static_cast<unsigned short>(__float_as_uint(f) >> 16);
   }
 };
+
+// D += A * B for one m16n8k16 tile, fp32 accumulate; A row-major 16x16, B 16x8 (k-major pairs).
+__device__ __forceinline__ void mma_16816_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_16816_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -97,17 +97,15 @@ __device__ __forceinline__ uint32_t run_owner(uint32_t pkt, const GemvParams& p)
   return pkt < split ? pkt / (p.run_base + 1) : p.run_rem + ((pkt - split) / p.run_base);
 }
 
-// Turns one group's raw activations (this lane's 4 consecutive 16-bit values, `raw`) into the order
-// and formats the unpack mode multiplies with -- per word-row the four pairs (a0,a4) (a1,a5)
-// (a2,a6) (a3,a7) -- writes them to the warp's activation buffer and returns S = sum a and the
-// constant term B.
+// Turns this lane's 4 consecutive raw activations of a group (`raw`; lanes >= G/4 hold nothing)
+// into the 8 bytes it contributes to the staged layout: per word-row the four pairs (a0,a4)
+// (a1,a5) (a2,a6) (a3,a7) in the formats the unpack mode multiplies with. Even lanes end up with
+// pairs 0 and 1 of word-row lane/2, odd lanes with pairs 2 and 3. Also accumulates this lane's
+// share of S = sum a and of the constant term B.
 template <int G, class Mode>
-__device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, int lane,
-                                                  float& s_out, float& b_out) {
+__device__ __forceinline__ uint2 stage_pairs(uint2 raw, int lane, float& s, float& b) {
   using E = typename Mode::Elem;
   constexpr int kActiveLanes = G / 4;
-  float s = 0.0f;
-  float b = 0.0f;
   uint32_t p01 = 0;
   uint32_t p23 = 0;
   if (lane < kActiveLanes) {
@@ -115,7 +113,7 @@ __device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, 
     const float f1 = E::to_float(static_cast<unsigned short>(raw.x >> 16));
     const float f2 = E::to_float(static_cast<unsigned short>(raw.y & 0xffffu));
     const float f3 = E::to_float(static_cast<unsigned short>(raw.y >> 16));
-    s = (f0 + f1) + (f2 + f3);
+    s += (f0 + f1) + (f2 + f3);
     // This lane holds nibbles 4*(lane&1) + {0,1,2,3} of a word-row: positions 1 and 3 are odd.
     const uint32_t h0 = Mode::stage(f0, false, b);
     const uint32_t h1 = Mode::stage(f1, true, b);
@@ -128,15 +126,25 @@ __device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, 
   // the neighbour so each lane can write two finished (nibble i, nibble i+4) pairs.
   const bool odd_lane = (lane & 1) != 0;
   const uint32_t recv = __shfl_xor_sync(0xffffffffu, odd_lane ? p01 : p23, 1);
-  if (lane < kActiveLanes) {
-    uint2 staged;
-    if (!odd_lane) {
-      staged.x = __byte_perm(p01, recv, 0x5410);  // (a0, a4)
-      staged.y = __byte_perm(p01, recv, 0x7632);  // (a1, a5)
-    } else {
-      staged.x = __byte_perm(recv, p23, 0x5410);  // (a2, a6)
-      staged.y = __byte_perm(recv, p23, 0x7632);  // (a3, a7)
-    }
+  uint2 staged;
+  if (!odd_lane) {
+    staged.x = __byte_perm(p01, recv, 0x5410);  // (a0, a4)
+    staged.y = __byte_perm(p01, recv, 0x7632);  // (a1, a5)
+  } else {
+    staged.x = __byte_perm(recv, p23, 0x5410);  // (a2, a6)
+    staged.y = __byte_perm(recv, p23, 0x7632);  // (a3, a7)
+  }
+  return staged;
+}
+
+// Stages one group's activations into the warp's shared-memory buffer and returns S and B.
+template <int G, class Mode>
+__device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, int lane,
+                                                  float& s_out, float& b_out) {
+  float s = 0.0f;
+  float b = 0.0f;
+  const uint2 staged = stage_pairs<G, Mode>(raw, lane, s, b);
+  if (lane < G / 4) {
     sts64(act_addr + lane * 8, staged);
   }
   s_out = warp_sum(s);
@@ -375,101 +383,24 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
   return false;
 }
 
-// Shared-memory plan of the stream kernel, used by host and device alike.
-struct StreamSmem {
-  uint32_t barriers;  // offset of warp 0's barriers (8 bytes per stage)
-  uint32_t slots;     // offset of the per-warp partial-sum slots (2 x M_TILE x 128 floats each)
-  uint32_t acts;      // offset of the per-warp staged activations (M_TILE x G 16-bit values each)
-  uint32_t rings;     // offset of warp 0's ring (stages x packet)
-  uint32_t total;
-};
-__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int stages, int group,
-                                                       int m_tile) {
-  StreamSmem plan;
-  plan.barriers = 0;
-  plan.slots = ((static_cast<uint32_t>(warps) * stages * 8) + 127u) & ~127u;
-  plan.acts = plan.slots + (static_cast<uint32_t>(warps) * 2 * m_tile * kTileCols * 4);
-  plan.rings = plan.acts + (static_cast<uint32_t>(warps) * m_tile * group * 2);
-  plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * packet_stride(group));
-  return plan;
-}
-
-template <int G, int M_TILE, class Mode>
-__global__ void __launch_bounds__(512, 1)
-    w4a16_gemv_stream_kernel(const __grid_constant__ GemvParams p) {
-  using E = typename Mode::Elem;
-  extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kStageBytes = packet_stride(G);
-  constexpr int kSlotFloats = M_TILE * kTileCols;
-
-  const int lane = static_cast<int>(threadIdx.x) & 31;
-  const int warp = static_cast<int>(threadIdx.x) >> 5;
-  const int warps_per_cta = static_cast<int>(blockDim.x) >> 5;
+// ---------------------------------------------------------------------------------------------
+// The finish shared by the GEMV kernels, run by every warp of a CTA after the CTA-wide barrier that
+// ends the runs: adds the per-warp partial-sum slots of each tile in warp order, stores tiles
+// that lie wholly inside the CTA's packet range, hands tiles shared with neighbouring CTAs to the
+// global slot + ticket protocol, and (multi-GPU calls) signals and awaits exchange completion.
+// ---------------------------------------------------------------------------------------------
+// Warp u's slot for its first tile is head_slots + u * head_stride, the one for its last tile
+// tail_slots + u * tail_stride (strides in floats); each holds [ROWS][128] floats.
+template <int ROWS, class E>
+__device__ __forceinline__ void finish_cta(const GemvParams& p, const float* head_slots,
+                                           uint32_t head_stride, const float* tail_slots,
+                                           uint32_t tail_stride, int warp, int lane,
+                                           int warps_per_cta, int row_tile, int row0, int m_act) {
+  constexpr int M_TILE = ROWS;
+  constexpr int kSlotFloats = ROWS * kTileCols;
   const uint32_t cta = blockIdx.x;
-  const uint32_t v = (cta * warps_per_cta) + warp;
   const uint32_t workers = static_cast<uint32_t>(p.active_warps);
-  const bool active = v < workers;
-  const int row_tile = static_cast<int>(blockIdx.y);
-  const int row0 = row_tile * M_TILE;
-  const int m_act = (p.m - row0) < M_TILE ? (p.m - row0) : M_TILE;
   const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
-
-  const int stages = p.stages;
-  const StreamSmem plan = stream_smem_plan(warps_per_cta, stages, G, M_TILE);
-  const uint32_t smem_base = smem_addr(smem);
-  const uint32_t bar_addr = smem_base + plan.barriers + (warp * stages * 8);
-  const uint32_t act_addr = smem_base + plan.acts + (warp * M_TILE * G * 2);
-  const uint32_t ring_addr = smem_base + plan.rings + (warp * stages * kStageBytes);
-  float* slots = reinterpret_cast<float*>(smem + plan.slots);  // [warp][2][kSlotFloats]
-
-  const uint32_t p_begin = active ? run_begin(v, p) : 0;
-  const uint32_t p_end = active ? run_begin(v + 1, p) : 0;
-  const uint32_t first_tile = p_begin / num_groups;
-
-  trace_mark(0);
-  if (active) {
-    if (lane == 0) {
-      for (int s = 0; s < stages; ++s) {
-        mbar_init(bar_addr + (s * 8), 1);
-      }
-      mbar_init_fence();
-    }
-    __syncwarp();
-
-    float y[M_TILE][4];
-#pragma unroll
-    for (int m = 0; m < M_TILE; ++m) {
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        y[m][c] = 0.0f;
-      }
-    }
-    auto on_tile_done = [&](uint32_t tile, uint32_t first_pkt, uint32_t end_pkt) {
-      if ((end_pkt - first_pkt) == num_groups) {
-#pragma unroll
-        for (int m = 0; m < M_TILE; ++m) {
-          if (m < m_act) {
-            store_tile_row<E>(p, row0 + m, tile, lane, y[m]);
-          }
-        }
-        return;
-      }
-      float* slot = slots + (((warp * 2) + (tile == first_tile ? 0 : 1)) * kSlotFloats);
-#pragma unroll
-      for (int m = 0; m < M_TILE; ++m) {
-        reinterpret_cast<float4*>(slot + (m * kTileCols))[lane] =
-            make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
-      }
-    };
-    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, act_addr, row0, m_act,
-                                              p_begin, p_end, lane, y, on_tile_done);
-  } else {
-    pdl_launch_dependents();
-    pdl_wait_for_prerequisites();
-  }
-  trace_mark(3);
-  __syncthreads();
-  trace_mark(4);
 
   // ---- CTA-level finish ---------------------------------------------------------------------
   const uint32_t cta_first_run = cta * warps_per_cta;
@@ -503,8 +434,9 @@ __global__ void __launch_bounds__(512, 1)
     }
     for (uint32_t u = run_a; u <= run_b; ++u) {
       // the tile is run u's first tile exactly when the run starts inside it
-      const int which = run_begin(u, p) >= tile_lo ? 0 : 1;
-      const float* slot = slots + ((((u - cta_first_run) * 2) + which) * kSlotFloats);
+      const uint32_t local = u - cta_first_run;
+      const float* slot = run_begin(u, p) >= tile_lo ? head_slots + (local * head_stride)
+                                                     : tail_slots + (local * tail_stride);
 #pragma unroll
       for (int m = 0; m < M_TILE; ++m) {
         const float4 part = reinterpret_cast<const float4*>(slot + (m * kTileCols))[lane];
@@ -628,6 +560,106 @@ __global__ void __launch_bounds__(512, 1)
       }
     }
   }
+}
+
+// Shared-memory plan of the stream kernel, used by host and device alike.
+struct StreamSmem {
+  uint32_t barriers;  // offset of warp 0's barriers (8 bytes per stage)
+  uint32_t slots;     // offset of the per-warp partial-sum slots (2 x M_TILE x 128 floats each)
+  uint32_t acts;      // offset of the per-warp staged activations (M_TILE x G 16-bit values each)
+  uint32_t rings;     // offset of warp 0's ring (stages x packet)
+  uint32_t total;
+};
+__host__ __device__ inline StreamSmem stream_smem_plan(int warps, int stages, int group,
+                                                       int m_tile) {
+  StreamSmem plan;
+  plan.barriers = 0;
+  plan.slots = ((static_cast<uint32_t>(warps) * stages * 8) + 127u) & ~127u;
+  plan.acts = plan.slots + (static_cast<uint32_t>(warps) * 2 * m_tile * kTileCols * 4);
+  plan.rings = plan.acts + (static_cast<uint32_t>(warps) * m_tile * group * 2);
+  plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * packet_stride(group));
+  return plan;
+}
+
+template <int G, int M_TILE, class Mode>
+__global__ void __launch_bounds__(512, 1)
+    w4a16_gemv_stream_kernel(const __grid_constant__ GemvParams p) {
+  using E = typename Mode::Elem;
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kStageBytes = packet_stride(G);
+  constexpr int kSlotFloats = M_TILE * kTileCols;
+
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int warps_per_cta = static_cast<int>(blockDim.x) >> 5;
+  const uint32_t cta = blockIdx.x;
+  const uint32_t v = (cta * warps_per_cta) + warp;
+  const uint32_t workers = static_cast<uint32_t>(p.active_warps);
+  const bool active = v < workers;
+  const int row_tile = static_cast<int>(blockIdx.y);
+  const int row0 = row_tile * M_TILE;
+  const int m_act = (p.m - row0) < M_TILE ? (p.m - row0) : M_TILE;
+  const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
+
+  const int stages = p.stages;
+  const StreamSmem plan = stream_smem_plan(warps_per_cta, stages, G, M_TILE);
+  const uint32_t smem_base = smem_addr(smem);
+  const uint32_t bar_addr = smem_base + plan.barriers + (warp * stages * 8);
+  const uint32_t act_addr = smem_base + plan.acts + (warp * M_TILE * G * 2);
+  const uint32_t ring_addr = smem_base + plan.rings + (warp * stages * kStageBytes);
+  float* slots = reinterpret_cast<float*>(smem + plan.slots);  // [warp][2][kSlotFloats]
+
+  const uint32_t p_begin = active ? run_begin(v, p) : 0;
+  const uint32_t p_end = active ? run_begin(v + 1, p) : 0;
+  const uint32_t first_tile = p_begin / num_groups;
+
+  trace_mark(0);
+  if (active) {
+    if (lane == 0) {
+      for (int s = 0; s < stages; ++s) {
+        mbar_init(bar_addr + (s * 8), 1);
+      }
+      mbar_init_fence();
+    }
+    __syncwarp();
+
+    float y[M_TILE][4];
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        y[m][c] = 0.0f;
+      }
+    }
+    auto on_tile_done = [&](uint32_t tile, uint32_t first_pkt, uint32_t end_pkt) {
+      if ((end_pkt - first_pkt) == num_groups) {
+#pragma unroll
+        for (int m = 0; m < M_TILE; ++m) {
+          if (m < m_act) {
+            store_tile_row<E>(p, row0 + m, tile, lane, y[m]);
+          }
+        }
+        return;
+      }
+      float* slot = slots + (((warp * 2) + (tile == first_tile ? 0 : 1)) * kSlotFloats);
+#pragma unroll
+      for (int m = 0; m < M_TILE; ++m) {
+        reinterpret_cast<float4*>(slot + (m * kTileCols))[lane] =
+            make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
+      }
+    };
+    (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, act_addr, row0, m_act,
+                                              p_begin, p_end, lane, y, on_tile_done);
+  } else {
+    pdl_launch_dependents();
+    pdl_wait_for_prerequisites();
+  }
+  trace_mark(3);
+  __syncthreads();
+  trace_mark(4);
+
+  finish_cta<M_TILE, E>(p, slots, 2 * kSlotFloats, slots + kSlotFloats, 2 * kSlotFloats, warp, lane,
+                        warps_per_cta, row_tile, row0, m_act);
   trace_mark(5);
 }
 

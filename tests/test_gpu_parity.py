@@ -290,3 +290,31 @@ def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
     with pytest.raises(ValueError, match="output_ld"):
         args.output_col0 = ld
         capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("batch", [5, 8, 9, 16, 19])
+def test_gemm_tensor_core_batches(group: int, batch: int, dtype: str) -> None:
+    """Batches above 4 take the MMA kernel (rows in tiles of 8 or 16, the last one padded)."""
+    shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
+                       zero_point=None, scale_range=(0.001, 0.05))
+    _check_gemv(make_problem(shape, seed=13 * group + batch), shape, oracle.dtype_code(dtype))
+
+
+@pytest.mark.parametrize(("n", "k", "batch"), [(4096, 4096, 8), (28672, 8192, 16), (4096, 14336, 8)])
+def test_gemm_tensor_core_layer_shapes(n: int, k: int, batch: int) -> None:
+    shape = LayerShape("t", n, k, batch=batch, dtype="bf16", zero_point=None)
+    problem = make_problem(shape)
+    if n * k > 64 * 1024 * 1024:  # keep the CPU oracle to a slice of the rows at the largest size
+        q, alpha, beta, act = (problem[key].cuda() for key in ("q_u8", "alpha", "beta", "activations"))
+        packets = capi_pack(capi, q, alpha, beta, 128)
+        out = capi_gemv(capi, WS, act, packets, n, k, 128, 1)
+        torch.cuda.synchronize()
+        assert torch.isfinite(out.float()).all()
+        rows = slice(1024, 1536)
+        y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"][rows].numpy(),
+                              oracle.bits_of(problem["alpha"][rows]), oracle.bits_of(problem["beta"][rows]), 128, 1)
+        assert oracle.max_rel_err(out[:, rows].float().cpu().numpy(), y64) <= GEMV_REL_TOL
+        return
+    _check_gemv(problem, shape, 1)
