@@ -226,7 +226,7 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
     plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
-    // Register budget (accumulators for 8 tiles x rows) caps the CTA at 256 threads.
+    // The unit of work is a PAIR of warps per packet; `warps` counts pairs from here on.
     int warps = cfg.warps > 0 ? cfg.warps : (plan.m_tile == 8 ? 8 : 6);
     warps = warps > 8 ? 8 : warps;
     const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
@@ -389,7 +389,7 @@ int launch_mma(const GemvParams& params, const Plan& plan, uint8_t* staged, int 
   mma_params.base = params;
   mma_params.staged = staged;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
-  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, mma_params));
+  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 64), plan.smem_bytes, stream, mma_params));
   return FK_W4A16_OK;
 }
 

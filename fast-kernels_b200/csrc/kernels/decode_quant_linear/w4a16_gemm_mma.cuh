@@ -103,8 +103,17 @@ __device__ __forceinline__ void mma_word_pair(float (&d)[4], const NibblePairs& 
   mma_16816_f16(d, lo.p15, hi.p15, lo.p37, hi.p37, b.y, b.w);
 }
 
+// Two warps share every packet: warp `side` (0 / 1) of a pair owns columns 64 side .. 64 side + 63
+// (MMA tiles 4 side .. 4 side + 3). That halves the accumulator registers per thread, so that 16
+// warps fit on an SM -- with fewer, the schedulers run dry between MMAs. The pair owns one ring;
+// side 0's lane 0 issues the copies, and a 64-thread named barrier per packet hands a consumed
+// buffer back.
+__device__ __forceinline__ void pair_barrier(int pair) {
+  asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory");
+}
+
 template <int G, int MT, class Mode>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
     w4a16_gemm_mma_kernel(const __grid_constant__ MmaParams mp) {
   using E = typename Mode::Elem;
   using Geom = MmaGeom<G, MT>;
@@ -115,11 +124,13 @@ __global__ void __launch_bounds__(256, 1)
   const GemvParams& p = mp.base;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int pair = warp >> 1;
+  const int side = warp & 1;
   const int g = lane >> 2;
   const int t = lane & 3;
-  const int warps_per_cta = static_cast<int>(blockDim.x) >> 5;
-  const uint32_t v = (blockIdx.x * warps_per_cta) + warp;
-  const uint32_t workers = static_cast<uint32_t>(p.active_warps);
+  const int pairs_per_cta = static_cast<int>(blockDim.x) >> 6;
+  const uint32_t v = (blockIdx.x * pairs_per_cta) + pair;
+  const uint32_t workers = static_cast<uint32_t>(p.active_warps);  // here: number of pairs
   const bool active = v < workers;
   const int row_tile = static_cast<int>(blockIdx.y);
   const int row0 = row_tile * MT;
@@ -127,14 +138,14 @@ __global__ void __launch_bounds__(256, 1)
   const uint32_t num_groups = static_cast<uint32_t>(p.num_groups);
   const int stages = p.stages;
 
-  // shared memory: barriers | head slots [warp][MT][128] | rings
+  // shared memory: barriers | one slot per pair [MT][128] | rings
   const uint32_t smem_base = smem_addr(smem);
-  const uint32_t bar_addr = smem_base + (warp * stages * 8);
-  const uint32_t slots_off = ((static_cast<uint32_t>(warps_per_cta) * stages * 8) + 127u) & ~127u;
-  const uint32_t rings_off = slots_off + (static_cast<uint32_t>(warps_per_cta) * Geom::kSlotFloats * 4);
+  const uint32_t bar_addr = smem_base + (pair * stages * 8);
+  const uint32_t slots_off = ((static_cast<uint32_t>(pairs_per_cta) * stages * 8) + 127u) & ~127u;
+  const uint32_t rings_off = slots_off + (static_cast<uint32_t>(pairs_per_cta) * Geom::kSlotFloats * 4);
   float* head_slots = reinterpret_cast<float*>(smem + slots_off);
   const uint32_t ring_stride = static_cast<uint32_t>(stages) * Geom::kStageBytes;
-  const uint32_t ring_addr = smem_base + rings_off + (warp * ring_stride);
+  const uint32_t ring_addr = smem_base + rings_off + (pair * ring_stride);
   float* tail_slots = reinterpret_cast<float*>(smem + rings_off);
 
   const uint32_t p_begin = active ? run_begin(v, p) : 0;
@@ -142,15 +153,15 @@ __global__ void __launch_bounds__(256, 1)
   const uint32_t count = p_end - p_begin;
   const uint32_t first_tile = p_begin / num_groups;
   const uint8_t* staged = mp.staged + (static_cast<size_t>(row_tile) * num_groups * Geom::kActBytes);
+  const bool issuer = side == 0 && lane == 0;
 
   if (active) {
-    if (lane == 0) {
+    if (issuer) {
       for (int s = 0; s < stages; ++s) {
         mbar_init(bar_addr + (s * 8), 1);
       }
       mbar_init_fence();
     }
-    __syncwarp();
     const uint64_t weight_policy = l2_evict_first_policy();
     const uint64_t act_policy = l2_evict_last_policy();
 
@@ -176,7 +187,7 @@ __global__ void __launch_bounds__(256, 1)
                     bar_addr + (slot * 8), act_policy);
     };
     const uint32_t prefill = count < static_cast<uint32_t>(stages) ? count : stages;
-    if (lane == 0) {
+    if (issuer) {
       for (uint32_t j = 0; j < prefill; ++j) {
         issue_weights(j, static_cast<int>(j));
       }
@@ -184,7 +195,7 @@ __global__ void __launch_bounds__(256, 1)
     // Weights do not depend on earlier kernels in the stream; the staged activations do.
     pdl_launch_dependents();
     pdl_wait_for_prerequisites();
-    if (lane == 0) {
+    if (issuer) {
       for (uint32_t j = 0; j < prefill; ++j) {
         issue_acts(issue_group, static_cast<int>(j));
         issue_group = (issue_group + 1 == num_groups) ? 0 : issue_group + 1;
@@ -192,10 +203,11 @@ __global__ void __launch_bounds__(256, 1)
       issue_idx = prefill;
       issue_slot = (prefill == static_cast<uint32_t>(stages)) ? 0 : static_cast<int>(prefill);
     }
+    pair_barrier(pair);  // the partner may not wait on barriers that are not initialised yet
 
-    float y[8][H][4];
+    float y[4][H][4];
 #pragma unroll
-    for (int tile = 0; tile < 8; ++tile) {
+    for (int tile = 0; tile < 4; ++tile) {
 #pragma unroll
       for (int h = 0; h < H; ++h) {
 #pragma unroll
@@ -205,18 +217,18 @@ __global__ void __launch_bounds__(256, 1)
       }
     }
 
-    // y element (tile = 4 s + j, h, c): column 64 s + 4 (g + 8 (c >> 1)) + j, row 8 h + 2 t + (c & 1)
+    // y element (tile j, h, c): column 64 side + 4 (g + 8 (c >> 1)) + j, row 8 h + 2 t + (c & 1)
     auto on_tile_done = [&](uint32_t tile_index, uint32_t first_pkt, uint32_t end_pkt) {
       const bool full = (end_pkt - first_pkt) == num_groups;
-      float* slot = (tile_index == first_tile) ? head_slots + (warp * Geom::kSlotFloats)
-                                               : tail_slots + (warp * (ring_stride / 4));
+      float* slot = (tile_index == first_tile) ? head_slots + (pair * Geom::kSlotFloats)
+                                               : tail_slots + (pair * (ring_stride / 4));
 #pragma unroll
-      for (int tile = 0; tile < 8; ++tile) {
+      for (int tile = 0; tile < 4; ++tile) {
 #pragma unroll
         for (int h = 0; h < H; ++h) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const int col = (64 * (tile >> 2)) + (4 * (g + (8 * (c >> 1)))) + (tile & 3);
+            const int col = (64 * side) + (4 * (g + (8 * (c >> 1)))) + tile;
             const int row = (8 * h) + (2 * t) + (c & 1);
             if (!full) {
               slot[(row * kTileCols) + col] = y[tile][h][c];
@@ -245,14 +257,14 @@ __global__ void __launch_bounds__(256, 1)
     int slot = 0;
     uint32_t parity = 0;
     bool ok = true;
-    const uint32_t const_b_even = g == 0 ? Mode::kEvenConstB : (g == 1 ? Mode::kEvenConstS : 0u);
-    const uint32_t const_b_odd = g == 0 ? Mode::kOddConstB : (g == 1 ? Mode::kOddConstS : 0u);
+    const uint32_t const_even = g == 0 ? Mode::kEvenConstB : (g == 1 ? Mode::kEvenConstS : 0u);
+    const uint32_t const_odd = g == 0 ? Mode::kOddConstB : (g == 1 ? Mode::kOddConstS : 0u);
 
     for (uint32_t j = 0; j < count; ++j, ++pkt) {
       if (pkt == tile_end) {
         on_tile_done(tile_index, tile_first, pkt);
 #pragma unroll
-        for (int tile = 0; tile < 8; ++tile) {
+        for (int tile = 0; tile < 4; ++tile) {
 #pragma unroll
           for (int h = 0; h < H; ++h) {
 #pragma unroll
@@ -267,11 +279,11 @@ __global__ void __launch_bounds__(256, 1)
       }
       const uint32_t stage = ring_addr + (slot * Geom::kStageBytes);
       if (!mbar_wait_bounded(bar_addr + (slot * 8), parity)) {
-        ok = false;
+        ok = false;  // the partner times out on the same barrier, so both leave the loop here
         break;
       }
 
-      float acc[8][H][4];
+      float acc[4][H][4];
       float vacc[H][4];
 #pragma unroll
       for (int h = 0; h < H; ++h) {
@@ -279,44 +291,41 @@ __global__ void __launch_bounds__(256, 1)
         for (int c = 0; c < 4; ++c) {
           vacc[h][c] = 0.0f;
 #pragma unroll
-          for (int tile = 0; tile < 8; ++tile) {
+          for (int tile = 0; tile < 4; ++tile) {
             acc[tile][h][c] = 0.0f;
           }
         }
       }
 
-      const uint32_t w_base = stage + (t * Geom::kChunkPitch) + (g * 16);
+      const uint32_t w_base = stage + (t * Geom::kChunkPitch) + (g * 16) + (side * 256);
       const uint32_t a_base = stage + Geom::kActOffset + (g * Geom::kActPitch) + (t * 16);
-#pragma unroll
+#pragma unroll 2
       for (int b = 0; b < Geom::kChunkRows; ++b) {
         uint4 bq[H];
 #pragma unroll
         for (int h = 0; h < H; ++h) {
           bq[h] = lds128(a_base + (h * 8 * Geom::kActPitch) + (b * 64));
         }
+        const uint4 w_lo = lds128(w_base + (b * kTileCols * 4));
+        const uint4 w_hi = lds128(w_base + (b * kTileCols * 4) + 128);
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          const uint4 w_lo = lds128(w_base + (b * kTileCols * 4) + (s * 256));
-          const uint4 w_hi = lds128(w_base + (b * kTileCols * 4) + (s * 256) + 128);
+        for (int jj = 0; jj < 4; ++jj) {
+          const NibblePairs lo = Mode::unpack(word_of(w_lo, jj));
+          const NibblePairs hi = Mode::unpack(word_of(w_hi, jj));
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const NibblePairs lo = Mode::unpack(word_of(w_lo, jj));
-            const NibblePairs hi = Mode::unpack(word_of(w_hi, jj));
-#pragma unroll
-            for (int h = 0; h < H; ++h) {
-              mma_word_pair<Mode>(acc[(4 * s) + jj][h], lo, hi, bq[h]);
-            }
+          for (int h = 0; h < H; ++h) {
+            mma_word_pair<Mode>(acc[jj][h], lo, hi, bq[h]);
           }
         }
         // the all-constant column: row 0 of this MMA tile yields B, row 1 yields S
 #pragma unroll
         for (int h = 0; h < H; ++h) {
           if (Mode::kEvenNibblesBf16) {
-            mma_16816_bf16(vacc[h], const_b_even, 0u, const_b_even, 0u, bq[h].x, bq[h].z);
+            mma_16816_bf16(vacc[h], const_even, 0u, const_even, 0u, bq[h].x, bq[h].z);
           } else {
-            mma_16816_f16(vacc[h], const_b_even, 0u, const_b_even, 0u, bq[h].x, bq[h].z);
+            mma_16816_f16(vacc[h], const_even, 0u, const_even, 0u, bq[h].x, bq[h].z);
           }
-          mma_16816_f16(vacc[h], const_b_odd, 0u, const_b_odd, 0u, bq[h].y, bq[h].w);
+          mma_16816_f16(vacc[h], const_odd, 0u, const_odd, 0u, bq[h].y, bq[h].w);
         }
       }
 
@@ -328,44 +337,42 @@ __global__ void __launch_bounds__(256, 1)
         for (int h = 0; h < H; ++h) {
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            bias[h][e] = __shfl_sync(0xffffffffu, vacc[h][e], t);      // lane (g = 0, t)
-            sum[h][e] = __shfl_sync(0xffffffffu, vacc[h][e], 4 + t);   // lane (g = 1, t)
+            bias[h][e] = __shfl_sync(0xffffffffu, vacc[h][e], t);     // lane (g = 0, t)
+            sum[h][e] = __shfl_sync(0xffffffffu, vacc[h][e], 4 + t);  // lane (g = 1, t)
           }
         }
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
+        for (int half = 0; half < 2; ++half) {
+          const int col0 = (64 * side) + (4 * (g + (8 * half)));
+          const uint2 a_raw = lds64(stage + Geom::kScaleOffset + (col0 * 2));
+          const uint2 b_raw = lds64(stage + Geom::kScaleOffset + (kTileCols * 2) + (col0 * 2));
+          const unsigned short a_bits[4] = {
+              static_cast<unsigned short>(a_raw.x & 0xffffu), static_cast<unsigned short>(a_raw.x >> 16),
+              static_cast<unsigned short>(a_raw.y & 0xffffu), static_cast<unsigned short>(a_raw.y >> 16)};
+          const unsigned short b_bits[4] = {
+              static_cast<unsigned short>(b_raw.x & 0xffffu), static_cast<unsigned short>(b_raw.x >> 16),
+              static_cast<unsigned short>(b_raw.y & 0xffffu), static_cast<unsigned short>(b_raw.y >> 16)};
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            const int col0 = (64 * s) + (4 * (g + (8 * half)));
-            const uint2 a_raw = lds64(stage + Geom::kScaleOffset + (col0 * 2));
-            const uint2 b_raw = lds64(stage + Geom::kScaleOffset + (kTileCols * 2) + (col0 * 2));
-            const unsigned short a_bits[4] = {
-                static_cast<unsigned short>(a_raw.x & 0xffffu), static_cast<unsigned short>(a_raw.x >> 16),
-                static_cast<unsigned short>(a_raw.y & 0xffffu), static_cast<unsigned short>(a_raw.y >> 16)};
-            const unsigned short b_bits[4] = {
-                static_cast<unsigned short>(b_raw.x & 0xffffu), static_cast<unsigned short>(b_raw.x >> 16),
-                static_cast<unsigned short>(b_raw.y & 0xffffu), static_cast<unsigned short>(b_raw.y >> 16)};
+          for (int jj = 0; jj < 4; ++jj) {
+            const float alpha = E::to_float(a_bits[jj]);
+            const float beta = E::to_float(b_bits[jj]);
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const float alpha = E::to_float(a_bits[jj]);
-              const float beta = E::to_float(b_bits[jj]);
+            for (int h = 0; h < H; ++h) {
 #pragma unroll
-              for (int h = 0; h < H; ++h) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                  const int c = (2 * half) + e;
-                  float& out = y[(4 * s) + jj][h][c];
-                  out = fmaf(alpha, acc[(4 * s) + jj][h][c] - bias[h][e], out);
-                  out = fmaf(beta, sum[h][e], out);
-                }
+              for (int e = 0; e < 2; ++e) {
+                const int c = (2 * half) + e;
+                float& out = y[jj][h][c];
+                out = fmaf(alpha, acc[jj][h][c] - bias[h][e], out);
+                out = fmaf(beta, sum[h][e], out);
               }
             }
           }
         }
       }
 
-      __syncwarp();
-      if (lane == 0 && issue_idx < count) {
+      // Both warps are done with this buffer: hand it back to the copy engine.
+      pair_barrier(pair);
+      if (issuer && issue_idx < count) {
         proxy_fence_async();
         issue_weights(issue_idx, issue_slot);
         issue_acts(issue_group, issue_slot);
@@ -382,11 +389,14 @@ __global__ void __launch_bounds__(256, 1)
     if (ok) {
       on_tile_done(tile_index, tile_first, pkt);
     } else {
-      issue_idx = __shfl_sync(0xffffffffu, issue_idx, 0);
-      if (lane == 0) {
+      // A copy never landed: record it and give the copies still in flight a bounded chance to
+      // finish. Packets [pkt - p_begin, min(count, that + stages)) were issued.
+      if (issuer) {
         atomicExch(p.status, static_cast<int>(kStatusCopyWaitTimeout));
       }
-      for (uint32_t j = pkt - p_begin; j < issue_idx; ++j) {
+      uint32_t issued_end = (pkt - p_begin) + static_cast<uint32_t>(stages);
+      issued_end = issued_end < count ? issued_end : count;
+      for (uint32_t j = pkt - p_begin; j < issued_end; ++j) {
         (void)mbar_wait_bounded(bar_addr + (slot * 8), parity);
         if (++slot == stages) {
           slot = 0;
@@ -399,8 +409,10 @@ __global__ void __launch_bounds__(256, 1)
     pdl_wait_for_prerequisites();
   }
   __syncthreads();
-  finish_cta<MT, E>(p, head_slots, Geom::kSlotFloats, tail_slots, ring_stride / 4, warp, lane,
-                    warps_per_cta, row_tile, row0, m_act);
+  // Side-0 warps carry the finish (warp index = pair); side-1 warps only take part in its
+  // CTA-wide steps.
+  finish_cta<MT, E>(p, head_slots, Geom::kSlotFloats, tail_slots, ring_stride / 4,
+                    side == 0 ? pair : (1 << 20), lane, pairs_per_cta, row_tile, row0, m_act);
 }
 
 }  // namespace fk_w4a16

@@ -486,7 +486,9 @@ __device__ __forceinline__ void finish_cta(const GemvParams& p, const float* hea
         sum[m][c] = 0.0f;
       }
     }
-    constexpr int kBatch = 4;  // independent loads in flight per step; order of addition is fixed
+    // independent loads in flight per step (fewer for tall slots, to stay in registers); the order
+    // of addition is fixed either way
+    constexpr int kBatch = M_TILE <= 4 ? 4 : 1;
     for (uint32_t base = cta_a; base <= cta_b; base += kBatch) {
       float4 part[kBatch][M_TILE];
 #pragma unroll
