@@ -16,6 +16,7 @@
 #include "w4a16_common.cuh"
 #include "w4a16_gemv_stream.cuh"
 #include "w4a16_gemm_mma.cuh"
+#include "w4a16_gemv_cluster.cuh"
 #include "w4a16_prep.cuh"
 
 #ifndef FK_W4A16_VERSION
@@ -203,6 +204,7 @@ struct Plan {
   uint32_t total_packets = 0;
   size_t smem_bytes = 0;
   size_t scratch_bytes = 0;
+  int cluster_size = 1;       // > 1: the cluster kernel, one cluster of this many CTAs per tile
   bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
   size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
@@ -217,8 +219,16 @@ size_t mma_smem_bytes(int warps, int stages, int group, int mt) {
 
 // `sm_count` and `max_smem` describe the device; the plan is a pure function of its arguments
 // so that fk_w4a16_workspace_bytes() and fk_w4a16_gemv() always agree.
+bool cluster_mode_enabled() {
+  static const bool enabled = [] {
+    const char* value = std::getenv("FK_W4A16_CLUSTER");
+    return value == nullptr || std::atoi(value) != 0;
+  }();
+  return enabled;
+}
+
 Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
-               const LaunchConfig& cfg) {
+               const LaunchConfig& cfg, bool allow_cluster = false) {
   Plan plan;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
@@ -256,6 +266,45 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.m_tile = m_tile_for_batch(batch);
   plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const int stage_bytes = packet_stride(group_size);
+
+  // Four or more CTAs per tile: every tile is shared by several CTAs anyway, so give each tile a
+  // cluster of CTAs that finishes it through distributed shared memory. (Measured: a win for
+  // 32-tile layers with clusters of 4; with clusters of 3 the idle SMs cost more than the
+  // global-memory finish.)
+  const int tiles = n / kTileCols;
+  const int groups = k / group_size;
+  if (allow_cluster && cluster_mode_enabled() && cfg.ctas == 0 && tiles * 4 <= sm_count) {
+    int cluster = sm_count / tiles;
+    cluster = cluster > 8 ? 8 : cluster;
+    cluster = cluster > groups ? groups : cluster;
+    if (cluster >= 2) {
+      int want_warps = (groups + cluster - 1) / cluster;
+      const int warp_cap = cfg.warps > 0 ? cfg.warps : kMaxWarps;
+      want_warps = want_warps > warp_cap ? warp_cap : want_warps;
+      for (int warps = want_warps; warps >= 1; --warps) {
+        const int longest_run = (groups + (cluster * warps) - 1) / (cluster * warps);
+        int stages = cfg.stages > 0 ? cfg.stages : 3;
+        stages = stages > longest_run ? longest_run : stages;
+        const int floor_stages = longest_run < 2 ? 1 : 2;
+        for (; stages >= floor_stages; --stages) {
+          if (cluster_smem_plan(warps, stages, group_size, plan.m_tile).total <=
+              static_cast<uint32_t>(max_smem)) {
+            break;
+          }
+        }
+        if (stages >= floor_stages) {
+          plan.cluster_size = cluster;
+          plan.warps = warps;
+          plan.stages = stages;
+          plan.grid_x = tiles * cluster;
+          plan.active_warps = plan.grid_x * warps;
+          plan.smem_bytes = cluster_smem_plan(warps, stages, group_size, plan.m_tile).total;
+          plan.scratch_bytes = 0;
+          return plan;
+        }
+      }
+    }
+  }
 
   // Default: as many warps as fit with a two-deep ring each (more warps hide more latency than
   // deeper rings do), at most 16.
@@ -345,17 +394,28 @@ bool pdl_enabled() {
 
 template <class Params>
 cudaError_t launch_kernel(void (*kernel)(Params), dim3 grid, dim3 block, size_t smem,
-                          cudaStream_t stream, const Params& params) {
+                          cudaStream_t stream, const Params& params, int cluster_size = 1) {
   cudaLaunchConfig_t config{};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = &attribute;
-  config.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchAttribute attributes[2]{};
+  unsigned count = 0;
+  if (pdl_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  if (cluster_size > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = static_cast<unsigned>(cluster_size);
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
   return cudaLaunchKernelEx(&config, kernel, params);
 }
 
@@ -369,6 +429,17 @@ int launch_stream(const GemvParams& params, const Plan& plan, int max_smem, cuda
   FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
   FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params));
+  return FK_W4A16_OK;
+}
+
+template <int G, int M_TILE, class E>
+int launch_cluster(const GemvParams& params, const Plan& plan, int max_smem, cudaStream_t stream) {
+  auto kernel = w4a16_gemv_cluster_kernel<G, M_TILE, UnpackModeFor<E>>;
+  static std::once_flag optin_flags[kMaxDevices];
+  FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
+  const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
+  FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params,
+                            plan.cluster_size));
   return FK_W4A16_OK;
 }
 
@@ -589,15 +660,21 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
 
   DeviceInfo* info = nullptr;
   FK_TRY(device_info(&info));
-  const Plan plan =
+  // The workspace requirement is that of the packet-stream plan whichever kernel runs, so that
+  // fk_w4a16_workspace_bytes() is a safe answer for every option combination.
+  const Plan stream_plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  const Plan plan = args->local_signal != nullptr
+                        ? stream_plan
+                        : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
+                                    launch_config(), /*allow_cluster=*/true);
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
-  if (args->workspace_bytes < workspace_bytes_for(plan)) {
+  if (args->workspace_bytes < workspace_bytes_for(stream_plan)) {
     std::ostringstream oss;
     oss << "workspace_bytes=" << args->workspace_bytes << " is smaller than the required "
-        << workspace_bytes_for(plan);
+        << workspace_bytes_for(stream_plan);
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
   }
   const int num_tiles = n / kTileCols;
@@ -644,6 +721,12 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
     };
     return args->dtype == FK_W4A16_DTYPE_BF16 ? for_group_mt<BF16>(group_size, plan.m_tile, run)
                                               : for_group_mt<F16>(group_size, plan.m_tile, run);
+  }
+  if (plan.cluster_size > 1) {
+    return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
+      return launch_cluster<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
+                                                                                    max_smem, s);
+    });
   }
   return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
     return launch_stream<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan,
