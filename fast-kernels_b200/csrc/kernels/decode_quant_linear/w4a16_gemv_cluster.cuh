@@ -91,13 +91,12 @@ __global__ void __launch_bounds__(512, 1)
   float* slots = reinterpret_cast<float*>(smem + plan.slots);
   float* cta_sum = reinterpret_cast<float*>(smem + plan.cta_sum);
 
-  // This warp's share of the tile's groups: worker s of S = C * W, runs differ by at most one.
+  // This warp's share of the tile's groups: worker s of S = C * W takes
+  // groups [floor(s NG / S), floor((s + 1) NG / S)): lengths differ by at most one, evenly spread.
   const uint32_t workers = cluster_ctas * static_cast<uint32_t>(warps_per_cta);
   const uint32_t s = (rank * warps_per_cta) + warp;
-  const uint32_t base = num_groups / workers;
-  const uint32_t rem = num_groups % workers;
-  const uint32_t g_begin = (s * base) + (s < rem ? s : rem);
-  const uint32_t g_end = g_begin + base + (s < rem ? 1u : 0u);
+  const uint32_t g_begin = (s * num_groups) / workers;
+  const uint32_t g_end = ((s + 1) * num_groups) / workers;
 
   trace_mark(0);
   float y[M_TILE][4];

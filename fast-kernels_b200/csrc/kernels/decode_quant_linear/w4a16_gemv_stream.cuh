@@ -37,26 +37,33 @@ namespace fk_w4a16 {
 // records the global timer at a few milestones. Compiled out of the shipped library.
 #ifdef FK_W4A16_TRACE
 constexpr int kTraceSlots = 8;
-__device__ unsigned long long g_trace[148 * 16 * kTraceSlots];  // this header is one TU's
-__device__ __forceinline__ void trace_mark(int slot) {
+constexpr int kTraceLaunches = 16;  // launches are told apart by a host-side counter modulo this
+__device__ unsigned long long g_trace[kTraceLaunches * 148 * 16 * kTraceSlots];  // one TU's
+__device__ __forceinline__ void trace_mark_at(int launch, int slot) {
   if ((threadIdx.x & 31) == 0 && blockIdx.x < 148 && (threadIdx.x >> 5) < 16) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    g_trace[((blockIdx.x * 16) + (threadIdx.x >> 5)) * kTraceSlots + slot] = t;
+    const size_t base =
+        ((((static_cast<size_t>(launch) * 148) + blockIdx.x) * 16) + (threadIdx.x >> 5)) * kTraceSlots;
+    g_trace[base + slot] = t;
     if (slot == 0) {
       unsigned int smid;
       asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-      g_trace[((blockIdx.x * 16) + (threadIdx.x >> 5)) * kTraceSlots + 6] = smid;
+      g_trace[base + 6] = smid;
     }
   }
 }
+#define trace_mark(slot) trace_mark_at(p.trace_id, (slot))
 #else
-__device__ __forceinline__ void trace_mark(int) {}
+#define trace_mark(slot) ((void)0)
 #endif
 
 constexpr int kMaxPeers = 7;
 
 struct GemvParams {
+#ifdef FK_W4A16_TRACE
+  int trace_id;
+#endif
   const void* act;         // [m, k] 16-bit, row-major
   const uint8_t* packets;  // [num_tiles * num_groups, stride]
   void* out;               // [m, n] 16-bit, row-major
@@ -84,17 +91,33 @@ struct GemvParams {
   int active_warps;        // V: number of runs
   int stages;              // ring depth per warp
   uint32_t total_packets;  // num_tiles * num_groups
-  uint32_t run_base;       // total_packets / V
-  uint32_t run_rem;        // total_packets % V: the first run_rem runs hold run_base + 1 packets
+  // Runs: run v holds packets [floor(v T / V), floor((v + 1) T / V)) with T = total_packets --
+  // lengths differ by at most one and the longer runs are spread evenly over the CTAs.
+  uint32_t run_base;       // T / V
+  uint32_t run_rem;        // T % V
+  uint64_t run_magic;      // floor(2^40 / V) + 1: exact division of x < 2^24 by V (V <= 4096)
+  float run_inv;           // V / T, for the inverse map
 };
 
-__device__ __forceinline__ uint32_t run_begin(uint32_t v, const GemvParams& p) {
-  return (v * p.run_base) + (v < p.run_rem ? v : p.run_rem);
+// floor(x / V) for x < 2^24 (see run_magic).
+__device__ __forceinline__ uint32_t div_by_workers(uint32_t x, const GemvParams& p) {
+  return static_cast<uint32_t>((static_cast<uint64_t>(x) * p.run_magic) >> 40);
 }
-// Run that holds packet `pkt`.
+__device__ __forceinline__ uint32_t run_begin(uint32_t v, const GemvParams& p) {
+  return (v * p.run_base) + div_by_workers(v * p.run_rem, p);
+}
+// Run that holds packet `pkt`: an estimate from the reciprocal, corrected by at most a step or two.
 __device__ __forceinline__ uint32_t run_owner(uint32_t pkt, const GemvParams& p) {
-  const uint32_t split = p.run_rem * (p.run_base + 1);
-  return pkt < split ? pkt / (p.run_base + 1) : p.run_rem + ((pkt - split) / p.run_base);
+  const uint32_t last = static_cast<uint32_t>(p.active_warps) - 1;
+  uint32_t v = static_cast<uint32_t>(static_cast<float>(pkt) * p.run_inv);
+  v = v > last ? last : v;
+  while (v < last && run_begin(v + 1, p) <= pkt) {
+    ++v;
+  }
+  while (v > 0 && run_begin(v, p) > pkt) {
+    --v;
+  }
+  return v;
 }
 
 // Turns this lane's 4 consecutive raw activations of a group (`raw`; lanes >= G/4 hold nothing)

@@ -173,4 +173,26 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
   out[idx] = E::from_float(sum);
 }
 
+// Host-resident activations: copies `count` 16-byte units from mapped (pinned) host memory into
+// device memory. The loads cross PCIe before the kernel waits for the work ahead of it in the
+// stream -- which may still be reading `dst` -- so their latency hides behind that work's tail.
+struct StageHostParams {
+  const uint4* src;  // device-side address of mapped host memory
+  uint4* dst;
+  int count;
+};
+__global__ void __launch_bounds__(256) stage_host_activations_kernel(
+    const __grid_constant__ StageHostParams sp) {
+  const int i = static_cast<int>((blockIdx.x * blockDim.x) + threadIdx.x);
+  pdl_launch_dependents();
+  uint4 value = make_uint4(0u, 0u, 0u, 0u);
+  if (i < sp.count) {
+    value = __ldcv(sp.src + i);  // never from a cache: the host rewrites this memory between calls
+  }
+  pdl_wait_for_prerequisites();
+  if (i < sp.count) {
+    sp.dst[i] = value;
+  }
+}
+
 }  // namespace fk_w4a16

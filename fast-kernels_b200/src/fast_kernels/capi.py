@@ -76,6 +76,11 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
          _c_int, _c_int, _c_void_p],
     ),
+    "fk_w4a16_gemv_host": (
+        _c_int,
+        [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
+         _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
     "fk_w4a16_gemv_ex": (_c_int, [ctypes.POINTER(GemvArgs)]),
     "fk_w4a16_gemv_static": (
         _c_int,

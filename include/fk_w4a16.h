@@ -83,6 +83,21 @@ FK_W4A16_API int fk_w4a16_gemv(const void* activations, const void* packets, voi
                   size_t workspace_bytes, int batch, int n, int k, int group_size,
                   int packet_stride_bytes, int dtype, void* stream);
 
+/* fk_w4a16_gemv for callers whose activations and results live in HOST memory (no counterpart in
+ * the reference, whose ops take device pointers only): enqueues, on `stream`, the copy of
+ * activations[batch, k] from `host_activations` to `device_activations`, the GEMV into
+ * `device_output`, and the copy of output[batch, n] back to `host_output`. The two device buffers
+ * are caller-owned staging (batch*k and batch*n 16-bit elements) and hold the same data afterwards.
+ * Nothing synchronises: read `host_output` after synchronising `stream`.
+ * With pinned host memory that the device can address (cudaHostAlloc / cudaHostRegister; what
+ * torch's pin_memory() gives) no copy engine is involved: a small kernel pulls the activations over
+ * PCIe and the GEMV kernel itself stores each finished tile to `host_output` (set
+ * FK_W4A16_HOST_ZERO_COPY=0 to force plain copies). Pageable memory takes cudaMemcpyAsync. */
+FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* packets, void* host_output,
+                       void* device_activations, void* device_output, void* workspace,
+                       size_t workspace_bytes, int batch, int n, int k, int group_size,
+                       int packet_stride_bytes, int dtype, void* stream);
+
 /* The same GEMV with every option spelled out; fk_w4a16_gemv(...) is this call with the options
  * at their defaults. The options exist for layers that are sharded over the GPUs of one node
  * (no counterpart in the reference, which is single-GPU):

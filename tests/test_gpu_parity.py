@@ -248,6 +248,53 @@ def test_gemv_respects_the_stream() -> None:
     assert oracle.max_rel_err(out.float().cpu().numpy(), y64) <= GEMV_REL_TOL
 
 
+def test_gemv_host_buffers_match_device_call() -> None:
+    """fk_w4a16_gemv_host: pinned host activations in, pinned host result out, same bits as the
+    device-pointer call; nothing synchronises inside the call."""
+    lib = capi.load_library()
+    shape = LayerShape("t", 128 * 9, 128 * 7, batch=3, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=515)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    plain = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    host_in = problem["activations"].pin_memory()
+    host_out = torch.zeros((3, shape.n), dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.zeros_like(act)
+    dev_out = torch.zeros_like(plain)
+    ws = WS.get(capi, 3, shape.n, shape.k, 128)
+    capi.check(lib.fk_w4a16_gemv_host(host_in.data_ptr(), packets.data_ptr(), host_out.data_ptr(),
+                                      dev_in.data_ptr(), dev_out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                      3, shape.n, shape.k, 128, 8704, 1, stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(host_out, plain.cpu())
+    assert torch.equal(dev_in, act)
+    assert torch.equal(dev_out, plain)
+    # pageable host memory takes the copy path; same bits
+    paged_in = problem["activations"].clone()
+    paged_out = torch.zeros((3, shape.n), dtype=torch.bfloat16)
+    dev_in.zero_()
+    dev_out.zero_()
+    capi.check(lib.fk_w4a16_gemv_host(paged_in.data_ptr(), packets.data_ptr(), paged_out.data_ptr(),
+                                      dev_in.data_ptr(), dev_out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                      3, shape.n, shape.k, 128, 8704, 1, stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(paged_out, plain.cpu()) and torch.equal(dev_out, plain)
+    # back-to-back calls that reuse one staging buffer see their own activations
+    host_in2 = (problem["activations"] * 0.5).pin_memory()
+    host_out2 = torch.zeros_like(host_out).pin_memory()
+    for h_in, h_out in ((host_in, host_out), (host_in2, host_out2), (host_in, host_out)):
+        capi.check(lib.fk_w4a16_gemv_host(h_in.data_ptr(), packets.data_ptr(), h_out.data_ptr(),
+                                          dev_in.data_ptr(), dev_out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                          3, shape.n, shape.k, 128, 8704, 1, stream_ptr()))
+    torch.cuda.synchronize()
+    half = capi_gemv(capi, WS, act * 0.5, packets, shape.n, shape.k, 128, 1)
+    assert torch.equal(host_out, plain.cpu()) and torch.equal(host_out2, half.cpu())
+    with pytest.raises(ValueError, match="host_output"):
+        capi.check(lib.fk_w4a16_gemv_host(host_in.data_ptr(), packets.data_ptr(), None,
+                                          dev_in.data_ptr(), dev_out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                          3, shape.n, shape.k, 128, 8704, 1, stream_ptr()))
+
+
 def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
     """fk_w4a16_gemv_ex: fp32 partial outputs, a slice of a wider matrix, a second destination
     and the completion counters -- here with both destinations on this GPU."""
