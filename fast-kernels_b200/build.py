@@ -51,7 +51,7 @@ def build_library(force: bool = False) -> Path:
     """libfk_w4a16.so: every CUDA kernel plus the extern "C" entry points of include/fk_w4a16.h."""
     kernel_dir = CSRC / "kernels" / "decode_quant_linear"
     sources = sorted(kernel_dir.glob("*.cu"))
-    deps = sources + sorted(kernel_dir.glob("*.cuh")) + [REPO / "include" / "fk_w4a16.h"]
+    deps = sources + sorted(kernel_dir.glob("*.cuh")) + sorted(kernel_dir.glob("*.h")) + [REPO / "include" / "fk_w4a16.h"]
     target = LIB_DIR / "libfk_w4a16.so"
     if not force and _newer(target, deps):
         return target
@@ -60,6 +60,7 @@ def build_library(force: bool = False) -> Path:
     _run(
         [
             _nvcc(), *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+            "--threads", "0",
             "-Xptxas", "-v", f"-DFK_W4A16_VERSION=\"{VERSION}\"",
             "-I", REPO / "include", "-I", kernel_dir,
             "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",

@@ -18,6 +18,8 @@
 #include "w4a16_gemv_stream.cuh"
 #include "w4a16_gemm_mma.cuh"
 #include "w4a16_gemv_cluster.cuh"
+#include "w4a16_launch.h"
+#include "w4a16_tc5_plan.cuh"
 #include "w4a16_prep.cuh"
 
 #ifndef FK_W4A16_VERSION
@@ -166,8 +168,13 @@ int device_info(DeviceInfo** out) {
 }
 
 // ---- launch planning for the fused GEMV --------------------------------------------------
-constexpr size_t kTicketBytes = 256 * 1024;  // fixed ticket area at the start of a workspace
+// A caller-owned workspace starts with a fixed header that must be zero before the first call
+// and that every call leaves zero again: the ticket area, then the pair-exchange area (see
+// finish_cta). Per-plan scratch follows the header.
+constexpr size_t kTicketBytes = 256 * 1024;
 constexpr int kTicketCapacity = static_cast<int>(kTicketBytes / sizeof(int));
+constexpr size_t kExchangeBytes = 768 * 1024;
+constexpr size_t kHeaderBytes = kTicketBytes + kExchangeBytes;
 constexpr int kMaxWarps = 16;
 constexpr int kMaxStages = 8;
 
@@ -207,6 +214,7 @@ struct Plan {
   size_t scratch_bytes = 0;
   int cluster_size = 1;       // > 1: the cluster kernel, one cluster of this many CTAs per tile
   bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
+  bool tc5 = false;           // the tcgen05 kernel: `warps` counts warpgroups, rows in {1,2,4,8,16}
   size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
 
@@ -233,8 +241,7 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   Plan plan;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
-  const int mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH") > 0 ? env_int("FK_W4A16_MMA_MIN_BATCH") : 5;
-  if (batch >= mma_min_batch) {
+  if (batch > 4) {
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
     plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
@@ -362,8 +369,59 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   return plan;
 }
 
-size_t workspace_bytes_for(const Plan& plan) {
-  return kTicketBytes + ((plan.scratch_bytes + 255) & ~size_t{255}) +
+std::atomic<int> g_variant{-1};  // -1: not set, take FK_W4A16_TC5 from the environment
+bool tc5_enabled() {
+  const int variant = g_variant.load(std::memory_order_relaxed);
+  if (variant >= 0) {
+    return variant == 1;
+  }
+  static const bool from_env = env_int("FK_W4A16_TC5") != 0;
+  return from_env;
+}
+
+// Plan of the tcgen05 kernel: one run per warpgroup.
+Plan make_tc5_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
+                   const LaunchConfig& cfg) {
+  Plan plan;
+  plan.tc5 = true;
+  const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
+  plan.total_packets = static_cast<uint32_t>(total_packets);
+  plan.m_tile = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : (batch <= 8 ? 8 : 16)));
+  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
+  int groups = tc5_groups_for_rows(plan.m_tile);
+  if (cfg.warps > 0 && cfg.warps < groups) {
+    groups = cfg.warps;
+  }
+  int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+  ctas = ctas > 256 ? 256 : ctas;
+  long long workers = static_cast<long long>(ctas) * groups;
+  workers = workers > total_packets ? total_packets : workers;
+  groups = static_cast<int>((workers + ctas - 1) / ctas);
+  plan.warps = groups;
+  plan.grid_x = static_cast<int>((workers + groups - 1) / groups);
+  plan.active_warps = static_cast<int>(workers);
+  const long long longest_run = (total_packets + workers - 1) / workers;
+  int wanted = cfg.stages > 0 ? cfg.stages : 4;
+  wanted = wanted > kMaxStages ? kMaxStages : wanted;
+  wanted = wanted > longest_run ? static_cast<int>(longest_run) : wanted;
+  plan.stages = 0;
+  for (int candidate = wanted; candidate >= 1; --candidate) {
+    if (tc5_smem_plan(groups, candidate, group_size, plan.m_tile).total <= static_cast<uint32_t>(max_smem)) {
+      plan.stages = candidate;
+      break;
+    }
+  }
+  plan.smem_bytes = tc5_smem_plan(groups, plan.stages < 1 ? 1 : plan.stages, group_size, plan.m_tile).total;
+  // at most two CTAs per SM: each holds half of the SM's tensor memory
+  const size_t floor_bytes = (static_cast<size_t>(max_smem) / 3) + 1024;
+  plan.smem_bytes = plan.smem_bytes < floor_bytes ? floor_bytes : plan.smem_bytes;
+  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
+                       (plan.m_tile * kTileCols) * sizeof(float);
+  return plan;
+}
+
+size_t workspace_bytes_for(const Plan& plan, size_t header_bytes = kHeaderBytes) {
+  return header_bytes + ((plan.scratch_bytes + 255) & ~size_t{255}) +
          ((plan.staged_bytes + 255) & ~size_t{255});
 }
 
@@ -566,6 +624,14 @@ int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas) {
   return FK_W4A16_OK;
 }
 
+int fk_w4a16_set_variant(int variant) {
+  if (variant != FK_W4A16_VARIANT_AUTO && variant != FK_W4A16_VARIANT_TCGEN05) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown kernel variant");
+  }
+  g_variant.store(variant, std::memory_order_relaxed);
+  return FK_W4A16_OK;
+}
+
 int fk_w4a16_pack_packets(const void* q, const void* alpha, const void* beta, void* packets, int n,
                           int k, int group_size, int packet_stride_bytes, void* stream) {
   FK_TRY(check_dimensions(1, n, k, group_size));
@@ -625,22 +691,36 @@ size_t fk_w4a16_workspace_bytes(int batch, int n, int k, int group_size) {
   }
   const Plan plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  return workspace_bytes_for(plan);
+  const Plan tc5_plan =
+      make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  const size_t a = workspace_bytes_for(plan);
+  const size_t b = workspace_bytes_for(tc5_plan);
+  return a > b ? a : b;
 }
 
 int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   FK_TRY(check_pointer(workspace, "workspace", 256));
-  if (workspace_bytes < kTicketBytes) {
-    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "workspace is smaller than the ticket area");
+  if (workspace_bytes < kHeaderBytes) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "workspace is smaller than its fixed header");
   }
-  FK_TRY_CUDA(cudaMemsetAsync(workspace, 0, kTicketBytes, static_cast<cudaStream_t>(stream)));
+  FK_TRY_CUDA(cudaMemsetAsync(workspace, 0, kHeaderBytes, static_cast<cudaStream_t>(stream)));
   return FK_W4A16_OK;
 }
 
-int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
+namespace {
+// `with_exchange_area`: the workspace has the full header (ticket + pair-exchange areas); without
+// it -- the library's own static scratch -- the header is the ticket area alone.
+int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area);
+}  // namespace
+
+int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) { return gemv_impl(args, true); }
+
+namespace {
+int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   if (args == nullptr) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "args must not be null");
   }
+  const size_t header_bytes = with_exchange_area ? kHeaderBytes : kTicketBytes;
   const int batch = args->batch;
   const int n = args->n;
   const int k = args->k;
@@ -677,17 +757,21 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
   // fk_w4a16_workspace_bytes() is a safe answer for every option combination.
   const Plan stream_plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  const Plan plan = args->local_signal != nullptr
-                        ? stream_plan
-                        : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
-                                    launch_config(), /*allow_cluster=*/true);
+  const Plan plan =
+      tc5_enabled()
+          ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
+          : (args->local_signal != nullptr
+                 ? stream_plan
+                 : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
+                             launch_config(), /*allow_cluster=*/true));
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
-  if (args->workspace_bytes < workspace_bytes_for(stream_plan)) {
+  if (args->workspace_bytes < workspace_bytes_for(stream_plan, header_bytes) ||
+      args->workspace_bytes < workspace_bytes_for(plan, header_bytes)) {
     std::ostringstream oss;
     oss << "workspace_bytes=" << args->workspace_bytes << " is smaller than the required "
-        << workspace_bytes_for(stream_plan);
+        << workspace_bytes_for(stream_plan, header_bytes);
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
   }
   const int num_tiles = n / kTileCols;
@@ -705,7 +789,15 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
   params.out = args->output;
   params.tickets = static_cast<int*>(args->workspace);
   params.exit_count = static_cast<int*>(args->workspace) + (kTicketCapacity - 1);
-  params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(args->workspace) + kTicketBytes);
+  params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(args->workspace) + header_bytes);
+  // Pair exchange: one area of m_tile x 128 64-bit words per boundary between neighbouring CTAs.
+  params.exchange = nullptr;
+  if (with_exchange_area && !plan.tensor_cores && plan.cluster_size == 1 && plan.m_tile <= 4 &&
+      static_cast<size_t>(plan.row_tiles) * static_cast<size_t>(plan.grid_x) * plan.m_tile *
+              kTileCols * sizeof(unsigned long long) <= kExchangeBytes) {
+    params.exchange = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(args->workspace) +
+                                                            kTicketBytes);
+  }
   params.status = info->status_word;
   params.out_ld = out_ld;
   params.out_col0 = args->output_col0;
@@ -732,8 +824,26 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
                                       static_cast<double>(plan.total_packets));
   auto* s = static_cast<cudaStream_t>(args->stream);
   const int max_smem = info->max_smem_optin;
+  if (plan.tc5) {
+    if (plan.smem_bytes > static_cast<size_t>(max_smem)) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch needs more shared memory than the device has");
+    }
+    Tc5Launch launch{};
+    launch.group_size = group_size;
+    launch.rows = plan.m_tile;
+    launch.bf16 = args->dtype == FK_W4A16_DTYPE_BF16;
+    launch.grid_x = plan.grid_x;
+    launch.row_tiles = plan.row_tiles;
+    launch.groups = plan.warps;
+    launch.smem_bytes = plan.smem_bytes;
+    launch.max_smem = max_smem;
+    launch.programmatic = pdl_enabled();
+    launch.stream = s;
+    FK_TRY_CUDA(launch_tc5_kernel(params, launch));
+    return FK_W4A16_OK;
+  }
   if (plan.tensor_cores) {
-    uint8_t* staged = static_cast<uint8_t*>(args->workspace) + kTicketBytes +
+    uint8_t* staged = static_cast<uint8_t*>(args->workspace) + header_bytes +
                       ((plan.scratch_bytes + 255) & ~size_t{255});
     auto run = [&](auto g, auto mt, auto e) {
       return launch_mma<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan, staged,
@@ -753,6 +863,7 @@ int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) {
                                                                                  max_smem, s);
   });
 }
+}  // namespace
 
 int fk_w4a16_gemv(const void* activations, const void* packets, void* output, void* workspace,
                   size_t workspace_bytes, int batch, int n, int k, int group_size,
@@ -879,7 +990,7 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
 
   const Plan plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  const size_t need = workspace_bytes_for(plan);
+  const size_t need = workspace_bytes_for(plan, kTicketBytes);
   if (need > static_cast<size_t>(FK_W4A16_STATIC_SCRATCH_BYTES)) {
     std::ostringstream oss;
     oss << "this problem needs " << need << " bytes of scratch but the static array holds "
@@ -894,9 +1005,20 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
   }
   FK_TRY_CUDA(cudaMemsetAsync(scratch_address[device], 0, ticket_bytes,
                               static_cast<cudaStream_t>(stream)));
-  return fk_w4a16_gemv(activations, packets, output, scratch_address[device],
-                       FK_W4A16_STATIC_SCRATCH_BYTES, batch, n, k, group_size, packet_stride_bytes,
-                       dtype, stream);
+  fk_w4a16_gemv_args args{};
+  args.activations = activations;
+  args.packets = packets;
+  args.output = output;
+  args.workspace = scratch_address[device];
+  args.workspace_bytes = FK_W4A16_STATIC_SCRATCH_BYTES;
+  args.batch = batch;
+  args.n = n;
+  args.k = k;
+  args.group_size = group_size;
+  args.packet_stride_bytes = packet_stride_bytes;
+  args.dtype = dtype;
+  args.stream = stream;
+  return gemv_impl(&args, /*with_exchange_area=*/false);
 }
 
 int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,

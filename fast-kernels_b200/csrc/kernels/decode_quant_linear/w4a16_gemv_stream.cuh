@@ -59,6 +59,7 @@ __device__ __forceinline__ void trace_mark_at(int launch, int slot) {
 #endif
 
 constexpr int kMaxPeers = 7;
+constexpr uint32_t kExchangePresent = 0x50415254u;  // upper half of a filled pair-exchange word
 
 struct GemvParams {
 #ifdef FK_W4A16_TRACE
@@ -69,6 +70,9 @@ struct GemvParams {
   void* out;               // [m, n] 16-bit, row-major
   float* scratch;          // [row_tiles][ctas][2][M_TILE * 128] fp32
   int* tickets;            // [row_tiles][num_tiles], zero between calls
+  // Pair exchange, or null: [row_tiles][ctas][M_TILE * 128] 64-bit words, zero between calls; area
+  // c serves the tile that straddles the boundary between CTA c and CTA c + 1.
+  unsigned long long* exchange;
   int* status;             // device status word
   // Output placement. Element (row, col) of the result goes to out[row * out_ld + out_col0 + col]
   // and to the same offset in each of peer_out[0 .. num_peers) -- buffers of other GPUs mapped
@@ -200,6 +204,22 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
   store_tile_row_to<E>(p.out, p.out_f32, offset, lane, y);
   for (int peer = 0; peer < p.num_peers; ++peer) {
     store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, y);
+  }
+}
+
+// Stores one element of a finished tile locally and on every peer.
+template <class E>
+__device__ __forceinline__ void store_tile_element(const GemvParams& p, int row, uint32_t tile,
+                                                   int col, float value) {
+  const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
+                           (static_cast<long long>(tile) * kTileCols) + col;
+  for (int dest = -1; dest < p.num_peers; ++dest) {
+    void* out = dest < 0 ? p.out : p.peer_out[dest];
+    if (p.out_f32 != 0) {
+      static_cast<float*>(out)[offset] = value;
+    } else {
+      static_cast<unsigned short*>(out)[offset] = E::from_float(value);
+    }
   }
 }
 
@@ -480,7 +500,66 @@ __device__ __forceinline__ void finish_cta(const GemvParams& p, const float* hea
       continue;
     }
 
-    // The tile continues in a neighbouring CTA: publish, take a ticket, last one finishes.
+    const uint32_t cta_a = run_owner(tile_lo, p) / warps_per_cta;
+    const uint32_t cta_b = run_owner(tile_hi - 1, p) / warps_per_cta;
+
+    // The tile continues in ONE neighbouring CTA (the usual case when a CTA's share is at least
+    // a tile): each element is swapped, together with a "present" mark, into the boundary's word
+    // with one atomic. Whoever finds the neighbour's value there adds the two -- the sum of two
+    // floats does not depend on their order -- stores the output and clears the word; whoever
+    // finds it empty is done. One round trip to L2, no fence, no ticket, no second pass.
+    if (ROWS <= 4 && p.exchange != nullptr && cta_b == cta_a + 1) {
+      unsigned long long* area =
+          p.exchange + ((((static_cast<size_t>(row_tile) * gridDim.x) + cta_a) * kSlotFloats) + (lane * 4));
+      unsigned long long seen[M_TILE][4];
+#pragma unroll
+      for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const unsigned long long mine =
+              (static_cast<unsigned long long>(kExchangePresent) << 32) | __float_as_uint(sum[m][c]);
+          seen[m][c] = atomicExch(area + (m * kTileCols) + c, mine);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M_TILE; ++m) {
+        bool present[4];
+        bool all = true;
+        bool any = false;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          present[c] = static_cast<uint32_t>(seen[m][c] >> 32) == kExchangePresent;
+          all = all && present[c];
+          any = any || present[c];
+          sum[m][c] += __uint_as_float(static_cast<uint32_t>(seen[m][c]));
+        }
+        if (!any) {
+          continue;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (present[c]) {
+            area[(m * kTileCols) + c] = 0ull;
+          }
+        }
+        if (m >= m_act) {
+          continue;
+        }
+        if (all) {
+          store_tile_row<E>(p, row0 + m, tile, lane, sum[m]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (present[c]) {
+              store_tile_element<E>(p, row0 + m, tile, (lane * 4) + c, sum[m][c]);
+            }
+          }
+        }
+      }
+      continue;
+    }
+
+    // The tile is shared by three or more CTAs: publish, take a ticket, last one finishes.
     float* mine = scratch + (((static_cast<size_t>(cta) * 2) + (cta_begin >= tile_lo ? 0 : 1)) *
                              kSlotFloats);
 #pragma unroll
@@ -490,8 +569,6 @@ __device__ __forceinline__ void finish_cta(const GemvParams& p, const float* hea
     }
     __threadfence();
     __syncwarp();
-    const uint32_t cta_a = run_owner(tile_lo, p) / warps_per_cta;
-    const uint32_t cta_b = run_owner(tile_hi - 1, p) / warps_per_cta;
     int ticket = 0;
     if (lane == 0) {
       ticket = atomicAdd(&tickets[tile], 1);

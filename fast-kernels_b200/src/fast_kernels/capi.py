@@ -21,6 +21,8 @@ ERR_DEVICE_STATUS = -3
 
 DTYPE_F16 = 0
 DTYPE_BF16 = 1
+VARIANT_AUTO = 0
+VARIANT_TCGEN05 = 1
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfk_w4a16.so"
 
@@ -76,6 +78,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int,
          _c_int, _c_int, _c_void_p],
     ),
+    "fk_w4a16_set_variant": (_c_int, [_c_int]),
     "fk_w4a16_gemv_host": (
         _c_int,
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,

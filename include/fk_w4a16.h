@@ -191,6 +191,15 @@ FK_W4A16_API int fk_w4a16_device_status(int* status);
  * ring stages per warp (1..8, 0 = auto) and CTAs in the grid (0 = one per SM). Process-wide. */
 FK_W4A16_API int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas);
 
+/* Kernel variant of the fused GEMV, process-wide, for measurements and tests (no counterpart in
+ * the reference). AUTO picks per problem between the CUDA-core stream kernel, its cluster form and
+ * the mma.sync kernel (batch > 4); TCGEN05 forces the tcgen05 / tensor-memory kernel for every
+ * batch size -- same results, slower on decode shapes (its header says why). The environment
+ * variable FK_W4A16_TC5=1 selects TCGEN05 when this function was never called. */
+#define FK_W4A16_VARIANT_AUTO 0
+#define FK_W4A16_VARIANT_TCGEN05 1
+FK_W4A16_API int fk_w4a16_set_variant(int variant);
+
 #ifdef __cplusplus
 }
 #endif

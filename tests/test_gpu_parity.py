@@ -365,3 +365,32 @@ def test_gemm_tensor_core_layer_shapes(n: int, k: int, batch: int) -> None:
         assert oracle.max_rel_err(out[:, rows].float().cpu().numpy(), y64) <= GEMV_REL_TOL
         return
     _check_gemv(problem, shape, 1)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("batch", [1, 2, 3, 8, 16, 19])
+def test_tcgen05_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
+    """The tcgen05 / tensor-memory kernel (opt-in) meets the same bar as the default kernels."""
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
+    try:
+        shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
+                           zero_point=None)
+        _check_gemv(make_problem(shape, seed=4242 + batch), shape, oracle.dtype_code(dtype))
+        assert capi.device_status() == 0
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+
+
+def test_tcgen05_variant_on_a_layer_shape_and_bad_variant() -> None:
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
+    try:
+        for shape in (LayerShape("o_proj", 4096, 4096, dtype="bf16", zero_point=None),
+                      LayerShape("down_proj", 4096, 14336, batch=4, dtype="bf16", zero_point=None)):
+            _check_gemv(make_problem(shape, seed=99), shape, oracle.dtype_code("bf16"))
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+    with pytest.raises(ValueError, match="variant"):
+        capi.check(lib.fk_w4a16_set_variant(7))
