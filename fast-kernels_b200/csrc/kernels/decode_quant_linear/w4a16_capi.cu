@@ -241,7 +241,13 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   Plan plan;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
-  if (batch > 4) {
+  // Batches 3 and 4 also go to the tensor-core kernel when the layer is large enough to hide its
+  // activation prepass (measured on B200: 23 us against 35 on 28672 x 4096, 18.5 against 22 on
+  // 4096 x 14336, but 13 against 7.7 on 4096 x 4096).
+  const int mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH") > 0
+                                ? env_int("FK_W4A16_MMA_MIN_BATCH")
+                                : (total_packets >= 3072 ? 3 : 5);
+  if (batch >= mma_min_batch) {
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
     plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
@@ -282,7 +288,8 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   // global-memory finish.)
   const int tiles = n / kTileCols;
   const int groups = k / group_size;
-  if (allow_cluster && cluster_mode_enabled() && cfg.ctas == 0 && tiles * 4 <= sm_count) {
+  const int min_cluster = env_int("FK_W4A16_CLUSTER_MIN") > 0 ? env_int("FK_W4A16_CLUSTER_MIN") : 4;
+  if (allow_cluster && cluster_mode_enabled() && cfg.ctas == 0 && tiles * min_cluster <= sm_count) {
     int cluster = sm_count / tiles;
     cluster = cluster > 8 ? 8 : cluster;
     cluster = cluster > groups ? groups : cluster;
@@ -520,12 +527,18 @@ int launch_mma(const GemvParams& params, const Plan& plan, uint8_t* staged, int 
   auto kernel = w4a16_gemm_mma_kernel<G, MT, Mode>;
   static std::once_flag optin_flags[kMaxDevices];
   FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
-  // Prepass (ordinary launch: it must not start before earlier work on the stream is done with
-  // the staging area), then the GEMM with programmatic serialisation behind it.
-  const long long items = static_cast<long long>(plan.row_tiles) * params.num_groups * MT;
-  stage_activations_mma_kernel<G, Mode><<<static_cast<unsigned>((items + 3) / 4), 128, 0, stream>>>(
-      static_cast<const uint16_t*>(params.act), staged, params.m, params.k, params.num_groups, MT, items);
-  FK_TRY_CUDA(cudaGetLastError());
+  // Prepass, then the GEMM, both with programmatic serialisation (each waits inside the kernel).
+  StageMmaParams stage{};
+  stage.act = static_cast<const uint16_t*>(params.act);
+  stage.staged = staged;
+  stage.batch = params.m;
+  stage.k = params.k;
+  stage.num_groups = params.num_groups;
+  stage.mt = MT;
+  stage.total_items = static_cast<long long>(plan.row_tiles) * params.num_groups * MT;
+  FK_TRY_CUDA(launch_kernel(stage_activations_mma_kernel<G, Mode>,
+                            dim3(static_cast<unsigned>((stage.total_items + 3) / 4)), dim3(128), 0,
+                            stream, stage));
   MmaParams mma_params{};
   mma_params.base = params;
   mma_params.staged = staged;

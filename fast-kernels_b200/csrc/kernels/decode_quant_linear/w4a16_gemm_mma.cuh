@@ -50,25 +50,37 @@ __host__ __device__ constexpr int mma_act_pitch(int group) {
 
 // Prepass: act[batch, k] -> staged[row_tile][group][MT][pitch] in the pair formats of the unpack
 // mode, 16-byte unit (4 b + t) of a row holding word-row t * (G/32) + b. Rows beyond `batch` are
-// zero. One warp per (row tile, group, row).
+// zero. One warp per (row tile, group, row). Launched with programmatic stream serialisation: it
+// lets the GEMM behind it start its weight copies at once, and itself waits for the work ahead of
+// it (which may produce the activations, or still read the staging area) before it touches either.
+struct StageMmaParams {
+  const uint16_t* act;
+  uint8_t* staged;
+  int batch;
+  int k;
+  int num_groups;
+  int mt;
+  long long total_items;
+};
 template <int G, class Mode>
 __global__ void __launch_bounds__(128) stage_activations_mma_kernel(
-    const uint16_t* __restrict__ act, uint8_t* __restrict__ staged, int batch, int k, int num_groups,
-    int mt, long long total_items) {
+    const __grid_constant__ StageMmaParams sp) {
   constexpr int kChunkRows = G / 32;
   const int lane = static_cast<int>(threadIdx.x) & 31;
   const long long item = (static_cast<long long>(blockIdx.x) * 4) + (threadIdx.x >> 5);
-  if (item >= total_items) {
+  pdl_launch_dependents();
+  pdl_wait_for_prerequisites();
+  if (item >= sp.total_items) {
     return;
   }
-  const int m = static_cast<int>(item % mt);
-  const long long rest = item / mt;
-  const int group = static_cast<int>(rest % num_groups);
-  const long long row_tile = rest / num_groups;
-  const long long row = (row_tile * mt) + m;
+  const int m = static_cast<int>(item % sp.mt);
+  const long long rest = item / sp.mt;
+  const int group = static_cast<int>(rest % sp.num_groups);
+  const long long row_tile = rest / sp.num_groups;
+  const long long row = (row_tile * sp.mt) + m;
   uint2 raw = make_uint2(0u, 0u);
-  if (row < batch && lane < G / 4) {
-    raw = __ldg(reinterpret_cast<const uint2*>(act + (row * k) + (static_cast<long long>(group) * G)) + lane);
+  if (row < sp.batch && lane < G / 4) {
+    raw = __ldg(reinterpret_cast<const uint2*>(sp.act + (row * sp.k) + (static_cast<long long>(group) * G)) + lane);
   }
   float s = 0.0f;
   float b = 0.0f;
@@ -76,7 +88,7 @@ __global__ void __launch_bounds__(128) stage_activations_mma_kernel(
   if (lane < G / 4) {
     const int word_row = lane >> 1;
     const int unit = (4 * (word_row % kChunkRows)) + (word_row / kChunkRows);
-    uint8_t* dst = staged + (item * mma_act_pitch(G)) + (unit * 16) + ((lane & 1) * 8);
+    uint8_t* dst = sp.staged + (item * mma_act_pitch(G)) + (unit * 16) + ((lane & 1) * 8);
     *reinterpret_cast<uint2*>(dst) = pairs;
   }
 }
