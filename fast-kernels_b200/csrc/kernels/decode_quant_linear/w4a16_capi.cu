@@ -763,6 +763,9 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   if (args->local_signal != nullptr) {
     FK_TRY(check_pointer(args->local_signal, "local_signal", 4));
   }
+  if (args->residual != nullptr) {
+    FK_TRY(check_pointer(args->residual, "residual", 8));
+  }
 
   DeviceInfo* info = nullptr;
   FK_TRY(device_info(&info));
@@ -820,6 +823,7 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
     params.peer_out[peer] = args->peer_outputs[peer];
     params.peer_signal[peer] = args->peer_signals[peer];
   }
+  params.residual = args->residual;
   params.local_signal = args->local_signal;
   params.wait_value = args->wait_value;
   params.m = batch;

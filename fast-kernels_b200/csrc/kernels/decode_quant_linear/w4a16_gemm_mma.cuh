@@ -245,17 +245,7 @@ __global__ void __launch_bounds__(512, 1)
             if (!full) {
               slot[(row * kTileCols) + col] = y[tile][h][c];
             } else if (row < m_act) {
-              const long long offset = (static_cast<long long>(row0 + row) * p.out_ld) + p.out_col0 +
-                                       (static_cast<long long>(tile_index) * kTileCols) + col;
-              const float value = y[tile][h][c];
-              for (int dest = -1; dest < p.num_peers; ++dest) {
-                void* out = dest < 0 ? p.out : p.peer_out[dest];
-                if (p.out_f32 != 0) {
-                  static_cast<float*>(out)[offset] = value;
-                } else {
-                  static_cast<unsigned short*>(out)[offset] = E::from_float(value);
-                }
-              }
+              store_tile_element<E>(p, row0 + row, tile_index, col, y[tile][h][c]);
             }
           }
         }

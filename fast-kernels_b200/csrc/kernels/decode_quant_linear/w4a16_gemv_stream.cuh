@@ -82,6 +82,9 @@ struct GemvParams {
   int out_f32;
   int num_peers;
   void* peer_out[kMaxPeers];
+  // Optional fused residual add: a 16-bit matrix laid out like the output (same out_ld and
+  // out_col0); every output becomes round(y + residual), one rounding. May alias `out`.
+  const void* residual;
   // Exchange completion. When local_signal is set, the last CTA to leave adds 1 (system scope,
   // after all of this GPU's stores) to local_signal and to every peer_signal, then stays until
   // local_signal has reached wait_value -- i.e. until every GPU of the group has delivered.
@@ -201,9 +204,17 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
                                                const float (&y)[4]) {
   const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
                            (static_cast<long long>(tile) * kTileCols);
-  store_tile_row_to<E>(p.out, p.out_f32, offset, lane, y);
+  float v[4] = {y[0], y[1], y[2], y[3]};
+  if (p.residual != nullptr) {
+    const uint2 r = *(reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(p.residual) + offset) + lane);
+    v[0] += E::to_float(static_cast<unsigned short>(r.x & 0xffffu));
+    v[1] += E::to_float(static_cast<unsigned short>(r.x >> 16));
+    v[2] += E::to_float(static_cast<unsigned short>(r.y & 0xffffu));
+    v[3] += E::to_float(static_cast<unsigned short>(r.y >> 16));
+  }
+  store_tile_row_to<E>(p.out, p.out_f32, offset, lane, v);
   for (int peer = 0; peer < p.num_peers; ++peer) {
-    store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, y);
+    store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, v);
   }
 }
 
@@ -213,6 +224,9 @@ __device__ __forceinline__ void store_tile_element(const GemvParams& p, int row,
                                                    int col, float value) {
   const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
                            (static_cast<long long>(tile) * kTileCols) + col;
+  if (p.residual != nullptr) {
+    value += E::to_float(static_cast<const unsigned short*>(p.residual)[offset]);
+  }
   for (int dest = -1; dest < p.num_peers; ++dest) {
     void* out = dest < 0 ? p.out : p.peer_out[dest];
     if (p.out_f32 != 0) {

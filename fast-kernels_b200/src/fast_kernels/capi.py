@@ -57,6 +57,7 @@ class GemvArgs(ctypes.Structure):
         ("local_signal", _c_void_p),
         ("wait_value", ctypes.c_uint),
         ("stream", _c_void_p),
+        ("residual", _c_void_p),
     ]
 
 

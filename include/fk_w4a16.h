@@ -113,6 +113,7 @@ FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* pa
  *     reached wait_value (bounded: after about two seconds it gives up and sets the device status
  *     word). With wait_value = calls_so_far * group_size, kernels queued after this call on the
  *     same stream see every GPU's contribution. Leave local_signal NULL for single-GPU use.
+ *   - residual: see the field.
  * Zero-initialise the struct; unset fields then mean "default". */
 #define FK_W4A16_MAX_PEERS 7
 typedef struct fk_w4a16_gemv_args {
@@ -131,6 +132,10 @@ typedef struct fk_w4a16_gemv_args {
   unsigned int* local_signal;
   unsigned int wait_value;
   void* stream;
+  /* Fused residual add (a decoder's o_proj / down_proj): a 16-bit matrix laid out like `output`
+   * (same output_ld and output_col0), or NULL. Every output becomes round16(y + residual) -- or
+   * y + residual in fp32 with output_f32 -- with one rounding. May be the output buffer itself. */
+  const void* residual;
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 

@@ -339,6 +339,59 @@ def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
         capi.check(lib.fk_w4a16_gemv_ex(args))
 
 
+def _gemv_ex(lib, act, packets, out, shape, code, *, f32=0, residual=None):
+    args = capi.GemvArgs()
+    ws = WS.get(capi, shape.batch, shape.n, shape.k, shape.group_size)
+    args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), out.data_ptr()
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    args.batch, args.n, args.k, args.group_size = shape.batch, shape.n, shape.k, shape.group_size
+    args.packet_stride_bytes, args.dtype = 64 * shape.group_size + 512, code
+    args.output_f32 = f32
+    args.residual = 0 if residual is None else residual.data_ptr()
+    args.stream = stream_ptr()
+    capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
+@pytest.mark.parametrize(
+    ("n", "k", "batch", "dtype", "variant"),
+    [
+        (128 * 6, 128 * 5, 1, "bf16", 0),      # stream kernel, tiles shared between CTAs
+        (128 * 6, 128 * 5, 3, "fp16", 0),
+        (4096, 4096, 1, "bf16", 0),            # cluster kernel
+        (28672, 4096, 2, "bf16", 0),           # pair-exchange finish
+        (128 * 6, 128 * 5, 8, "bf16", 0),      # mma.sync kernel
+        (128 * 6, 128 * 5, 2, "bf16", 1),      # tcgen05 kernel
+    ],
+)
+def test_gemv_ex_fused_residual_add(n: int, k: int, batch: int, dtype: str, variant: int) -> None:
+    """residual: out = round16(y + residual) with ONE rounding, also in place."""
+    lib = capi.load_library()
+    shape = LayerShape("t", n, k, batch=batch, dtype=dtype, zero_point=None)
+    problem = make_problem(shape, seed=31 + batch)
+    code = oracle.dtype_code(dtype)
+    q, alpha, beta, act = (problem[key].cuda() for key in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    gen = torch.Generator().manual_seed(5)
+    residual = torch.randn((batch, n), generator=gen).to(act.dtype).cuda()
+    capi.check(lib.fk_w4a16_set_variant(variant))
+    try:
+        y32 = torch.empty((batch, n), dtype=torch.float32, device="cuda")
+        _gemv_ex(lib, act, packets, y32, shape, code, f32=1)
+        fused = torch.empty((batch, n), dtype=act.dtype, device="cuda")
+        _gemv_ex(lib, act, packets, fused, shape, code, residual=residual)
+        in_place = residual.clone()
+        _gemv_ex(lib, act, packets, in_place, shape, code, residual=in_place)
+        sum32 = torch.empty_like(y32)
+        _gemv_ex(lib, act, packets, sum32, shape, code, f32=1, residual=residual)
+        torch.cuda.synchronize()
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+    expected32 = y32 + residual.float()
+    assert torch.equal(sum32, expected32)
+    assert torch.equal(fused, expected32.to(act.dtype))
+    assert torch.equal(in_place, fused)
+
+
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("group", [32, 64, 128])
 @pytest.mark.parametrize("batch", [5, 8, 9, 16, 19])
