@@ -647,9 +647,12 @@ __device__ __forceinline__ void finish_cta(const GemvParams& p, const float* hea
 
   // ---- exchange completion (multi-GPU calls only) ------------------------------------------
   if (p.local_signal != nullptr) {
-    __threadfence_system();  // this thread's peer stores are performed before it counts as done
+    // One system-scope fence per CTA, by the thread that then counts the CTA as done: the barrier
+    // orders every thread's peer stores before it, and the fence is cumulative. (A fence in every
+    // thread costs tens of microseconds: system-scope fences of one SM do not overlap.)
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const unsigned int ctas_total = gridDim.x * gridDim.y;
       const int finished = atomicAdd(p.exit_count, 1);
       if (finished == static_cast<int>(ctas_total) - 1) {

@@ -58,8 +58,11 @@ def _rank_main(rank: int, world: int, port: int) -> None:
                     gathered = [torch.empty_like(bits) for _ in range(world)]
                     dist.all_gather(gathered, bits)
                     assert all(torch.equal(g, bits) for g in gathered), "ranks disagree"
-                if mode == "column":  # same local sums either way, only the transport differs
-                    assert torch.equal(results["nccl"], results["peer"])
+                # the two exchanges may run different local kernels (cluster vs stream finish), so
+                # their fp32 sums can differ in the last bit before the 16-bit rounding
+                pair_err = oracle.max_rel_err(results["peer"].float().cpu().numpy(),
+                                              results["nccl"].double().cpu().numpy())
+                assert pair_err <= 1e-2, (mode, dtype_name, pair_err)
         assert capi.device_status() == 0
     finally:
         dist.destroy_process_group()
