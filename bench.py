@@ -327,17 +327,20 @@ def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
     torch.cuda.synchronize(device)
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    host_begin = time.perf_counter()
     start.record()
     for _ in range(steps):
         step()
     stop.record()
+    host_seconds = time.perf_counter() - host_begin  # time the host spent enqueueing
     torch.cuda.synchronize(device)
     seconds = start.elapsed_time(stop) / 1e3
     # the results are real: the last call's output on the host equals the device tensor
     last_shape, _, _, last_out = layers.calls[-1]
     if not torch.equal(host_out[last_shape.name], last_out.cpu()):
         raise SystemExit("e2e: host result differs from the device result")
-    return {"seconds": seconds, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    return {"seconds": seconds, "host_seconds": host_seconds, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h}
 
 
 def _cpu_baseline_leg() -> dict:
@@ -554,6 +557,7 @@ def run_ours(args) -> int:
                 "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
                 "us_per_call": e2e_seconds * 1e6 / (e2e_steps * calls_per_step),
+                "host_enqueue_us_per_call": e2e["host_seconds"] * 1e6 / (e2e_steps * calls_per_step),
                 "steps": e2e_steps,
                 "api": "C ABI fk_w4a16_gemv_host per call: pinned host activations in, pinned host result out",
             },

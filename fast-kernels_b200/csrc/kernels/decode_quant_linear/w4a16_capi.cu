@@ -745,11 +745,20 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   FK_TRY(check_pointer(args->packets, "packets", 16));
   FK_TRY(check_pointer(args->output, "output", args->output_f32 != 0 ? 16 : 8));
   FK_TRY(check_pointer(args->workspace, "workspace", 256));
-  const long long out_ld = args->output_ld == 0 ? n : args->output_ld;
-  if (out_ld < n || args->output_col0 < 0 || args->output_col0 + n > out_ld ||
+  if (args->epilogue != FK_W4A16_EPILOGUE_NONE && args->epilogue != FK_W4A16_EPILOGUE_SILU_MUL) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown epilogue");
+  }
+  const bool gated = args->epilogue == FK_W4A16_EPILOGUE_SILU_MUL;
+  if (gated && (n % (2 * kTileCols)) != 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                "the SiLU-and-multiply epilogue needs n to be a multiple of 256 ([gate; up] halves of whole tiles)");
+  }
+  const int n_out = gated ? n / 2 : n;  // columns the caller receives
+  const long long out_ld = args->output_ld == 0 ? n_out : args->output_ld;
+  if (out_ld < n_out || args->output_col0 < 0 || args->output_col0 + n_out > out_ld ||
       (out_ld % 4) != 0 || (args->output_col0 % 4) != 0) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
-                "output_ld / output_col0 must place n columns inside a row, in multiples of 4");
+                "output_ld / output_col0 must place the output columns inside a row, in multiples of 4");
   }
   if (args->num_peers < 0 || args->num_peers > FK_W4A16_MAX_PEERS) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "num_peers must be between 0 and 7");
@@ -808,9 +817,28 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(args->workspace) + header_bytes);
   // Pair exchange: one area of m_tile x 128 64-bit words per boundary between neighbouring CTAs.
   params.exchange = nullptr;
-  if (with_exchange_area && !plan.tensor_cores && plan.cluster_size == 1 && plan.m_tile <= 4 &&
-      static_cast<size_t>(plan.row_tiles) * static_cast<size_t>(plan.grid_x) * plan.m_tile *
-              kTileCols * sizeof(unsigned long long) <= kExchangeBytes) {
+  params.gated = nullptr;
+  size_t exchange_bytes = static_cast<size_t>(plan.row_tiles) * static_cast<size_t>(plan.grid_x) *
+                          plan.m_tile * kTileCols * sizeof(unsigned long long);
+  const size_t gated_bytes =
+      gated ? static_cast<size_t>(batch) * (n / 2) * sizeof(unsigned long long) : 0;
+  const bool wants_exchange =
+      with_exchange_area && !plan.tensor_cores && !plan.tc5 && plan.cluster_size == 1 && plan.m_tile <= 4;
+  if (!wants_exchange || exchange_bytes + gated_bytes > kExchangeBytes) {
+    exchange_bytes = 0;  // split tiles take the ticket finish; the area is the epilogue's alone
+  }
+  if (gated) {
+    if (!with_exchange_area || gated_bytes > kExchangeBytes) {
+      std::ostringstream oss;
+      oss << "the SiLU-and-multiply epilogue needs " << gated_bytes
+          << " bytes of the workspace header's exchange area, which holds " << kExchangeBytes
+          << " (batch * n / 2 <= " << kExchangeBytes / sizeof(unsigned long long) << ")";
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+    }
+    params.gated = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(args->workspace) +
+                                                         kTicketBytes + exchange_bytes);
+  }
+  if (exchange_bytes > 0) {
     params.exchange = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(args->workspace) +
                                                             kTicketBytes);
   }

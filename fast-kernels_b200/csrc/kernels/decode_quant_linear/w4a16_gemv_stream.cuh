@@ -85,6 +85,11 @@ struct GemvParams {
   // Optional fused residual add: a 16-bit matrix laid out like the output (same out_ld and
   // out_col0); every output becomes round(y + residual), one rounding. May alias `out`.
   const void* residual;
+  // Optional fused SiLU-and-multiply over a stacked [gate; up] layer, or null: the output has n/2
+  // columns, out[j] = silu(y[j]) * y[j + n/2]. The two halves of a column are finished by
+  // different warps at different times; they meet in `gated` ([m][n/2] 64-bit words, zero between
+  // calls) exactly like the two halves of a split tile meet in `exchange`.
+  unsigned long long* gated;
   // Exchange completion. When local_signal is set, the last CTA to leave adds 1 (system scope,
   // after all of this GPU's stores) to local_signal and to every peer_signal, then stays until
   // local_signal has reached wait_value -- i.e. until every GPU of the group has delivered.
@@ -198,10 +203,76 @@ __device__ __forceinline__ void store_tile_row_to(void* out, int out_f32, long l
   *dst = packed;
 }
 
+constexpr uint32_t kGatedGate = 0x47415445u;  // upper half of a `gated` word holding a gate value
+constexpr uint32_t kGatedUp = 0x55505550u;    // ... holding an up value
+
+__device__ __forceinline__ float silu_times(float gate, float up) {
+  return (gate / (1.0f + __expf(-gate))) * up;
+}
+
+// SiLU-and-multiply meeting point for one element: swaps (value, kind) into the column's word;
+// returns true, with the finished product in `value` and the output column in `out_col`, when the
+// other half was already there (the word is cleared for the next call).
+__device__ __forceinline__ bool gated_meet(const GemvParams& p, int row, uint32_t tile, int col,
+                                           float& value, long long& out_col) {
+  const uint32_t half_tiles = static_cast<uint32_t>(p.num_tiles) >> 1;
+  const bool is_gate = tile < half_tiles;
+  out_col = (static_cast<long long>(is_gate ? tile : tile - half_tiles) * kTileCols) + col;
+  unsigned long long* word = p.gated + ((static_cast<long long>(row) * (p.n >> 1)) + out_col);
+  const unsigned long long mine =
+      (static_cast<unsigned long long>(is_gate ? kGatedGate : kGatedUp) << 32) | __float_as_uint(value);
+  const unsigned long long seen = atomicExch(word, mine);
+  if (static_cast<uint32_t>(seen >> 32) != (is_gate ? kGatedUp : kGatedGate)) {
+    return false;
+  }
+  const float other = __uint_as_float(static_cast<uint32_t>(seen));
+  value = is_gate ? silu_times(value, other) : silu_times(other, value);
+  *word = 0ull;
+  return true;
+}
+
+template <class E>
+__device__ __forceinline__ void store_element_at(const GemvParams& p, long long offset, float value) {
+  if (p.residual != nullptr) {
+    value += E::to_float(static_cast<const unsigned short*>(p.residual)[offset]);
+  }
+  for (int dest = -1; dest < p.num_peers; ++dest) {
+    void* out = dest < 0 ? p.out : p.peer_out[dest];
+    if (p.out_f32 != 0) {
+      static_cast<float*>(out)[offset] = value;
+    } else {
+      static_cast<unsigned short*>(out)[offset] = E::from_float(value);
+    }
+  }
+}
+
+// Stores one element of a finished tile locally and on every peer. Deliberately not inlined: it
+// is called from many places in every kernel instantiation and sits outside the streaming loop.
+template <class E>
+__device__ __noinline__ void store_tile_element(const GemvParams& p, int row, uint32_t tile,
+                                                   int col, float value) {
+  if (p.gated != nullptr) {
+    long long out_col;
+    if (gated_meet(p, row, tile, col, value, out_col)) {
+      store_element_at<E>(p, (static_cast<long long>(row) * p.out_ld) + p.out_col0 + out_col, value);
+    }
+    return;
+  }
+  store_element_at<E>(p, (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
+                             (static_cast<long long>(tile) * kTileCols) + col, value);
+}
+
 // Stores one row of a finished tile (this lane's 4 columns) locally and on every peer.
 template <class E>
 __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uint32_t tile, int lane,
                                                const float (&y)[4]) {
+  if (p.gated != nullptr) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      store_tile_element<E>(p, row, tile, (lane * 4) + c, y[c]);
+    }
+    return;
+  }
   const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
                            (static_cast<long long>(tile) * kTileCols);
   float v[4] = {y[0], y[1], y[2], y[3]};
@@ -215,25 +286,6 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
   store_tile_row_to<E>(p.out, p.out_f32, offset, lane, v);
   for (int peer = 0; peer < p.num_peers; ++peer) {
     store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, v);
-  }
-}
-
-// Stores one element of a finished tile locally and on every peer.
-template <class E>
-__device__ __forceinline__ void store_tile_element(const GemvParams& p, int row, uint32_t tile,
-                                                   int col, float value) {
-  const long long offset = (static_cast<long long>(row) * p.out_ld) + p.out_col0 +
-                           (static_cast<long long>(tile) * kTileCols) + col;
-  if (p.residual != nullptr) {
-    value += E::to_float(static_cast<const unsigned short*>(p.residual)[offset]);
-  }
-  for (int dest = -1; dest < p.num_peers; ++dest) {
-    void* out = dest < 0 ? p.out : p.peer_out[dest];
-    if (p.out_f32 != 0) {
-      static_cast<float*>(out)[offset] = value;
-    } else {
-      static_cast<unsigned short*>(out)[offset] = E::from_float(value);
-    }
   }
 }
 

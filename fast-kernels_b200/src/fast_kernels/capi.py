@@ -21,6 +21,8 @@ ERR_DEVICE_STATUS = -3
 
 DTYPE_F16 = 0
 DTYPE_BF16 = 1
+EPILOGUE_NONE = 0
+EPILOGUE_SILU_MUL = 1
 VARIANT_AUTO = 0
 VARIANT_TCGEN05 = 1
 
@@ -58,6 +60,7 @@ class GemvArgs(ctypes.Structure):
         ("wait_value", ctypes.c_uint),
         ("stream", _c_void_p),
         ("residual", _c_void_p),
+        ("epilogue", _c_int),
     ]
 
 

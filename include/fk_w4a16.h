@@ -113,9 +113,11 @@ FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* pa
  *     reached wait_value (bounded: after about two seconds it gives up and sets the device status
  *     word). With wait_value = calls_so_far * group_size, kernels queued after this call on the
  *     same stream see every GPU's contribution. Leave local_signal NULL for single-GPU use.
- *   - residual: see the field.
+ *   - residual, epilogue: see the fields.
  * Zero-initialise the struct; unset fields then mean "default". */
 #define FK_W4A16_MAX_PEERS 7
+#define FK_W4A16_EPILOGUE_NONE 0
+#define FK_W4A16_EPILOGUE_SILU_MUL 1
 typedef struct fk_w4a16_gemv_args {
   const void* activations;
   const void* packets;
@@ -136,6 +138,12 @@ typedef struct fk_w4a16_gemv_args {
    * (same output_ld and output_col0), or NULL. Every output becomes round16(y + residual) -- or
    * y + residual in fp32 with output_f32 -- with one rounding. May be the output buffer itself. */
   const void* residual;
+  /* Fused epilogue. FK_W4A16_EPILOGUE_SILU_MUL treats the layer as a stacked [gate; up] projection
+   * (a decoder's fused MLP input layer: rows 0 .. n/2-1 of W are the gate, the rest the up part):
+   * the output has n/2 columns, out[m, j] = silu(y[m, j]) * y[m, j + n/2], computed in fp32 from
+   * the unrounded sums and rounded once. n must be a multiple of 256; output_ld defaults to n/2;
+   * batch * n/2 may not exceed 98304 (the two halves of a column meet in the workspace header). */
+  int epilogue;
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 

@@ -392,6 +392,78 @@ def test_gemv_ex_fused_residual_add(n: int, k: int, batch: int, dtype: str, vari
     assert torch.equal(in_place, fused)
 
 
+@pytest.mark.parametrize(
+    ("n", "k", "batch", "dtype", "variant"),
+    [
+        (128 * 6, 128 * 5, 1, "bf16", 0),      # stream kernel, tiles shared between CTAs
+        (128 * 6, 128 * 5, 3, "fp16", 0),
+        (4096, 4096, 2, "bf16", 0),            # cluster kernel
+        (28672, 4096, 1, "bf16", 0),           # the 8B gate_up layer
+        (128 * 6, 128 * 5, 8, "bf16", 0),      # mma.sync kernel
+        (128 * 6, 128 * 5, 2, "fp16", 1),      # tcgen05 kernel
+    ],
+)
+def test_gemv_ex_fused_silu_mul(n: int, k: int, batch: int, dtype: str, variant: int) -> None:
+    """epilogue = SILU_MUL: out[:, j] = silu(y[:, j]) * y[:, j + n/2], from the unrounded sums."""
+    lib = capi.load_library()
+    shape = LayerShape("t", n, k, batch=batch, dtype=dtype, zero_point=None)
+    problem = make_problem(shape, seed=77 + batch)
+    code = oracle.dtype_code(dtype)
+    q, alpha, beta, act = (problem[key].cuda() for key in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    half = n // 2
+    capi.check(lib.fk_w4a16_set_variant(variant))
+    try:
+        outs = []
+        for _ in range(2):  # twice on one workspace: the meeting words clear themselves
+            out = torch.full((batch, half), float("nan"), dtype=act.dtype, device="cuda")
+            args = capi.GemvArgs()
+            ws = WS.get(capi, batch, n, k, 128)
+            args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), out.data_ptr()
+            args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+            args.batch, args.n, args.k, args.group_size = batch, n, k, 128
+            args.packet_stride_bytes, args.dtype = 8704, code
+            args.epilogue = capi.EPILOGUE_SILU_MUL
+            args.stream = stream_ptr()
+            capi.check(lib.fk_w4a16_gemv_ex(args))
+            torch.cuda.synchronize()
+            outs.append(out)
+        plain = capi_gemv(capi, WS, act, packets, n, k, 128, code)  # the workspace still works
+        torch.cuda.synchronize()
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+    y64 = oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"].numpy(),
+                          oracle.bits_of(problem["alpha"]), oracle.bits_of(problem["beta"]), 128, code)
+    gate, up = y64[:, :half], y64[:, half:]
+    want = gate / (1.0 + np.exp(-gate)) * up
+    got = outs[0].float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all(), "some outputs were never written"
+    assert oracle.max_rel_err(got, want) <= GEMV_REL_TOL
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert oracle.max_rel_err(plain.float().cpu().numpy(), y64) <= GEMV_REL_TOL
+
+
+def test_gemv_ex_silu_mul_refusals() -> None:
+    lib = capi.load_library()
+    shape = LayerShape("t", 128 * 3, 128, batch=1, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=1)
+    q, alpha, beta, act = (problem[key].cuda() for key in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    out = torch.empty((1, shape.n), dtype=act.dtype, device="cuda")
+    args = capi.GemvArgs()
+    ws = WS.get(capi, 1, shape.n, shape.k, 128)
+    args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), out.data_ptr()
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    args.batch, args.n, args.k, args.group_size = 1, shape.n, shape.k, 128
+    args.packet_stride_bytes, args.dtype = 8704, 1
+    args.epilogue = capi.EPILOGUE_SILU_MUL
+    with pytest.raises(ValueError, match="multiple of 256"):
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+    args.epilogue = 9
+    with pytest.raises(ValueError, match="epilogue"):
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("group", [32, 64, 128])
 @pytest.mark.parametrize("batch", [5, 8, 9, 16, 19])
