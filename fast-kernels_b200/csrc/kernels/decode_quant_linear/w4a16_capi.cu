@@ -237,7 +237,7 @@ bool cluster_mode_enabled() {
 }
 
 Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
-               const LaunchConfig& cfg, bool allow_cluster = false) {
+               const LaunchConfig& cfg, bool allow_cluster = false, bool cuda_cores_only = false) {
   Plan plan;
   const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
   plan.total_packets = static_cast<uint32_t>(total_packets);
@@ -247,7 +247,7 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   const int mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH") > 0
                                 ? env_int("FK_W4A16_MMA_MIN_BATCH")
                                 : (total_packets >= 3072 ? 3 : 5);
-  if (batch >= mma_min_batch) {
+  if (batch >= mma_min_batch && !(cuda_cores_only && batch <= 4)) {
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
     plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
@@ -782,13 +782,20 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   // fk_w4a16_workspace_bytes() is a safe answer for every option combination.
   const Plan stream_plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  const bool normalise = args->norm_weight != nullptr;
+  if (normalise) {
+    FK_TRY(check_pointer(args->norm_weight, "norm_weight", 16));
+    if (batch > 4 || !(args->norm_eps >= 0.0f)) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "the fused RMSNorm needs batch <= 4 and a non-negative norm_eps");
+    }
+  }
+  // The fused RMSNorm lives in the CUDA-core kernels (stream and cluster).
   const Plan plan =
-      tc5_enabled()
+      (tc5_enabled() && !normalise)
           ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
-          : (args->local_signal != nullptr
-                 ? stream_plan
-                 : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
-                             launch_config(), /*allow_cluster=*/true));
+          : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
+                      /*allow_cluster=*/args->local_signal == nullptr, /*cuda_cores_only=*/normalise);
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
@@ -852,6 +859,8 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
     params.peer_signal[peer] = args->peer_signals[peer];
   }
   params.residual = args->residual;
+  params.norm_weight = args->norm_weight;
+  params.norm_eps = args->norm_eps;
   params.local_signal = args->local_signal;
   params.wait_value = args->wait_value;
   params.m = batch;

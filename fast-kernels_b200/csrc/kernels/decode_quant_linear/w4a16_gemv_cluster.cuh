@@ -117,11 +117,21 @@ __global__ void __launch_bounds__(512, 1)
     __syncwarp();
     auto keep = [](uint32_t, uint32_t, uint32_t) {};
     const uint32_t first_pkt = tile * num_groups;
+    auto after_wait = [&](float (&inv_rms)[M_TILE]) {
+      if (p.norm_weight != nullptr) {
+        cta_inverse_rms<M_TILE, E>(p, row0, m_act, inv_rms);
+      }
+    };
     (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, act_addr, row0, m_act,
-                                              first_pkt + g_begin, first_pkt + g_end, lane, y, keep);
+                                              first_pkt + g_begin, first_pkt + g_end, lane, y, keep,
+                                              after_wait);
   } else {
     pdl_launch_dependents();
     pdl_wait_for_prerequisites();
+    if (p.norm_weight != nullptr) {  // the CTA-wide step of the fused RMSNorm needs every warp
+      float unused[M_TILE];
+      cta_inverse_rms<M_TILE, E>(p, row0, m_act, unused);
+    }
   }
 
   trace_mark(3);

@@ -90,6 +90,10 @@ struct GemvParams {
   // different warps at different times; they meet in `gated` ([m][n/2] 64-bit words, zero between
   // calls) exactly like the two halves of a split tile meet in `exchange`.
   unsigned long long* gated;
+  // Optional fused RMSNorm in front of the GEMV, or null: the activations the GEMV multiplies are
+  // round16(norm_weight[k] * round16(x[k] * rsqrt(mean_k(x^2) + norm_eps))) per row.
+  const void* norm_weight;  // [k] 16-bit
+  float norm_eps;
   // Exchange completion. When local_signal is set, the last CTA to leave adds 1 (system scope,
   // after all of this GPU's stores) to local_signal and to every peer_signal, then stays until
   // local_signal has reached wait_value -- i.e. until every GPU of the group has delivered.
@@ -289,15 +293,86 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
   }
 }
 
+// Fused RMSNorm, part one: 1 / rms of each of the CTA's rows, computed by the whole CTA (every
+// thread must call this once; it contains a CTA barrier). Sum of squares in a fixed order: per
+// thread over a strided share of the row, then the warp tree, then the warps in order.
+template <int M_TILE, class E>
+__device__ __forceinline__ void cta_inverse_rms(const GemvParams& p, int row0, int m_act,
+                                                float (&inv_rms)[M_TILE]) {
+  __shared__ float partial[16][M_TILE];
+  __shared__ float result[M_TILE];
+  const int lane = static_cast<int>(threadIdx.x) & 31;
+  const int warp = static_cast<int>(threadIdx.x) >> 5;
+  const int warps = static_cast<int>(blockDim.x) >> 5;
+  const int units = p.k >> 3;  // 16-byte units per row
+#pragma unroll
+  for (int m = 0; m < M_TILE; ++m) {
+    float acc = 0.0f;
+    if (m < m_act) {
+      const uint4* row = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(p.act) +
+                                                        (static_cast<size_t>(row0 + m) * p.k));
+      for (int i = static_cast<int>(threadIdx.x); i < units; i += static_cast<int>(blockDim.x)) {
+        const uint4 v = __ldg(row + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = E::to_float(static_cast<unsigned short>(w[j] & 0xffffu));
+          const float hi = E::to_float(static_cast<unsigned short>(w[j] >> 16));
+          acc = fmaf(lo, lo, acc);
+          acc = fmaf(hi, hi, acc);
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      partial[warp][m] = acc;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < M_TILE) {
+    float total = 0.0f;
+    for (int w = 0; w < warps; ++w) {
+      total += partial[w][threadIdx.x];
+    }
+    result[threadIdx.x] = rsqrtf((total / static_cast<float>(p.k)) + p.norm_eps);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < M_TILE; ++m) {
+    inv_rms[m] = result[m];
+  }
+}
+
+// Fused RMSNorm, part two: this lane's four raw activations -> the four normalised ones.
+template <class E>
+__device__ __forceinline__ uint2 normalise4(uint2 raw, uint2 weight, float inv_rms) {
+  auto one = [&](uint32_t x, uint32_t w) -> uint32_t {
+    const float scaled = E::to_float(static_cast<unsigned short>(x)) * inv_rms;
+    const float rounded = E::to_float(E::from_float(scaled));
+    return E::from_float(rounded * E::to_float(static_cast<unsigned short>(w)));
+  };
+  uint2 out;
+  out.x = one(raw.x & 0xffffu, weight.x & 0xffffu) | (one(raw.x >> 16, weight.x >> 16) << 16);
+  out.y = one(raw.y & 0xffffu, weight.y & 0xffffu) | (one(raw.y >> 16, weight.y >> 16) << 16);
+  return out;
+}
+
 // One warp's pass over packets [p_begin, p_end) of the tile-major packet stream, accumulating
 // `y` per tile and handing every finished tile run to on_tile_done(tile, first_pkt, end_pkt).
 // Returns false if a copy never arrived (the status word is set).
-template <int G, int M_TILE, class Mode, class TileDone>
+// `after_wait(inv_rms)` runs once, right after the kernel has waited for the work ahead of it in
+// the stream: the place for CTA-wide preparation that reads the activations (fused RMSNorm).
+struct NoPreparation {
+  template <int M_TILE>
+  __device__ __forceinline__ void operator()(float (&)[M_TILE]) const {}
+};
+template <int G, int M_TILE, class Mode, class TileDone, class AfterWait = NoPreparation>
 __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t ring_addr,
                                                    uint32_t bar_addr, uint32_t act_addr, int row0,
                                                    int m_act,
                                                    uint32_t p_begin, uint32_t p_end, int lane,
-                                                   float (&y)[M_TILE][4], TileDone&& on_tile_done) {
+                                                   float (&y)[M_TILE][4], TileDone&& on_tile_done,
+                                                   AfterWait&& after_wait = AfterWait{}) {
   using E = typename Mode::Elem;
   constexpr int kStride = packet_stride(G);
   constexpr int kQBytes = packet_q_bytes(G);
@@ -342,9 +417,17 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
   // scratch (all of which it may have written).
   pdl_launch_dependents();
   pdl_wait_for_prerequisites();
+  float inv_rms[M_TILE];
+#pragma unroll
+  for (int m = 0; m < M_TILE; ++m) {
+    inv_rms[m] = 1.0f;
+  }
+  after_wait(inv_rms);
+  const bool normalise = p.norm_weight != nullptr;
 
   // Activations: plain global loads (they stay in L2), one packet ahead, straight to registers.
   uint32_t act_group = first_group;
+  uint2 next_weight = make_uint2(0u, 0u);  // the group's RMSNorm weights, when fused
   auto load_activations = [&](uint2 (&dst)[M_TILE]) {
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
@@ -353,6 +436,10 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
         const size_t elem = (static_cast<size_t>(row0 + m) * p.k) + (act_group * G);
         dst[m] = __ldg(reinterpret_cast<const uint2*>(act_bytes + (elem * 2)) + lane);
       }
+    }
+    if (normalise && lane < kActLanes) {
+      next_weight = __ldg(reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(p.norm_weight) +
+                                                         (static_cast<size_t>(act_group) * G)) + lane);
     }
     act_group = (act_group + 1 == num_groups) ? 0 : act_group + 1;
   };
@@ -394,7 +481,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
     uint2 raw[M_TILE];
 #pragma unroll
     for (int m = 0; m < M_TILE; ++m) {
-      raw[m] = next_raw[m];
+      raw[m] = normalise ? normalise4<E>(next_raw[m], next_weight, inv_rms[m]) : next_raw[m];
     }
     if (j + 1 < count) {
       load_activations(next_raw);
@@ -819,11 +906,20 @@ __global__ void __launch_bounds__(512, 1)
             make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
       }
     };
+    auto after_wait = [&](float (&inv_rms)[M_TILE]) {
+      if (p.norm_weight != nullptr) {
+        cta_inverse_rms<M_TILE, E>(p, row0, m_act, inv_rms);
+      }
+    };
     (void)consume_packet_run<G, M_TILE, Mode>(p, ring_addr, bar_addr, act_addr, row0, m_act,
-                                              p_begin, p_end, lane, y, on_tile_done);
+                                              p_begin, p_end, lane, y, on_tile_done, after_wait);
   } else {
     pdl_launch_dependents();
     pdl_wait_for_prerequisites();
+    if (p.norm_weight != nullptr) {  // the CTA-wide step of the fused RMSNorm needs every warp
+      float unused[M_TILE];
+      cta_inverse_rms<M_TILE, E>(p, row0, m_act, unused);
+    }
   }
   trace_mark(3);
   __syncthreads();

@@ -61,6 +61,8 @@ class GemvArgs(ctypes.Structure):
         ("stream", _c_void_p),
         ("residual", _c_void_p),
         ("epilogue", _c_int),
+        ("norm_weight", _c_void_p),
+        ("norm_eps", ctypes.c_float),
     ]
 
 

@@ -113,7 +113,7 @@ FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* pa
  *     reached wait_value (bounded: after about two seconds it gives up and sets the device status
  *     word). With wait_value = calls_so_far * group_size, kernels queued after this call on the
  *     same stream see every GPU's contribution. Leave local_signal NULL for single-GPU use.
- *   - residual, epilogue: see the fields.
+ *   - residual, epilogue, norm_weight / norm_eps: see the fields.
  * Zero-initialise the struct; unset fields then mean "default". */
 #define FK_W4A16_MAX_PEERS 7
 #define FK_W4A16_EPILOGUE_NONE 0
@@ -144,6 +144,12 @@ typedef struct fk_w4a16_gemv_args {
    * the unrounded sums and rounded once. n must be a multiple of 256; output_ld defaults to n/2;
    * batch * n/2 may not exceed 98304 (the two halves of a column meet in the workspace header). */
   int epilogue;
+  /* Fused RMSNorm in front of the GEMV (a decoder's input_layernorm -> qkv, post_attention
+   * layernorm -> gate/up), or NULL: `activations` holds the un-normalised rows x, and the GEMV
+   * multiplies round16(norm_weight[k] * round16(x[k] * rsqrt(mean_k(x[k]^2) + norm_eps))) -- the
+   * two roundings of the usual module. norm_weight: [k] of the 16-bit type. batch <= 4. */
+  const void* norm_weight;
+  float norm_eps;
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 

@@ -443,6 +443,61 @@ def test_gemv_ex_fused_silu_mul(n: int, k: int, batch: int, dtype: str, variant:
     assert oracle.max_rel_err(plain.float().cpu().numpy(), y64) <= GEMV_REL_TOL
 
 
+@pytest.mark.parametrize(
+    ("n", "k", "batch", "dtype"),
+    [
+        (128 * 6, 128 * 5, 1, "bf16"),   # stream kernel
+        (128 * 6, 128 * 5, 3, "fp16"),
+        (4096, 4096, 2, "bf16"),         # cluster kernel
+        (28672, 4096, 1, "bf16"),        # the 8B gate_up layer behind its post-attention norm
+        (28672, 4096, 4, "bf16"),        # a batch the plain call would send to the mma.sync kernel
+    ],
+)
+def test_gemv_ex_fused_rmsnorm(n: int, k: int, batch: int, dtype: str) -> None:
+    """norm_weight: the GEMV multiplies round16(w * round16(x * rsqrt(mean(x^2) + eps)))."""
+    lib = capi.load_library()
+    shape = LayerShape("t", n, k, batch=batch, dtype=dtype, zero_point=None)
+    problem = make_problem(shape, seed=55 + batch)
+    code = oracle.dtype_code(dtype)
+    q, alpha, beta = (problem[key].cuda() for key in ("q_u8", "alpha", "beta"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    gen = torch.Generator().manual_seed(9)
+    torch_dtype_ = torch.bfloat16 if code else torch.float16
+    x = (3.0 * torch.randn((batch, k), generator=gen)).to(torch_dtype_)
+    weight = (1.0 + 0.1 * torch.randn((k,), generator=gen)).to(torch_dtype_)
+    eps = 1e-5
+    # the module's arithmetic, with the sum of squares in fp64
+    inv = 1.0 / np.sqrt((x.double().numpy() ** 2).mean(axis=1, keepdims=True) + eps)
+    x_norm = torch.from_numpy(x.float().numpy() * inv.astype(np.float32)).to(torch_dtype_)
+    normed = (weight.float() * x_norm.float()).to(torch_dtype_)
+    y64 = oracle.gemv_f64(oracle.bits_of(normed), problem["q_u8"].numpy(), oracle.bits_of(problem["alpha"]),
+                          oracle.bits_of(problem["beta"]), 128, code)
+
+    out = torch.full((batch, n), float("nan"), dtype=torch_dtype_, device="cuda")
+    x_dev, w_dev = x.cuda(), weight.cuda()
+    args = capi.GemvArgs()
+    ws = WS.get(capi, batch, n, k, 128)
+    args.activations, args.packets, args.output = x_dev.data_ptr(), packets.data_ptr(), out.data_ptr()
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    args.batch, args.n, args.k, args.group_size = batch, n, k, 128
+    args.packet_stride_bytes, args.dtype = 8704, code
+    args.norm_weight, args.norm_eps = w_dev.data_ptr(), eps
+    args.stream = stream_ptr()
+    capi.check(lib.fk_w4a16_gemv_ex(args))
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all()
+    assert oracle.max_rel_err(got, y64) <= GEMV_REL_TOL
+    # and it equals the unfused pipeline on the same normalised activations up to the rare element
+    # whose first rounding falls the other way (the sum of squares is added in another order)
+    unfused = capi_gemv(capi, WS, normed.cuda(), packets, n, k, 128, code)
+    torch.cuda.synchronize()
+    assert oracle.max_rel_err(got, unfused.double().cpu().numpy()) <= GEMV_REL_TOL
+    args.batch = 5
+    with pytest.raises(ValueError, match="RMSNorm"):
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
 def test_gemv_ex_silu_mul_refusals() -> None:
     lib = capi.load_library()
     shape = LayerShape("t", 128 * 3, 128, batch=1, dtype="bf16", zero_point=None)
