@@ -8,7 +8,7 @@ bench does the same with ``_make_case_inputs`` / ``_explicit_reference_output``
 functions from a reference checkout, calls them on CPU tensors, and stores inputs and outputs as
 bit patterns. It needs the checkout; the tests that consume the fixtures do not.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <path of the reference checkout>]
 
 Cases mirror the reference's six GPU tests (same shapes, same seed formulas, same value recipes;
 drawn with the CPU generator because CUDA draws cannot be reproduced off-GPU) plus three cases
