@@ -18,6 +18,7 @@
 #include "w4a16_gemv_stream.cuh"
 #include "w4a16_gemm_mma.cuh"
 #include "w4a16_gemv_cluster.cuh"
+#include "w4a16_gemv_wmma.cuh"
 #include "w4a16_launch.h"
 #include "w4a16_tc5_plan.cuh"
 #include "w4a16_prep.cuh"
@@ -214,6 +215,7 @@ struct Plan {
   size_t scratch_bytes = 0;
   int cluster_size = 1;       // > 1: the cluster kernel, one cluster of this many CTAs per tile
   bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
+  bool wmma = false;          // batch <= 2: the stream kernel with its inner product on mma.sync
   bool tc5 = false;           // the tcgen05 kernel: `warps` counts warpgroups, rows in {1,2,4,8,16}
   size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
@@ -332,11 +334,20 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
     }
   }
 
+  // Batches of 1 and 2 may take the warp-level MMA form of the stream kernel (opt-in while it is
+  // being measured): same plan, slightly larger ring stages.
+  plan.wmma = plan.m_tile <= 2 && env_int("FK_W4A16_WMMA") != 0;
+  const int ring_stage_bytes = plan.wmma ? wmma_stage_bytes(group_size) : stage_bytes;
+  auto smem_plan = [&](int w, int s) {
+    return plan.wmma ? wmma_smem_plan(w, s, group_size, plan.m_tile)
+                     : stream_smem_plan(w, s, group_size, plan.m_tile);
+  };
+
   // Default: as many warps as fit with a two-deep ring each (more warps hide more latency than
   // deeper rings do), at most 16.
   int warps = cfg.warps;
   if (warps <= 0) {
-    const int per_warp = (2 * stage_bytes) + (2 * plan.m_tile * kTileCols * 4) +
+    const int per_warp = (2 * ring_stage_bytes) + (2 * plan.m_tile * kTileCols * 4) +
                          (plan.m_tile * group_size * 2) + 16;
     warps = (max_smem - 256) / per_warp;
     warps = warps > kMaxWarps ? kMaxWarps : (warps < 1 ? 1 : warps);
@@ -363,14 +374,13 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   }
   int stages = 0;
   for (int candidate = wanted; candidate >= (longest_run < 2 ? 1 : 2); --candidate) {
-    if (stream_smem_plan(warps, candidate, group_size, plan.m_tile).total <=
-        static_cast<uint32_t>(max_smem)) {
+    if (smem_plan(warps, candidate).total <= static_cast<uint32_t>(max_smem)) {
       stages = candidate;
       break;
     }
   }
   plan.stages = stages;
-  plan.smem_bytes = stream_smem_plan(warps, stages < 1 ? 1 : stages, group_size, plan.m_tile).total;
+  plan.smem_bytes = smem_plan(warps, stages < 1 ? 1 : stages).total;
   plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
                        (plan.m_tile * kTileCols) * sizeof(float);
   return plan;
@@ -518,6 +528,21 @@ int launch_cluster(const GemvParams& params, const Plan& plan, int max_smem, cud
   FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params,
                             plan.cluster_size));
   return FK_W4A16_OK;
+}
+
+template <int G, int M_TILE, class E>
+int launch_wmma(const GemvParams& params, const Plan& plan, int max_smem, cudaStream_t stream) {
+  if constexpr (M_TILE <= 2) {
+    auto kernel = w4a16_gemv_wmma_kernel<G, M_TILE, UnpackModeFor<E>>;
+    static std::once_flag optin_flags[kMaxDevices];
+    FK_TRY(ensure_smem_optin(kernel, optin_flags, plan.smem_bytes, max_smem));
+    const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.row_tiles), 1);
+    FK_TRY_CUDA(launch_kernel(kernel, grid, dim3(plan.warps * 32), plan.smem_bytes, stream, params));
+    return FK_W4A16_OK;
+  } else {
+    (void)params; (void)plan; (void)max_smem; (void)stream;
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "the warp-level MMA kernel takes batches of 1 and 2");
+  }
 }
 
 template <int G, int MT, class E>
@@ -905,6 +930,11 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
     };
     return args->dtype == FK_W4A16_DTYPE_BF16 ? for_group_mt<BF16>(group_size, plan.m_tile, run)
                                               : for_group_mt<F16>(group_size, plan.m_tile, run);
+  }
+  if (plan.wmma) {
+    return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
+      return launch_wmma<decltype(g)::value, decltype(mt)::value, decltype(e)>(params, plan, max_smem, s);
+    });
   }
   if (plan.cluster_size > 1) {
     return dispatch(group_size, plan.m_tile, args->dtype, [&](auto g, auto mt, auto e) {
