@@ -3,7 +3,11 @@
 // but the 512 mixed-precision FMAs of a packet become 64 mma.sync.m16n8k16 -- the streaming phase
 // of the CUDA-core kernel is bound by instruction issue (1150 warp instructions per packet), and
 // an MMA mixed into a stream of ALU work costs 3-5 issue slots where the eight FMAs it replaces
-// cost eight.
+// cost eight (microbenchmark: 8 mma.sync + 64 independent LOP3 per iteration).
+//
+// Outcome (B200, measured): same results as the CUDA-core kernel, and slower -- 28672 x 4096 at
+// batch 1: 17.3 us against 15.3 on the same box; 6144 x 4096: 7.5 against 6.8 -- so it is opt-in
+// (FK_W4A16_WMMA=1) and the FMA kernel stays the default for batches 1 and 2.
 //
 // Operand mapping (that of w4a16_gemm_mma.cuh, one warp covering both column halves): A = weights
 // (16 output columns x 16 k), B = activations (16 k x 8 "batch" columns, of which only the first

@@ -574,3 +574,17 @@ def test_tcgen05_variant_on_a_layer_shape_and_bad_variant() -> None:
         capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
     with pytest.raises(ValueError, match="variant"):
         capi.check(lib.fk_w4a16_set_variant(7))
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("batch", [1, 2])
+def test_warp_mma_variant_matches_the_oracle(group: int, batch: int, dtype: str, monkeypatch) -> None:
+    """FK_W4A16_WMMA=1: the stream kernel with its inner product on mma.sync (batches 1 and 2)."""
+    monkeypatch.setenv("FK_W4A16_WMMA", "1")
+    shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
+                       zero_point=None)
+    _check_gemv(make_problem(shape, seed=777 + batch), shape, oracle.dtype_code(dtype))
+    big = LayerShape("gate_up", 28672, 4096, batch=batch, dtype=dtype, zero_point=None)
+    if group == 128:
+        _check_gemv(make_problem(big, seed=778), big, oracle.dtype_code(dtype))
