@@ -284,16 +284,21 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
   const int stage_bytes = packet_stride(group_size);
 
-  // Four or more CTAs per tile: every tile is shared by several CTAs anyway, so give each tile a
-  // cluster of CTAs that finishes it through distributed shared memory. (Measured: a win for
-  // 32-tile layers with clusters of 4; with clusters of 3 the idle SMs cost more than the
-  // global-memory finish.)
+  // Two or more CTAs per tile: every tile is shared by several CTAs anyway, so give each tile a
+  // cluster of CTAs that finishes it through distributed shared memory. The cluster size is the
+  // largest power of two that fits (#SM / tiles, at most 8): clusters of 3 do not pack into the
+  // GPCs one CTA per SM and run in two waves (6144 x 4096: 9.4 us with 3, 5.7 with 2, 6.8 on the
+  // stream kernel), and the idle SMs of a power-of-two grid cost less than the global-memory
+  // finish even on large layers (8192 x 8192: 10.3 against 12.6 us; 8192 x 28672: 25.7 / 26.2).
   const int tiles = n / kTileCols;
   const int groups = k / group_size;
-  const int min_cluster = env_int("FK_W4A16_CLUSTER_MIN") > 0 ? env_int("FK_W4A16_CLUSTER_MIN") : 4;
+  const int min_cluster = env_int("FK_W4A16_CLUSTER_MIN") > 0 ? env_int("FK_W4A16_CLUSTER_MIN") : 2;
   if (allow_cluster && cluster_mode_enabled() && cfg.ctas == 0 && tiles * min_cluster <= sm_count) {
     int cluster = sm_count / tiles;
-    cluster = cluster > 8 ? 8 : cluster;
+    cluster = cluster >= 8 ? 8 : (cluster >= 4 ? 4 : 2);
+    if (env_int("FK_W4A16_CLUSTER_SIZE") > 0) {
+      cluster = env_int("FK_W4A16_CLUSTER_SIZE");
+    }
     cluster = cluster > groups ? groups : cluster;
     if (cluster >= 2) {
       int want_warps = (groups + cluster - 1) / cluster;
