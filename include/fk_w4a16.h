@@ -203,7 +203,9 @@ FK_W4A16_API int fk_w4a16_cublaslt_matmul(const void* activations, const void* w
                              int k, int dtype, void* stream);
 
 /* Reads (and clears) the device status word of the current device into *status (host pointer):
- * 0 = no device-side wait ever timed out. Synchronises the device. */
+ * 0 = no device-side wait ever timed out. Synchronises the device. After a non-zero status the
+ * outputs of the calls since the last check are undefined and their workspaces may hold
+ * half-finished split-K state: zero them again (fk_w4a16_workspace_init) before reuse. */
 FK_W4A16_API int fk_w4a16_device_status(int* status);
 
 /* Launch-shape knobs of the fused GEMV, for tuning and tests: warps per CTA (1..16, 0 = auto),
