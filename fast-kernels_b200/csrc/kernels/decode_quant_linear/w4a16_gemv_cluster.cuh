@@ -5,9 +5,12 @@
 // ticket, a second round of loads -- three dependent L2 round trips, 2-3 us at the end of a 5-10 us
 // kernel. Here one thread-block CLUSTER owns a whole tile instead: its C CTAs x W warps split the
 // tile's K/G packets into contiguous runs (same warp routine, same rings and bulk copies), each
-// CTA adds its warps' sums in shared memory, and rank 0 of the cluster adds the C per-CTA sums
-// through distributed shared memory in rank order and stores the outputs. No scratch, no
-// atomics, two cluster barriers; summation order is fixed, so results are bit-reproducible.
+// CTA adds its warps' sums in shared memory and PUSHES the result into rank 0's shared memory
+// (st.async through distributed shared memory, counted by an mbarrier there), after which it is
+// free to leave; rank 0 waits for the C - 1 deliveries, adds the per-CTA sums in rank order and
+// stores the outputs. No scratch, no atomics, one split cluster barrier (arrive at kernel start,
+// wait before the push: it only guards the mbarrier's initialisation); summation order is fixed,
+// so results are bit-reproducible.
 // C = floor(#SM / tiles) (2..8), so 128-144 of the 148 SMs stream -- the few idle SMs cost less
 // than the global finish did.
 #pragma once
@@ -31,32 +34,42 @@ __device__ __forceinline__ uint32_t cluster_index() {
   asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_barrier() {
+__device__ __forceinline__ void cluster_barrier_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_barrier_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// 128-bit load from the same shared-memory offset in CTA `rank` of this cluster.
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t rank) {
+// Address of the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(remote)
-               : "memory");
-  return v;
+  return remote;
 }
-
-// Shared memory: barriers | per-warp slots [W][M_TILE][128] | CTA sum [M_TILE][128] | per-warp
-// activation buffers | rings.
+// 16 bytes from registers into another CTA's shared memory; the mbarrier there (also a cluster
+// address) counts the bytes when they have landed.
+__device__ __forceinline__ void st_async_f4(uint32_t remote_addr, float4 v, uint32_t remote_bar) {
+  asm volatile(
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1,%2,%3,%4}, [%5];" ::"r"(
+          remote_addr),
+      "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)),
+      "r"(__float_as_uint(v.w)), "r"(remote_bar)
+      : "memory");
+}
+// Shared memory: ring barriers + the delivery barrier | per-warp slots [W][M_TILE][128] | CTA sum
+// [M_TILE][128] | delivered sums [8][M_TILE][128] (used in rank 0) | per-warp activation buffers |
+// rings.
+constexpr int kMaxClusterCtas = 8;
 struct ClusterSmem {
-  uint32_t slots, cta_sum, acts, rings, total;
+  uint32_t recv_bar, slots, cta_sum, recv, acts, rings, total;
 };
 __host__ __device__ inline ClusterSmem cluster_smem_plan(int warps, int stages, int group, int m_tile) {
   ClusterSmem plan;
-  plan.slots = ((static_cast<uint32_t>(warps) * stages * 8) + 127u) & ~127u;
+  plan.recv_bar = static_cast<uint32_t>(warps) * stages * 8;
+  plan.slots = (plan.recv_bar + 8u + 127u) & ~127u;
   plan.cta_sum = plan.slots + (static_cast<uint32_t>(warps) * m_tile * kTileCols * 4);
-  plan.acts = plan.cta_sum + (static_cast<uint32_t>(m_tile) * kTileCols * 4);
+  plan.recv = plan.cta_sum + (static_cast<uint32_t>(m_tile) * kTileCols * 4);
+  plan.acts = plan.recv + (static_cast<uint32_t>(kMaxClusterCtas) * m_tile * kTileCols * 4);
   plan.rings = plan.acts + (static_cast<uint32_t>(warps) * m_tile * group * 2);
   plan.total = plan.rings + (static_cast<uint32_t>(warps) * stages * packet_stride(group));
   return plan;
@@ -99,6 +112,12 @@ __global__ void __launch_bounds__(512, 1)
   const uint32_t g_end = ((s + 1) * num_groups) / workers;
 
   trace_mark(0);
+  const uint32_t recv_bar = smem_base + plan.recv_bar;
+  if (rank == 0 && threadIdx.x == 0) {
+    mbar_init(recv_bar, 1);
+    mbar_init_fence();
+  }
+  cluster_barrier_arrive();  // the matching wait sits in front of the push, after the runs
   float y[M_TILE][4];
 #pragma unroll
   for (int m = 0; m < M_TILE; ++m) {
@@ -142,6 +161,9 @@ __global__ void __launch_bounds__(512, 1)
         make_float4(y[m][0], y[m][1], y[m][2], y[m][3]);
   }
   __syncthreads();
+  cluster_barrier_wait();  // rank 0's delivery barrier is initialised
+  trace_mark(4);
+  const uint32_t cta_bytes = static_cast<uint32_t>(kSlotFloats) * 4u;
   for (int idx = static_cast<int>(threadIdx.x); idx < kSlotFloats / 4; idx += static_cast<int>(blockDim.x)) {
     float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int w = 0; w < warps_per_cta; ++w) {
@@ -151,30 +173,43 @@ __global__ void __launch_bounds__(512, 1)
       total.z += part.z;
       total.w += part.w;
     }
-    reinterpret_cast<float4*>(cta_sum)[idx] = total;
+    if (rank == 0) {
+      reinterpret_cast<float4*>(cta_sum)[idx] = total;
+    } else {
+      // push into rank 0: delivered[rank][idx]
+      st_async_f4(cluster_map(smem_base + plan.recv + (rank * cta_bytes) + (idx * 16), 0), total,
+                  cluster_map(recv_bar, 0));
+    }
   }
-
-  // CTA sums -> outputs (rank order), by rank 0 through distributed shared memory
-  cluster_barrier();
-  trace_mark(4);
   if (rank == 0) {
-    const uint32_t sum_addr = smem_base + plan.cta_sum;
-    for (int idx = static_cast<int>(threadIdx.x); idx < kSlotFloats / 4; idx += static_cast<int>(blockDim.x)) {
-      float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      for (uint32_t r = 0; r < cluster_ctas; ++r) {
-        const float4 part = ld_cluster_f4(sum_addr + (idx * 16), r);
-        total[0] += part.x;
-        total[1] += part.y;
-        total[2] += part.z;
-        total[3] += part.w;
+    // CTA sums -> outputs, in rank order, once every other CTA of the cluster has delivered
+    if (threadIdx.x == 0) {
+      mbar_expect_tx(recv_bar, (cluster_ctas - 1) * cta_bytes);
+    }
+    __syncthreads();  // own sums written; the arrival above is in place
+    if (!mbar_wait_bounded(recv_bar, 0)) {
+      if (threadIdx.x == 0) {
+        atomicExch(p.status, static_cast<int>(kStatusCopyWaitTimeout));
       }
-      const int m = idx / (kTileCols / 4);
-      if (m < m_act) {
-        store_tile_row<E>(p, row0 + m, tile, idx % (kTileCols / 4), total);
+    } else {
+      const float* delivered = reinterpret_cast<const float*>(smem + plan.recv);
+      for (int idx = static_cast<int>(threadIdx.x); idx < kSlotFloats / 4; idx += static_cast<int>(blockDim.x)) {
+        float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t r = 0; r < cluster_ctas; ++r) {
+          const float4 part = r == 0 ? reinterpret_cast<const float4*>(cta_sum)[idx]
+                                     : reinterpret_cast<const float4*>(delivered + (r * kSlotFloats))[idx];
+          total[0] += part.x;
+          total[1] += part.y;
+          total[2] += part.z;
+          total[3] += part.w;
+        }
+        const int m = idx / (kTileCols / 4);
+        if (m < m_act) {
+          store_tile_row<E>(p, row0 + m, tile, idx % (kTileCols / 4), total);
+        }
       }
     }
   }
-  cluster_barrier();  // the other CTAs' shared memory must outlive rank 0's reads
   trace_mark(5);
 }
 
