@@ -104,7 +104,7 @@ __device__ __forceinline__ uint64_t l2_evict_last_policy() {
 }
 
 // Global -> this CTA's shared memory, `bytes` a multiple of 16, both addresses 16-byte aligned.
-// Completion is signalled on `bar` as transferred bytes. No cluster multicast is ever used.
+// Completion is signalled on `bar` as transferred bytes. Every copy has exactly one destination CTA.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
                                               uint32_t bar, uint64_t policy) {
   asm volatile(
