@@ -109,6 +109,19 @@ def build_python_module(force: bool = False) -> Path:
     return target
 
 
+def reference_checkout() -> Path | None:
+    """Where a checkout of the reference project lies, if anywhere: $FK_REFERENCE_ROOT, else a
+    directory named `reference` beside this repository."""
+    candidates = []
+    if os.environ.get("FK_REFERENCE_ROOT"):
+        candidates.append(Path(os.environ["FK_REFERENCE_ROOT"]))
+    candidates.append(REPO.parent / "reference")
+    for candidate in candidates:
+        if (candidate / "csrc" / "kernels" / "decode_quant_linear" / "arc_w4a16.cu").exists():
+            return candidate
+    return None
+
+
 def build_oracle(force: bool = False) -> None:
     """The CPU checker (tests and bench baseline only) and, if the reference checkout is there,
     the reference's own kernels as oracle/_ref/libfk_reference.so."""
@@ -117,8 +130,8 @@ def build_oracle(force: bool = False) -> None:
     if force:
         args.insert(1, "-B")
     _run(args)
-    reference = Path(os.environ.get("FK_REFERENCE_ROOT", "/root/reference"))
-    if (reference / "csrc" / "kernels" / "decode_quant_linear" / "arc_w4a16.cu").exists():
+    reference = reference_checkout()
+    if reference is not None:
         _run(["make", "-C", str(oracle_dir), "ref", f"REF={reference}"])
 
 

@@ -140,29 +140,36 @@ struct DeviceInfo {
 
 int device_info(DeviceInfo** out) {
   static DeviceInfo infos[kMaxDevices];
-  static std::once_flag flags[kMaxDevices];
+  static std::atomic<bool> ready[kMaxDevices];
+  static std::mutex lock;
   int device = 0;
   FK_TRY_CUDA(cudaGetDevice(&device));
   if (device < 0 || device >= kMaxDevices) {
     return fail(FK_W4A16_ERR_CUDA, "device index out of range");
   }
-  cudaError_t err = cudaSuccess;
-  std::call_once(flags[device], [&] {
-    DeviceInfo& info = infos[device];
-    err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device);
-    if (err == cudaSuccess) {
-      err = cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin,
-                                   device);
+  if (!ready[device].load(std::memory_order_acquire)) {
+    // A lookup that fails (a first call made while a stream is being captured, say) leaves the
+    // entry unset, so a later call made under better conditions can still succeed.
+    std::lock_guard<std::mutex> guard(lock);
+    if (!ready[device].load(std::memory_order_relaxed)) {
+      DeviceInfo info;
+      cudaError_t err = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device);
+      if (err == cudaSuccess) {
+        err = cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                     device);
+      }
+      if (err == cudaSuccess) {
+        void* addr = nullptr;
+        err = cudaGetSymbolAddress(&addr, g_device_status);
+        info.status_word = static_cast<int*>(addr);
+      }
+      if (err != cudaSuccess || info.status_word == nullptr) {
+        return fail(FK_W4A16_ERR_CUDA,
+                    std::string("device query failed: ") + cudaGetErrorString(err));
+      }
+      infos[device] = info;
+      ready[device].store(true, std::memory_order_release);
     }
-    if (err == cudaSuccess) {
-      void* addr = nullptr;
-      err = cudaGetSymbolAddress(&addr, g_device_status);
-      info.status_word = static_cast<int*>(addr);
-    }
-  });
-  if (err != cudaSuccess || infos[device].status_word == nullptr) {
-    return fail(FK_W4A16_ERR_CUDA,
-                std::string("device query failed: ") + cudaGetErrorString(err));
   }
   *out = &infos[device];
   return FK_W4A16_OK;
@@ -753,13 +760,15 @@ int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* strea
 namespace {
 // `with_exchange_area`: the workspace has the full header (ticket + pair-exchange areas); without
 // it -- the library's own static scratch -- the header is the ticket area alone.
-int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area);
+// `small_batch_on_cuda_cores`: batches of at most 4 never take the tensor-core plan (whose slots
+// and staged activations need more scratch than the static array holds).
+int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool small_batch_on_cuda_cores);
 }  // namespace
 
-int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) { return gemv_impl(args, true); }
+int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args) { return gemv_impl(args, true, false); }
 
 namespace {
-int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
+int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool small_batch_on_cuda_cores) {
   if (args == nullptr) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "args must not be null");
   }
@@ -810,8 +819,8 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
   FK_TRY(device_info(&info));
   // The workspace requirement is that of the packet-stream plan whichever kernel runs, so that
   // fk_w4a16_workspace_bytes() is a safe answer for every option combination.
-  const Plan stream_plan =
-      make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  const Plan stream_plan = make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
+                                     launch_config(), false, small_batch_on_cuda_cores);
   const bool normalise = args->norm_weight != nullptr;
   if (normalise) {
     FK_TRY(check_pointer(args->norm_weight, "norm_weight", 16));
@@ -825,7 +834,8 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area) {
       (tc5_enabled() && !normalise)
           ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
           : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
-                      /*allow_cluster=*/args->local_signal == nullptr, /*cuda_cores_only=*/normalise);
+                      /*allow_cluster=*/args->local_signal == nullptr,
+                      /*cuda_cores_only=*/normalise || small_batch_on_cuda_cores);
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
   }
@@ -1059,26 +1069,32 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
   DeviceInfo* info = nullptr;
   FK_TRY(device_info(&info));
 
-  // Once per device, with that device current: the device address of the static array.
+  // Once per device, with that device current: the device address of the static array. A failed
+  // lookup is not remembered, so a first call that came at a bad moment (during stream capture)
+  // does not poison the device for the rest of the process.
   static void* scratch_address[kMaxDevices] = {};
-  static std::once_flag scratch_once[kMaxDevices];
+  static std::mutex scratch_lock;
   int device = 0;
   FK_TRY_CUDA(cudaGetDevice(&device));
-  cudaError_t lookup = cudaSuccess;
-  std::call_once(scratch_once[device], [&] {
-    void* address = nullptr;
-    lookup = cudaGetSymbolAddress(&address, g_static_scratch);
-    if (lookup == cudaSuccess) {
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(scratch_lock);
+    if (scratch_address[device] == nullptr) {
+      void* address = nullptr;
+      const cudaError_t lookup = cudaGetSymbolAddress(&address, g_static_scratch);
+      if (lookup != cudaSuccess || address == nullptr) {
+        return fail(FK_W4A16_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch) failed: ") +
+                                           cudaGetErrorString(lookup));
+      }
       scratch_address[device] = address;
     }
-  });
-  if (lookup != cudaSuccess || scratch_address[device] == nullptr) {
-    return fail(FK_W4A16_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch) failed: ") +
-                                       cudaGetErrorString(lookup));
+    scratch = scratch_address[device];
   }
 
-  const Plan plan =
-      make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  // Batches of at most 4 stay on the CUDA-core kernels here (their scratch always fits); the plan
+  // below is the one gemv_impl makes with the same flag.
+  const Plan plan = make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin,
+                              launch_config(), /*allow_cluster=*/false, /*cuda_cores_only=*/true);
   const size_t need = workspace_bytes_for(plan, kTicketBytes);
   if (need > static_cast<size_t>(FK_W4A16_STATIC_SCRATCH_BYTES)) {
     std::ostringstream oss;
@@ -1092,13 +1108,12 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
   if (ticket_bytes > kTicketBytes) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * batch exceeds the ticket area of a workspace");
   }
-  FK_TRY_CUDA(cudaMemsetAsync(scratch_address[device], 0, ticket_bytes,
-                              static_cast<cudaStream_t>(stream)));
+  FK_TRY_CUDA(cudaMemsetAsync(scratch, 0, ticket_bytes, static_cast<cudaStream_t>(stream)));
   fk_w4a16_gemv_args args{};
   args.activations = activations;
   args.packets = packets;
   args.output = output;
-  args.workspace = scratch_address[device];
+  args.workspace = scratch;
   args.workspace_bytes = FK_W4A16_STATIC_SCRATCH_BYTES;
   args.batch = batch;
   args.n = n;
@@ -1107,7 +1122,7 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
   args.packet_stride_bytes = packet_stride_bytes;
   args.dtype = dtype;
   args.stream = stream;
-  return gemv_impl(&args, /*with_exchange_area=*/false);
+  return gemv_impl(&args, /*with_exchange_area=*/false, /*small_batch_on_cuda_cores=*/true);
 }
 
 int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,

@@ -161,11 +161,15 @@ FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
  * fixed array of FK_W4A16_STATIC_SCRATCH_BYTES inside the library's device image; every GPU that
  * loads the library holds that much until the process exits, whether or not this function is used.
  *
- * Same arguments and results as fk_w4a16_gemv minus the workspace. Problems whose scratch need
- * exceeds the array (in practice batch > 4, or devices with far more SMs than a B200) are refused
- * with FK_W4A16_ERR_INVALID_ARGUMENT and a message that states both sizes. The function calls no
+ * Same arguments and results as fk_w4a16_gemv minus the workspace. Batches of 1 to 4 always run on
+ * the CUDA-core kernels here, whose scratch (at most 862 KB on a 148-SM device) fits the array for
+ * every layer shape -- so for batch 3 and 4 on large layers the result can differ in the last bit
+ * from fk_w4a16_gemv, which moves those to the tensor-core kernel. Batches above 4 need more than
+ * the array holds (the tensor-core plan's slots and staged activations) and are refused with
+ * FK_W4A16_ERR_INVALID_ARGUMENT and a message that states both sizes. The function calls no
  * allocator of any kind. The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress, with that device current); make that first call outside stream capture.
+ * (cudaGetSymbolAddress, with that device current); make that first call outside stream capture
+ * (a lookup that fails is retried by the next call).
  * All calls on a device share the one array: the part a call depends on being zero is cleared on
  * `stream` before each launch, but two calls that overlap on the GPU (different streams, no
  * ordering between them) would race on it -- serialise them or use fk_w4a16_gemv with separate

@@ -79,4 +79,14 @@ int fkref_cublaslt_after_dequant(std::uintptr_t act, std::uintptr_t q, std::uint
   });
 }
 
+int fkref_cublaslt_after_packet_dequant(std::uintptr_t act, std::uintptr_t packets, std::uintptr_t out,
+                                        std::uintptr_t weight, std::uintptr_t workspace,
+                                        std::size_t workspace_bytes, int batch, int n, int k,
+                                        int group, int stride, std::uintptr_t stream) {
+  return guarded([&] {
+    ref::cublaslt_fp16_after_packet_dequant(act, packets, out, weight, workspace, workspace_bytes, batch,
+                                            n, k, group, stride, stream);
+  });
+}
+
 }  // extern "C"

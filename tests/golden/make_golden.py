@@ -21,6 +21,7 @@ import argparse
 import hashlib
 import importlib.util
 import json
+import os
 import sys
 import types
 from pathlib import Path
@@ -78,7 +79,8 @@ def _sha(*arrays: np.ndarray) -> str:
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("FK_REFERENCE_ROOT"), required="FK_REFERENCE_ROOT" not in os.environ,
+                        help="checkout of the reference project (or set FK_REFERENCE_ROOT)")
     ns = parser.parse_args()
     tests_mod, bench_mod = _load_reference(Path(ns.reference))
     explicit = tests_mod._explicit_reference_output

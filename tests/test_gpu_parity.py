@@ -178,6 +178,128 @@ def test_gemv_full_size_properties() -> None:
     assert oracle.max_rel_err(y1[:, rows].cpu().numpy(), y64) <= GEMV_REL_TOL
 
 
+def _oracle_rows(problem: dict, rows: slice, group: int, code: int) -> np.ndarray:
+    return oracle.gemv_f64(oracle.bits_of(problem["activations"]), problem["q_u8"][rows].numpy(),
+                           oracle.bits_of(problem["alpha"][rows]), oracle.bits_of(problem["beta"][rows]),
+                           group, code)
+
+
+def test_gemv_lm_head_against_the_oracle() -> None:
+    """The largest configured shape, 128256 x 4096 (1002 tiles, 32064 packets): row slices at the
+    start, across the middle and at the very end of the output against the fp64 oracle; every
+    output written; a second call gives the same bits."""
+    shape = LayerShape("lm_head", 128256, 4096, dtype="bf16")
+    problem = make_problem(shape)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    del q
+    out = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    again = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all(), "some outputs were never written"
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16))
+    got = out.float().cpu().numpy()
+    for rows in (slice(0, 384), slice(64000, 64512), slice(128256 - 384, 128256)):
+        assert oracle.max_rel_err(got[:, rows], _oracle_rows(problem, rows, 128, 1)) <= GEMV_REL_TOL, rows
+
+
+@pytest.mark.parametrize("batch", [2, 4, 8])
+def test_gemv_batched_sweep_shape_against_the_oracle(batch: int) -> None:
+    """28672 x 8192 with per-group uint4 zero points at batches 2, 4 and 8 (4 is where the launch
+    plan switches to the tensor-core kernel on a layer this large)."""
+    shape = LayerShape("mlp_up", 28672, 8192, batch=batch, dtype="bf16", zero_point=None)
+    problem = make_problem(shape)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    del q
+    out = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    again = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all(), "some outputs were never written"
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16))
+    got = out.float().cpu().numpy()
+    for rows in (slice(0, 256), slice(14200, 14456), slice(28672 - 256, 28672)):
+        assert oracle.max_rel_err(got[:, rows], _oracle_rows(problem, rows, 128, 1)) <= GEMV_REL_TOL, rows
+
+
+def test_gemv_13b_mlp_group_128() -> None:
+    shape = LayerShape("mlp13b_g128", 13824, 5120, group_size=128, dtype="fp16", scale_range=(0.001, 0.05),
+                       zero_point=None)
+    _check_gemv(make_problem(shape), shape, 0)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_shards_of_the_fused_gate_up_layer(world: int) -> None:
+    """57344 x 8192 split by output columns over 2, 4 and 8 ranks, every rank's shard run on this
+    GPU: each shard's outputs land in its slice of the full row (output_ld / output_col0), and the
+    assembled row meets the fp64 oracle on slices that straddle shard boundaries."""
+    from fast_kernels.dist import column_shard_packets
+
+    lib = capi.load_library()
+    shape = LayerShape("gate_up_70b", 57344, 8192, dtype="bf16")
+    problem = make_problem(shape)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    del q
+    n_local = shape.n // world
+    full = torch.full((1, shape.n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rank in range(world):
+        shard = column_shard_packets(packets, n=shape.n, k=shape.k, group_size=128, rank=rank, world=world)
+        args = capi.GemvArgs()
+        ws = WS.get(capi, 1, n_local, shape.k, 128)
+        args.activations, args.packets, args.output = act.data_ptr(), shard.data_ptr(), full.data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = 1, n_local, shape.k, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.output_ld, args.output_col0 = shape.n, rank * n_local
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+    torch.cuda.synchronize()
+    assert torch.isfinite(full.float()).all(), "some outputs were never written"
+    got = full.float().cpu().numpy()
+    edge = n_local  # the boundary between rank 0 and rank 1
+    for rows in (slice(0, 256), slice(edge - 128, edge + 128), slice(shape.n - 256, shape.n)):
+        assert oracle.max_rel_err(got[:, rows], _oracle_rows(problem, rows, 128, 1)) <= GEMV_REL_TOL, rows
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_shards_of_the_down_projection(world: int) -> None:
+    """8192 x 28672 split by input features over 2, 4 and 8 ranks, every rank's shard run on this
+    GPU with unrounded fp32 outputs; the partials, added in rank order and rounded once, meet the
+    fp64 oracle."""
+    from fast_kernels.dist import activation_shard, row_shard_packets
+
+    lib = capi.load_library()
+    shape = LayerShape("down_70b", 8192, 28672, dtype="bf16")
+    problem = make_problem(shape)
+    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    del q
+    k_local = shape.k // world
+    partials = torch.full((world, 1, shape.n), float("nan"), dtype=torch.float32, device="cuda")
+    for rank in range(world):
+        shard = row_shard_packets(packets, n=shape.n, k=shape.k, group_size=128, rank=rank, world=world)
+        local_act = activation_shard(act, rank=rank, world=world, mode="row")
+        args = capi.GemvArgs()
+        ws = WS.get(capi, 1, shape.n, k_local, 128)
+        args.activations, args.packets = local_act.data_ptr(), shard.data_ptr()
+        args.output = partials[rank].data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = 1, shape.n, k_local, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.output_f32 = 1
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+        torch.cuda.synchronize()
+    assert torch.isfinite(partials).all(), "some partial sums were never written"
+    total = partials[0].clone()
+    for rank in range(1, world):
+        total = total + partials[rank]
+    got = total.to(torch.bfloat16).float().cpu().numpy()
+    for rows in (slice(0, 512), slice(4000, 4256), slice(shape.n - 256, shape.n)):
+        assert oracle.max_rel_err(got[:, rows], _oracle_rows(problem, rows, 128, 1)) <= GEMV_REL_TOL, rows
+
+
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize(("batch", "slices"), [(1, 2), (8, 4), (3, 7)])
 def test_split_k_and_reduce(batch: int, slices: int, dtype: str) -> None:
