@@ -14,9 +14,23 @@ The step is captured once as a CUDA graph of 128 launches of the library's C-ABI
 (`fk_w4a16_gemv`) and replayed; timing is by CUDA events on the launching stream between a barrier
 and a device synchronisation, maximum over ranks. One JSON line is printed by rank 0.
 
+The timed region of K steps is repeated (`--regions`, default 15); `value` is the median region,
+the spread is reported beside it. `roofline` names the kernel with the largest share of the step
+and carries one entry per kernel (`kernels`) and per layer shape (`per_layer`).
+
 `e2e` measures the same work through the C-ABI entry point that takes HOST buffers
-(`fk_w4a16_gemv_host`), one call per GEMV: every call copies its activations from pinned host
-memory to the device and its result back inside the timed region.
+(`fk_w4a16_gemv_host`), one call per GEMV: every call pulls its activations from pinned host
+memory and stores its result to pinned host memory inside the timed region. The 128 calls of a
+step are recorded once into a CUDA graph (as a decode loop would) and replayed; the eager
+call-by-call figure is reported beside it.
+
+Extra keys, measured outside the headline's timed region on one GPU: `configs` (the other
+benchmark configurations: the single fp16 case, the batched sweep at 28672 x 8192, the 13B MLP at
+three group sizes, the LM head), `pack` (weight packing throughput), `reference_gpu` (the
+reference's own CUDA kernels, compiled unmodified into oracle/_ref, on the same layer shapes) and
+`cpu_baseline`. With N > 1 -- and as a one-GPU row at N = 1 -- `sharded_layers` strong-scales the
+two large sharded layers, checks every result against the fp64 oracle and reports the speed-up
+over one GPU.
 
 `--impl reference` times the reference's CPU-runnable arithmetic for this path -- its torch
 expression `_explicit_reference_output`, restated in C in oracle/ -- on the host cores, on the same
@@ -228,14 +242,20 @@ class LayerSet:
         shapes = _layer_shapes()
         stride = capi.packet_stride_bytes(128)
         base = {}
+        self.pack = None
         for shape in shapes:
             prob = make_problem(shape)
             q, alpha, beta = (prob[key].to(device) for key in ("q_u8", "alpha", "beta"))
             packets = torch.empty(((shape.n // 128) * (shape.k // 128), stride), dtype=torch.uint8,
                                   device=device)
-            capi.check(self.lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(),
-                                                      packets.data_ptr(), shape.n, shape.k, 128, stride,
-                                                      self.stream_ptr()))
+
+            def pack() -> None:
+                capi.check(self.lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(),
+                                                          packets.data_ptr(), shape.n, shape.k, 128, stride,
+                                                          self.stream_ptr()))
+            pack()
+            if shape.name == "gate_up":
+                self.pack = self._time_pack(pack, shape, q, alpha, beta, packets)
             base[shape.name] = (prob["activations"].to(device), packets)
         torch.cuda.synchronize(device)
         gen = torch.Generator(device="cpu").manual_seed(1234)
@@ -253,6 +273,25 @@ class LayerSet:
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)
         self.stride = stride
 
+    def _time_pack(self, pack, shape, q, alpha, beta, packets) -> dict:
+        """Throughput of the one-time weight packing on the 62 MB layer (reads q, alpha, beta;
+        writes the packets), CUDA events around 5 back-to-back runs after 2 warm-ups."""
+        torch = self.torch
+        for _ in range(2):
+            pack()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(self.device)
+        start.record()
+        for _ in range(5):
+            pack()
+        stop.record()
+        torch.cuda.synchronize(self.device)
+        us = start.elapsed_time(stop) * 1e3 / 5
+        moved = q.numel() + 2 * alpha.numel() + 2 * beta.numel() + packets.numel()
+        return {"layer": shape.name, "n": shape.n, "k": shape.k, "us_per_call": us,
+                "bytes_read_plus_written": moved, "gbs": moved / (us * 1e-6) / 1e9,
+                "kernel": "fk_w4a16::pack_packets_kernel<128>"}
+
     def stream_ptr(self) -> int:
         return int(self.torch.cuda.current_stream(self.device).cuda_stream)
 
@@ -265,21 +304,25 @@ class LayerSet:
                 self.workspace.numel(), 1, shape.n, shape.k, 128, self.stride, self.capi.DTYPE_BF16, stream))
 
     def capture(self, calls=None):
-        torch = self.torch
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream(device=self.device)
-        side.wait_stream(torch.cuda.current_stream(self.device))
         saved = self.calls
         if calls is not None:
             self.calls = calls
         try:
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(graph, stream=side):
-                    self.launch_all()
+            return _capture(self.torch, self.device, self.launch_all)
         finally:
             self.calls = saved
-        torch.cuda.current_stream(self.device).wait_stream(side)
-        return graph
+
+
+def _capture(torch, device, enqueue):
+    """Records `enqueue()` (which launches on the current stream) into a CUDA graph."""
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            enqueue()
+    torch.cuda.current_stream(device).wait_stream(side)
+    return graph
 
 
 def _time_graph(torch, graph, reps: int, device) -> float:
@@ -300,8 +343,9 @@ NCU_TRAFFIC_RATIO = 1.003
 
 def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
     """The same step through the C-ABI call that takes HOST buffers (`fk_w4a16_gemv_host`): every
-    call copies its activations from pinned host memory to the device, runs the GEMV and copies
-    the result back to pinned host memory, all inside the timed region."""
+    call pulls its activations from pinned host memory, runs the GEMV and delivers the result to
+    pinned host memory, all inside the timed region. Measured twice: with the step's 128 calls
+    recorded once into a CUDA graph and replayed, and eagerly, call by call."""
     capi = layers.capi
     lib = layers.lib
     host_in, host_out, dev_in = {}, {}, {}
@@ -311,20 +355,27 @@ def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
         dev_in[shape.name] = torch.empty_like(act)
     h2d = sum(t.numel() * 2 for t in host_in.values()) * NUM_LAYERS
     d2h = sum(t.numel() * 2 for t in host_out.values()) * NUM_LAYERS
-    stream = layers.stream_ptr()
     plan = [(host_in[s.name].data_ptr(), packets.data_ptr(), host_out[s.name].data_ptr(),
              dev_in[s.name].data_ptr(), out.data_ptr(), s.n, s.k) for s, _, packets, out in layers.calls]
     ws, ws_bytes = layers.workspace.data_ptr(), layers.workspace.numel()
 
     def step() -> None:
+        stream = layers.stream_ptr()
         for h_in, packets, h_out, d_in, d_out, n, k in plan:
             rc = lib.fk_w4a16_gemv_host(h_in, packets, h_out, d_in, d_out, ws, ws_bytes, 1, n, k, 128,
                                         layers.stride, capi.DTYPE_BF16, stream)
             if rc != 0:
                 capi.check(rc)
 
+    def check_results() -> None:
+        # the results are real: the last call's output on the host equals the device tensor
+        last_shape, _, _, last_out = layers.calls[-1]
+        if not torch.equal(host_out[last_shape.name], last_out.cpu()):
+            raise SystemExit("e2e: host result differs from the device result")
+
     step()
     torch.cuda.synchronize(device)
+    # eager, call by call
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     host_begin = time.perf_counter()
@@ -334,13 +385,18 @@ def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
     stop.record()
     host_seconds = time.perf_counter() - host_begin  # time the host spent enqueueing
     torch.cuda.synchronize(device)
-    seconds = start.elapsed_time(stop) / 1e3
-    # the results are real: the last call's output on the host equals the device tensor
-    last_shape, _, _, last_out = layers.calls[-1]
-    if not torch.equal(host_out[last_shape.name], last_out.cpu()):
-        raise SystemExit("e2e: host result differs from the device result")
-    return {"seconds": seconds, "host_seconds": host_seconds, "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h}
+    eager_seconds = start.elapsed_time(stop) / 1e3
+    check_results()
+    # recorded once, replayed: what a decode loop does with a fixed sequence of calls
+    for tensor in host_out.values():
+        tensor.zero_()
+    graph = _capture(torch, device, step)
+    for _ in range(2):
+        graph.replay()
+    graph_seconds = _time_graph(torch, graph, steps, device)
+    check_results()
+    return {"seconds": graph_seconds, "eager_seconds": eager_seconds, "host_seconds": host_seconds,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
 
 def _cpu_baseline_leg() -> dict:
@@ -369,13 +425,172 @@ def _cpu_baseline_leg() -> dict:
     }
 
 
+# ------------------------------------------------------------------------------------------
+# single calls over rotated weight copies: the other configurations, the reference's kernels
+# ------------------------------------------------------------------------------------------
+def _rotated_copies(torch, packets, total_bytes: float = 6.0e8):
+    count = max(2, int(total_bytes // packets.numel()) + 1)
+    return [packets] + [packets.clone() for _ in range(count - 1)]
+
+
+def _time_rotation(torch, device, enqueue_one, copies, reps: int = 5) -> float:
+    """Microseconds per call: one CUDA graph that calls `enqueue_one(copy)` once per weight copy
+    (the copies together exceed L2 several times over), best of `reps` replays after 2 warm-ups."""
+    enqueue_one(copies[0])
+    torch.cuda.synchronize(device)
+
+    def all_copies() -> None:
+        for copy in copies:
+            enqueue_one(copy)
+
+    graph = _capture(torch, device, all_copies)
+    for _ in range(2):
+        graph.replay()
+    best = min(_time_graph(torch, graph, 1, device) for _ in range(reps))
+    return best * 1e6 / len(copies)
+
+
+def _configs_leg(torch, capi, device, peak_gbs: float) -> list[dict]:
+    """Per-call device time of the benchmark configurations the headline does not cover."""
+    from fast_kernels.workloads import EDGE_SHAPES, REFERENCE_CASE, LayerShape, make_problem
+
+    lib = capi.load_library()
+    results = []
+
+    def packed(shape, seed=None):
+        prob = make_problem(shape, seed=seed)
+        q, alpha, beta = (prob[key].to(device) for key in ("q_u8", "alpha", "beta"))
+        stride = capi.packet_stride_bytes(shape.group_size)
+        packets = torch.empty(((shape.n // 128) * (shape.k // shape.group_size), stride), dtype=torch.uint8,
+                              device=device)
+        capi.check(lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(), packets.data_ptr(),
+                                             shape.n, shape.k, shape.group_size, stride,
+                                             int(torch.cuda.current_stream(device).cuda_stream)))
+        torch.cuda.synchronize(device)
+        return prob, packets
+
+    def measure(config: str, shape, act, copies, workspace) -> None:
+        code = capi.DTYPE_BF16 if shape.dtype == "bf16" else capi.DTYPE_F16
+        out = torch.empty((shape.batch, shape.n), dtype=act.dtype, device=device)
+        stride = capi.packet_stride_bytes(shape.group_size)
+
+        def one(copy) -> None:
+            capi.check(lib.fk_w4a16_gemv(act.data_ptr(), copy.data_ptr(), out.data_ptr(), workspace.data_ptr(),
+                                         workspace.numel(), shape.batch, shape.n, shape.k, shape.group_size,
+                                         stride, code, int(torch.cuda.current_stream(device).cuda_stream)))
+
+        us = _time_rotation(torch, device, one, copies)
+        gbs = shape.algorithmic_bytes() / (us * 1e-6) / 1e9
+        results.append({"config": config, "name": shape.name, "batch": shape.batch, "n": shape.n, "k": shape.k,
+                        "group_size": shape.group_size, "dtype": shape.dtype, "us_per_call": us,
+                        "achieved_gbs": gbs, "frac_of_peak": gbs / peak_gbs,
+                        "algorithmic_bytes": shape.algorithmic_bytes(),
+                        "kernel": capi.describe_plan(shape.batch, shape.n, shape.k, shape.group_size, code),
+                        "weight_copies": len(copies)})
+
+    def workspace_for(shape):
+        need = int(lib.fk_w4a16_workspace_bytes(shape.batch, shape.n, shape.k, shape.group_size))
+        return torch.zeros(need, dtype=torch.uint8, device=device)
+
+    # configs[0]: the single fp16 case, seed 0
+    prob, packets = packed(REFERENCE_CASE, seed=0)
+    measure("configs[0]", REFERENCE_CASE, prob["activations"].to(device), _rotated_copies(torch, packets),
+            workspace_for(REFERENCE_CASE))
+    # configs[2]: batched sweep over one set of weights (per-group uint4 zero points)
+    base = LayerShape("mlp_up", 28672, 8192, zero_point=None)
+    prob, packets = packed(base)
+    copies = _rotated_copies(torch, packets)
+    gen = torch.Generator().manual_seed(2)
+    for batch in (1, 2, 4, 8, 16):
+        shape = LayerShape(f"mlp_up_m{batch}", 28672, 8192, batch=batch, zero_point=None)
+        act = torch.randn((batch, shape.k), generator=gen).to(torch.bfloat16).to(device)
+        measure("configs[2]", shape, act, copies, workspace_for(shape))
+    del copies, packets
+    torch.cuda.empty_cache()
+    # configs[4]: 13B MLP at three group sizes (fp16, asymmetric zeros), and the LM head
+    for shape in EDGE_SHAPES:
+        prob, packets = packed(shape)
+        measure("configs[4]", shape, prob["activations"].to(device), _rotated_copies(torch, packets, 8.0e8),
+                workspace_for(shape))
+        del packets
+        torch.cuda.empty_cache()
+    return results
+
+
+def _reference_gpu_leg(torch, capi, device) -> dict:
+    """The reference's own CUDA kernels (arc_w4a16.cu compiled unmodified into oracle/_ref) on the
+    four layer shapes -- fp16, group 128, the only type it has -- timed the same way as `configs`:
+    its scalar path as its Python op chains it (group-sum prepass + arc_w4a16_forward) and its
+    vendor subject (packet dequant + cuBLASLt). Baseline only; never on the product path."""
+    from fast_kernels.workloads import LayerShape, make_problem
+    from oracle import reference_gpu as ref
+
+    if not ref.available():
+        return {"unavailable": "oracle/_ref/libfk_reference.so is not built (no reference checkout at build time)"}
+    lib = capi.load_library()
+    rows = []
+    for base in _layer_shapes():
+        shape = LayerShape(base.name, base.n, base.k, dtype="fp16")
+        prob = make_problem(shape)
+        q, alpha, beta, act = (prob[key].to(device) for key in ("q_u8", "alpha", "beta", "activations"))
+        packets = torch.empty(((shape.n // 128) * (shape.k // 128), 8704), dtype=torch.uint8, device=device)
+        capi.check(lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(), packets.data_ptr(),
+                                             shape.n, shape.k, 128, 8704, 0))
+        torch.cuda.synchronize(device)
+        copies = _rotated_copies(torch, packets, 3.0e8)
+        sums = torch.empty((1, shape.k // 128), dtype=torch.float32, device=device)
+        out = torch.empty((1, shape.n), dtype=torch.float16, device=device)
+        weight = torch.empty((shape.n, shape.k), dtype=torch.float16, device=device)
+        lt_ws = torch.empty(32 << 20, dtype=torch.uint8, device=device)
+
+        def scalar(copy) -> None:
+            stream = int(torch.cuda.current_stream(device).cuda_stream)
+            ref.group_sums(act.data_ptr(), sums.data_ptr(), 1, shape.k, 128, stream)
+            ref.forward(act.data_ptr(), copy.data_ptr(), sums.data_ptr(), out.data_ptr(), 1, shape.n, shape.k, 128,
+                        stream)
+
+        def vendor(copy) -> None:
+            stream = int(torch.cuda.current_stream(device).cuda_stream)
+            ref.cublaslt_after_packet_dequant(act.data_ptr(), copy.data_ptr(), out.data_ptr(), weight.data_ptr(),
+                                              lt_ws.data_ptr(), lt_ws.numel(), 1, shape.n, shape.k, 128, stream)
+
+        ws = torch.zeros(int(lib.fk_w4a16_workspace_bytes(1, shape.n, shape.k, 128)), dtype=torch.uint8,
+                         device=device)
+
+        def ours(copy) -> None:
+            capi.check(lib.fk_w4a16_gemv(act.data_ptr(), copy.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         1, shape.n, shape.k, 128, 8704, capi.DTYPE_F16,
+                                         int(torch.cuda.current_stream(device).cuda_stream)))
+
+        row = {"name": shape.name, "n": shape.n, "k": shape.k, "dtype": "fp16", "group_size": 128}
+        row["reference_scalar_us"] = _time_rotation(torch, device, scalar, copies, reps=3)
+        try:
+            row["reference_cublaslt_after_packet_dequant_us"] = _time_rotation(torch, device, vendor, copies, reps=3)
+        except Exception as exc:  # cuBLASLt under capture is the reference's affair, not ours
+            row["reference_cublaslt_after_packet_dequant_us"] = None
+            row["cublaslt_note"] = f"{type(exc).__name__}: {exc}"[:160]
+        row["this_library_fp16_us"] = _time_rotation(torch, device, ours, copies, reps=3)
+        rows.append(row)
+        del copies, packets, weight
+        torch.cuda.empty_cache()
+    return {"note": "reference kernels: csrc/kernels/decode_quant_linear/arc_w4a16.cu of the reference, "
+                    "compiled for sm_100a without changes; us per call, CUDA graph over rotated weight copies",
+            "layers": rows}
+
+
+# ------------------------------------------------------------------------------------------
+# sharded layers
+# ------------------------------------------------------------------------------------------
 def _sharded_layers(torch, dist, capi, device, world: int, rank: int, peak_gbs: float) -> list[dict]:
     """The two layers that are large enough to be split over the GPUs of a node (70B-style fused
-    gate+up, N-split; down_proj, K-split), each with the NCCL exchange and with the exchange done
-    by the GEMV kernel itself through peer memory. Per-call device time over a CUDA graph that
-    cycles through several weight copies (so shards that would fit in L2 still come from HBM)."""
-    from fast_kernels.dist import ShardedW4A16Linear, column_shard_packets, row_shard_packets
+    gate+up, N-split; down_proj, K-split): first on ONE GPU (every rank times the whole layer on
+    its own device; rank 0's figure is the strong-scaling baseline), then sharded, with the NCCL
+    exchange and with the exchange done by the GEMV kernel itself through peer memory. Every
+    sharded result is checked against the fp64 oracle on a 512-column slice and must be bit-equal
+    on all ranks. Per-call device time over a CUDA graph that cycles through several weight copies
+    (so shards that would fit in L2 still come from HBM), maximum over ranks."""
     from fast_kernels.workloads import SHARDED_COLUMN, SHARDED_ROW, make_problem
+    from oracle import w4a16_oracle as oracle
 
     lib = capi.load_library()
     results = []
@@ -388,20 +603,70 @@ def _sharded_layers(torch, dist, capi, device, world: int, rank: int, peak_gbs: 
         capi.check(lib.fk_w4a16_pack_packets(q.data_ptr(), alpha.data_ptr(), beta.data_ptr(), packets.data_ptr(),
                                              shape.n, shape.k, 128, stride,
                                              int(torch.cuda.current_stream(device).cuda_stream)))
+        torch.cuda.synchronize(device)
+        del q, alpha, beta
+        cols = slice(shape.n // 2 - 256, shape.n // 2 + 256)  # straddles a shard boundary at every world size
+        y64 = oracle.gemv_f64(oracle.bits_of(prob["activations"]), prob["q_u8"][cols].numpy(),
+                              oracle.bits_of(prob["alpha"][cols]), oracle.bits_of(prob["beta"][cols]), 128,
+                              oracle.BF16)
+
+        # ---- one GPU: the whole layer through fk_w4a16_gemv -------------------------------------
+        copies = _rotated_copies(torch, packets, 5.0e8)
+        ws = torch.zeros(int(lib.fk_w4a16_workspace_bytes(1, shape.n, shape.k, 128)), dtype=torch.uint8,
+                         device=device)
+        out1 = torch.empty((1, shape.n), dtype=torch.bfloat16, device=device)
+
+        def whole(copy) -> None:
+            capi.check(lib.fk_w4a16_gemv(act.data_ptr(), copy.data_ptr(), out1.data_ptr(), ws.data_ptr(), ws.numel(),
+                                         1, shape.n, shape.k, 128, stride, capi.DTYPE_BF16,
+                                         int(torch.cuda.current_stream(device).cuda_stream)))
+
+        one_gpu_us = _time_rotation(torch, device, whole, copies)
+        whole(copies[0])
+        torch.cuda.synchronize(device)
+        err1 = oracle.max_rel_err(out1[:, cols].float().cpu().numpy(), y64)
+        if world > 1:
+            t = torch.tensor([one_gpu_us], dtype=torch.float64, device=device)
+            dist.broadcast(t, src=0)
+            one_gpu_us = float(t.item())
+        gbs1 = shape.algorithmic_bytes() / (one_gpu_us * 1e-6) / 1e9
+        results.append({"layer": shape.name, "n": shape.n, "k": shape.k, "split": "none", "exchange": "none",
+                        "gpus": 1, "us_per_call": one_gpu_us, "aggregate_gbs": gbs1,
+                        "frac_of_n_gpu_peak": gbs1 / peak_gbs, "max_rel_err": err1, "speedup_vs_1gpu": 1.0,
+                        "launch": "cuda graph", "weight_copies": len(copies)})
+        if err1 > 1e-2:
+            raise SystemExit(f"sharded_layers: one-GPU result of {shape.name} is off the fp64 oracle by {err1:.3e}")
+        del copies, ws
+        torch.cuda.empty_cache()
+        if world == 1:
+            del packets
+            continue
+
+        # ---- sharded over the run's GPUs ----------------------------------------------------------
+        from fast_kernels.dist import ShardedW4A16Linear, column_shard_packets, row_shard_packets
+
         shard = (column_shard_packets if mode == "column" else row_shard_packets)(
-            packets, n=shape.n, k=shape.k, group_size=128, rank=rank, world=world).contiguous()
-        del q, alpha, beta, packets
-        copies = max(2, min(8, int(400e6 // shard.numel()) + 1))
-        gen = torch.Generator().manual_seed(7)
-        shards = [shard] + [shard[torch.randperm(shard.shape[0], generator=gen).to(device)].contiguous()
-                            for _ in range(copies - 1)]
+            packets, n=shape.n, k=shape.k, group_size=128, rank=rank, world=world).contiguous().clone()
+        del packets
+        torch.cuda.empty_cache()
+        count = max(2, min(8, int(400e6 // shard.numel()) + 1))
+        shards = [shard] + [shard.clone() for _ in range(count - 1)]
         for exchange in ("nccl", "peer"):
             layers = [ShardedW4A16Linear(s, n=shape.n, k=shape.k, group_size=128, mode=mode,
                                          dtype=torch.bfloat16, exchange=exchange, packets_are_local=True,
                                          max_batch=1) for s in shards]
+            result = None
             for layer in layers:  # eager warm-up (function attributes, communicators)
-                layer(act)
+                result = layer(act)
             torch.cuda.synchronize(device)
+            # every layer object holds the same weights: check the last one's result
+            got = result[:, cols].float().cpu().numpy()
+            err = oracle.max_rel_err(got, y64)
+            bits = result.view(torch.int16).to(torch.int64)
+            checksum = torch.stack([bits.sum(), (bits * torch.arange(1, bits.numel() + 1, device=device)).sum()])
+            gathered = [torch.empty_like(checksum) for _ in range(world)]
+            dist.all_gather(gathered, checksum)
+            ranks_agree = all(torch.equal(g, checksum) for g in gathered)
             dist.barrier()
             mode_used = "cuda graph"
             try:
@@ -435,13 +700,43 @@ def _sharded_layers(torch, dist, capi, device, world: int, rank: int, peak_gbs: 
             us = float(t.item()) * 1e3 / (reps * len(layers))
             total_gbs = shape.algorithmic_bytes() / (us * 1e-6) / 1e9
             results.append({"layer": shape.name, "n": shape.n, "k": shape.k, "split": mode, "exchange": exchange,
-                            "us_per_call": us, "aggregate_gbs": total_gbs,
-                            "frac_of_n_gpu_peak": total_gbs / (peak_gbs * world), "launch": mode_used,
-                            "weight_copies": len(layers)})
+                            "gpus": world, "us_per_call": us, "aggregate_gbs": total_gbs,
+                            "frac_of_n_gpu_peak": total_gbs / (peak_gbs * world), "max_rel_err": err,
+                            "ranks_bit_equal": ranks_agree, "speedup_vs_1gpu": one_gpu_us / us,
+                            "launch": mode_used, "weight_copies": len(layers)})
+            status = capi.device_status()
+            if err > 1e-2 or not ranks_agree or status != 0:
+                raise SystemExit(f"sharded_layers: {shape.name} {mode}/{exchange} on {world} GPUs: max_rel_err "
+                                 f"{err:.3e}, ranks bit-equal {ranks_agree}, device status {status}")
             del layers
         del shards, shard
         torch.cuda.empty_cache()
     return results
+
+
+def _kernel_table(capi, per_layer: list[dict], ms_per_step: float) -> list[dict]:
+    """Per kernel (template instantiation): launches per step, time share and achieved bandwidth,
+    from the per-shape timings."""
+    table: dict[str, dict] = {}
+    for row in per_layer:
+        name = capi.describe_plan(1, row["n"], row["k"], 128, capi.DTYPE_BF16).split(" grid=")[0]
+        entry = table.setdefault(name, {"name": name, "launches_per_step": 0, "us_per_step": 0.0,
+                                        "bytes_per_step": 0, "layers": []})
+        entry["launches_per_step"] += NUM_LAYERS
+        entry["us_per_step"] += NUM_LAYERS * row["us_per_call"]
+        entry["bytes_per_step"] += NUM_LAYERS * row["algorithmic_bytes"]
+        entry["layers"].append(row["name"])
+    peak_gbs, _ = _measured_peak()
+    out = []
+    for entry in table.values():
+        us_per_call = entry["us_per_step"] / entry["launches_per_step"]
+        achieved = entry["bytes_per_step"] / (entry["us_per_step"] * 1e-6) / 1e9
+        out.append({"name": entry["name"], "layers": entry["layers"],
+                    "launches_per_step": entry["launches_per_step"], "us_per_call": us_per_call,
+                    "algorithmic_bytes_per_launch": entry["bytes_per_step"] / entry["launches_per_step"],
+                    "share_of_step": entry["us_per_step"] / (ms_per_step * 1e3),
+                    "achieved": achieved, "frac": achieved / peak_gbs})
+    return sorted(out, key=lambda e: -e["share_of_step"])
 
 
 def run_ours(args) -> int:
@@ -465,19 +760,25 @@ def run_ours(args) -> int:
     torch.cuda.synchronize(device)
     graph = layers.capture()
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         graph.replay()
     torch.cuda.synchronize(device)
 
-    if world > 1:
-        dist.barrier()
+    # R timed regions of exactly `steps` steps each; the headline is the median region
+    regions = []
     with ClockSampler(local_rank) as clocks:
-        seconds = _time_graph(torch, graph, args.steps, device)
-    if world > 1:
-        dist.barrier()
-        t = torch.tensor([seconds], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        seconds = float(t.item())
+        for _ in range(max(1, args.regions)):
+            if world > 1:
+                dist.barrier()
+            seconds = _time_graph(torch, graph, args.steps, device)
+            if world > 1:
+                dist.barrier()
+                t = torch.tensor([seconds], dtype=torch.float64, device=device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                seconds = float(t.item())
+            regions.append(seconds)
+    seconds = statistics.median(regions)
 
     status = capi.device_status()
     if status != 0:
@@ -496,12 +797,13 @@ def run_ours(args) -> int:
         for _ in range(3):
             sub_graph.replay()
         reps = max(4, args.steps // 4)
-        sub_seconds = _time_graph(torch, sub_graph, reps, device)
+        sub_seconds = min(_time_graph(torch, sub_graph, reps, device) for _ in range(3))
         us = sub_seconds * 1e6 / (reps * len(subset))
         gbs = shape.algorithmic_bytes() / (us * 1e-6) / 1e9
         per_layer.append({"name": shape.name, "n": shape.n, "k": shape.k, "us_per_call": us,
                           "achieved_gbs": gbs, "frac_of_peak": gbs / peak_gbs,
-                          "algorithmic_bytes": shape.algorithmic_bytes()})
+                          "algorithmic_bytes": shape.algorithmic_bytes(),
+                          "kernel": capi.describe_plan(1, shape.n, shape.k, 128, capi.DTYPE_BF16)})
 
     e2e_steps = max(2, min(args.steps, 20))
     e2e = _e2e(torch, layers, e2e_steps, device)
@@ -512,20 +814,32 @@ def run_ours(args) -> int:
         e2e_seconds = float(t.item())
     e2e_value = step_bytes * world * e2e_steps / e2e_seconds / 1e12
 
+    pack = layers.pack
+    del graph, layers
+    torch.cuda.empty_cache()
+
     sharded = None
-    if world > 1 and not args.no_sharded:
+    if not args.no_sharded:
         sharded = _sharded_layers(torch, dist, capi, device, world, rank, peak_gbs)
 
+    extra = {}
+    if world == 1 and not args.no_extras:
+        extra["configs"] = _configs_leg(torch, capi, device, peak_gbs)
+        extra["reference_gpu"] = _reference_gpu_leg(torch, capi, device)
+
     if rank == 0:
-        achieved_gbs = step_bytes * args.steps / seconds / 1e9  # this rank's kernels, gaps included
+        ms_per_step = seconds * 1e3 / args.steps
+        step_gbs = step_bytes * args.steps / seconds / 1e9  # this rank's kernels, gaps included
+        kernels = _kernel_table(capi, per_layer, ms_per_step)
+        top = kernels[0]
         line = {
             "metric": METRIC,
             "value": value,
             "unit": UNIT,
             "n_gpus": world,
             "steps": args.steps,
-            "warmup": max(args.warmup, 3),
-            "ms_per_step": seconds * 1e3 / args.steps,
+            "warmup": warmup,
+            "ms_per_step": ms_per_step,
             "us_per_call": seconds * 1e6 / (args.steps * calls_per_step),
             "higher_is_better": True,
             "scaling": "weak",
@@ -533,22 +847,38 @@ def run_ours(args) -> int:
             "dtype": "bf16",
             "data": "synthetic",
             "config": _config(world),
+            "regions": {
+                "count": len(regions),
+                "steps_each": args.steps,
+                "ms_per_step_median": ms_per_step,
+                "ms_per_step_min": min(regions) * 1e3 / args.steps,
+                "ms_per_step_max": max(regions) * 1e3 / args.steps,
+                "value_min": step_bytes * world * args.steps / max(regions) / 1e12,
+                "value_max": step_bytes * world * args.steps / min(regions) / 1e12,
+            },
             "roofline": {
                 "bound": "hbm",
-                "achieved": achieved_gbs,
+                # the kernel with the largest share of the step: its algorithmic bytes per launch
+                # over its average launch duration inside its own back-to-back graph
+                "kernel": top["name"],
+                "achieved": top["achieved"],
                 "peak": peak_gbs,
                 "unit": "GB/s",
-                "frac": achieved_gbs / peak_gbs,
+                "frac": top["frac"],
                 "peak_source": f"{peak_kind} (STREAM-style copy)",
-                "frac_of_nominal_8tbs": achieved_gbs / 8000.0,
-                "kernel": "w4a16_gemv_stream_kernel<128, 1, UnpackBF16>",
-                "algorithmic_bytes_per_launch_avg": step_bytes / calls_per_step,
-                # DRAM bytes per average launch: the algorithmic bytes times the ratio that one ncu
-                # capture each of the largest and the smallest layer gave (dram read + write over
-                # algorithmic bytes: 1.002 and 1.004; the kernel reads every packet exactly once)
-                "traffic": NCU_TRAFFIC_RATIO * step_bytes / calls_per_step,
+                "frac_of_nominal_8tbs": top["achieved"] / 8000.0,
+                "algorithmic_bytes_per_launch": top["algorithmic_bytes_per_launch"],
+                # DRAM bytes per launch: the algorithmic bytes times the ratio that one ncu capture
+                # each of the largest and the smallest layer gave (dram read + write over
+                # algorithmic bytes: 1.002 and 1.004; the kernels read every packet exactly once)
+                "traffic": NCU_TRAFFIC_RATIO * top["algorithmic_bytes_per_launch"],
                 "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of two layer shapes "
-                                  "(ratio to algorithmic bytes 1.002-1.004), scaled to the average launch",
+                                  "(ratio to algorithmic bytes 1.002-1.004), scaled to this kernel's average launch",
+                "step": {"achieved": step_gbs, "frac": step_gbs / peak_gbs,
+                         "frac_of_nominal_8tbs": step_gbs / 8000.0,
+                         "algorithmic_bytes_per_launch_avg": step_bytes / calls_per_step,
+                         "note": "whole step, gaps between launches included"},
+                "kernels": kernels,
                 "per_layer": per_layer,
             },
             "e2e": {
@@ -557,19 +887,28 @@ def run_ours(args) -> int:
                 "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
                 "us_per_call": e2e_seconds * 1e6 / (e2e_steps * calls_per_step),
-                "host_enqueue_us_per_call": e2e["host_seconds"] * 1e6 / (e2e_steps * calls_per_step),
                 "steps": e2e_steps,
-                "api": "C ABI fk_w4a16_gemv_host per call: pinned host activations in, pinned host result out",
+                "api": "C ABI fk_w4a16_gemv_host per GEMV (pinned host activations in, pinned host result out); "
+                       "the step's 128 calls recorded once into a CUDA graph and replayed",
+                "eager": {
+                    "value": step_bytes * e2e_steps / e2e["eager_seconds"] / 1e12,
+                    "us_per_call": e2e["eager_seconds"] * 1e6 / (e2e_steps * calls_per_step),
+                    "host_enqueue_us_per_call": e2e["host_seconds"] * 1e6 / (e2e_steps * calls_per_step),
+                    "note": "the same calls issued one by one from Python (ctypes), this rank",
+                },
             },
             "gpu_launches": calls_per_step * args.steps,
             "clocks": clocks.summary(),
+            "pack": pack,
         }
         if sharded is not None:
             line["sharded_layers"] = {
                 "note": "strong scaling of single large layers over this run's GPUs (N-split + gather, "
-                        "K-split + reduce); us_per_call is the max over ranks",
+                        "K-split + reduce) against the same layer on one GPU; us_per_call is the max over ranks; "
+                        "max_rel_err is against the fp64 oracle on a 512-column slice",
                 "results": sharded,
             }
+        line.update(extra)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = _cpu_baseline_leg()
         print(json.dumps(line), flush=True)
@@ -584,15 +923,18 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=None)
     parser.add_argument("--warmup", type=int, default=None)
+    parser.add_argument("--regions", type=int, default=15, help="timed regions of --steps steps each")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu-baseline", action="store_true", help="skip the ~10 s CPU baseline leg")
-    parser.add_argument("--no-sharded", action="store_true", help="N > 1: skip the sharded-layer measurements")
+    parser.add_argument("--no-sharded", action="store_true", help="skip the sharded-layer measurements")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the other configurations and the reference's GPU kernels")
     args = parser.parse_args()
     if args.impl == "reference":
         args.steps = 10 if args.steps is None else args.steps
         args.warmup = 1 if args.warmup is None else args.warmup
         return run_reference_arm(args)
-    args.steps = 200 if args.steps is None else args.steps
+    args.steps = 100 if args.steps is None else args.steps
     args.warmup = 5 if args.warmup is None else args.warmup
     return run_ours(args)
 

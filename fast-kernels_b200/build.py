@@ -71,6 +71,33 @@ def build_library(force: bool = False) -> Path:
     return target
 
 
+def build_python_module_without_cuda(out_dir: Path) -> Path:
+    """A `_native` module built WITHOUT CUDA into `out_dir`: same names and keyword arguments,
+    every op raises RuntimeError("fast-kernels was built without CUDA support"), and
+    build_info()["compiled_with_cuda"] is False -- the contract of the reference's CPU-only build
+    (csrc/bindings/python_module.cpp:241-287 there). Needs only g++ and pybind11."""
+    import pybind11
+
+    out_dir.mkdir(parents=True, exist_ok=True)
+    suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+    target = out_dir / f"_native{suffix}"
+    cxx = shutil.which("g++") or "g++"
+    version = subprocess.run([cxx, "-dumpfullversion"], capture_output=True, text=True).stdout.strip()
+    _run(
+        [
+            cxx, "-O1", "-std=c++20", "-shared", "-fPIC", "-fvisibility=hidden",
+            f"-DFK_PROJECT_VERSION=\"{VERSION}\"", "-DFK_COMPILED_WITH_CUDA=0",
+            "-DFK_CXX_COMPILER_ID=\"GNU\"", f"-DFK_CXX_COMPILER_VERSION=\"{version}\"",
+            "-DFK_CUDA_COMPILER_VERSION=\"\"", "-DFK_CUDA_ARCHITECTURES=\"\"",
+            "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", CSRC,
+            "-o", target,
+            CSRC / "bindings" / "python_module.cpp",
+            CSRC / "ops" / "decode_quant_linear" / "arc_w4a16_nocuda.cpp",
+        ]
+    )
+    return target
+
+
 def build_python_module(force: bool = False) -> Path:
     """fast_kernels._native: the reference's pybind11 surface over the C++ launchers."""
     import pybind11
@@ -147,7 +174,12 @@ def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--force", action="store_true", help="rebuild even if outputs are up to date")
     parser.add_argument("--oracle", action="store_true", help="also build the CPU oracle / reference .so")
+    parser.add_argument("--no-cuda", metavar="DIR", default=None,
+                        help="build only a CUDA-less _native module into DIR (every op raises)")
     ns = parser.parse_args()
+    if ns.no_cuda is not None:
+        build_python_module_without_cuda(Path(ns.no_cuda))
+        return 0
     build_all(force=ns.force, oracle=ns.oracle)
     return 0
 

@@ -11,8 +11,14 @@
 #include <cstdint>
 #include <string>
 
-#include "fk_w4a16.h"
 #include "ops/decode_quant_linear/arc_w4a16.h"
+
+#ifndef FK_COMPILED_WITH_CUDA
+#define FK_COMPILED_WITH_CUDA 1
+#endif
+#if FK_COMPILED_WITH_CUDA
+#include "fk_w4a16.h"
+#endif
 
 namespace py = pybind11;
 namespace dql = fast_kernels::decode_quant_linear;
@@ -40,12 +46,16 @@ PYBIND11_MODULE(_native, m) {
   m.def("build_info", []() {
     py::dict info;
     info["project_version"] = std::string(FK_PROJECT_VERSION);
-    info["compiled_with_cuda"] = true;
+    info["compiled_with_cuda"] = FK_COMPILED_WITH_CUDA != 0;
     info["cxx_compiler_id"] = std::string(FK_CXX_COMPILER_ID);
     info["cxx_compiler_version"] = std::string(FK_CXX_COMPILER_VERSION);
     info["cuda_compiler_version"] = std::string(FK_CUDA_COMPILER_VERSION);
     info["cuda_architectures"] = std::string(FK_CUDA_ARCHITECTURES);
+#if FK_COMPILED_WITH_CUDA
     info["kernel_library_version"] = std::string(fk_w4a16_version());
+#else
+    info["kernel_library_version"] = std::string("none");
+#endif
     return info;
   });
 
@@ -167,11 +177,19 @@ PYBIND11_MODULE(_native, m) {
   m.attr("ELEMENT_FLOAT16") = dql::kElementFloat16;
   m.attr("ELEMENT_BFLOAT16") = dql::kElementBFloat16;
   m.def("arc_packet_stride_bytes", [](int group_size) {
+#if FK_COMPILED_WITH_CUDA
     const int stride = fk_w4a16_packet_stride_bytes(group_size);
     if (stride < 0) {
       throw py::value_error(fk_w4a16_last_error());
     }
     return stride;
+#else
+    // pure arithmetic (reference: expected_packet_stride_bytes, arc_w4a16.cu:23-26)
+    if (group_size != 32 && group_size != 64 && group_size != 128) {
+      throw py::value_error("group_size must be 32, 64 or 128");
+    }
+    return (64 * group_size) + 512;
+#endif
   }, py::arg("group_size"));
   m.def("arc_w4a16_workspace_bytes", &dql::arc_w4a16_workspace_bytes, py::arg("batch"),
         py::arg("n"), py::arg("k"), py::arg("group_size"));

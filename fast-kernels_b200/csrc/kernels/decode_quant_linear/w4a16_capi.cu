@@ -8,6 +8,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <atomic>
 #include <mutex>
 #include <sstream>
@@ -21,6 +22,7 @@
 #include "w4a16_gemv_wmma.cuh"
 #include "w4a16_launch.h"
 #include "w4a16_tc5_plan.cuh"
+#include "w4a16_umma_plan.cuh"
 #include "w4a16_prep.cuh"
 
 #ifndef FK_W4A16_VERSION
@@ -185,6 +187,7 @@ constexpr size_t kExchangeBytes = 768 * 1024;
 constexpr size_t kHeaderBytes = kTicketBytes + kExchangeBytes;
 constexpr int kMaxWarps = 16;
 constexpr int kMaxStages = 8;
+constexpr int kUmmaDefaultMinBatch = 0;  // 0: the pipelined tcgen05 kernel is opt-in
 
 struct LaunchConfig {
   int warps = 0;
@@ -208,6 +211,35 @@ const LaunchConfig& launch_config() {
   return g_config;
 }
 
+// Tuning knobs of the launch plan. Each starts from its environment variable, read ONCE (a
+// getenv per knob on every call costs more host time than the launch itself), and can be
+// changed at run time with fk_w4a16_set_tuning().
+struct Tuning {
+  int mma_min_batch = 0;   // FK_W4A16_MMA_MIN_BATCH: smallest batch for the mma.sync kernel (0 = rule)
+  int cluster_min = 0;     // FK_W4A16_CLUSTER_MIN: smallest cluster size tried (0 = 2)
+  int cluster_size = 0;    // FK_W4A16_CLUSTER_SIZE: forced cluster size (0 = rule)
+  int wmma = 0;            // FK_W4A16_WMMA: batches 1-2 on the warp-level mma.sync form
+  int umma_min_batch = -1; // FK_W4A16_UMMA_MIN_BATCH: smallest batch for the pipelined tcgen05 kernel
+                           // (-1 = built-in default, 0 = never)
+  int peer_wait_ms = 2000; // FK_W4A16_PEER_WAIT_MS: how long a multi-GPU call waits for the other GPUs
+};
+Tuning g_tuning;
+std::once_flag g_tuning_once;
+Tuning& tuning() {
+  std::call_once(g_tuning_once, [] {
+    g_tuning.mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH");
+    g_tuning.cluster_min = env_int("FK_W4A16_CLUSTER_MIN");
+    g_tuning.cluster_size = env_int("FK_W4A16_CLUSTER_SIZE");
+    g_tuning.wmma = env_int("FK_W4A16_WMMA");
+    const char* text = std::getenv("FK_W4A16_UMMA_MIN_BATCH");
+    g_tuning.umma_min_batch = text == nullptr ? -1 : std::atoi(text);
+    if (env_int("FK_W4A16_PEER_WAIT_MS") > 0) {
+      g_tuning.peer_wait_ms = env_int("FK_W4A16_PEER_WAIT_MS");
+    }
+  });
+  return g_tuning;
+}
+
 int m_tile_for_batch(int batch) { return batch <= 1 ? 1 : (batch <= 2 ? 2 : 4); }
 
 struct Plan {
@@ -224,6 +256,7 @@ struct Plan {
   bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
   bool wmma = false;          // batch <= 2: the stream kernel with its inner product on mma.sync
   bool tc5 = false;           // the tcgen05 kernel: `warps` counts warpgroups, rows in {1,2,4,8,16}
+  bool umma = false;          // the pipelined tcgen05 kernel: one run per CTA, rows in {1,2,4,8,16}
   size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
 
@@ -253,9 +286,13 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   // Batches 3 and 4 also go to the tensor-core kernel when the layer is large enough to hide its
   // activation prepass (measured on B200: 23 us against 35 on 28672 x 4096, 18.5 against 22 on
   // 4096 x 14336, but 13 against 7.7 on 4096 x 4096).
-  const int mma_min_batch = env_int("FK_W4A16_MMA_MIN_BATCH") > 0
-                                ? env_int("FK_W4A16_MMA_MIN_BATCH")
-                                : (total_packets >= 3072 ? 3 : 5);
+  // ... and batches of 2 as well on layers too wide for the cluster kernel (28672 x 8192: 32.2
+  // against 37.3 us; 28672 x 4096: 20.5 against 22.6), where the CUDA-core kernel pays its FMAs
+  // twice; the cluster kernel keeps batch 2 (4096 x 14336: 13.5 against 16.6 us).
+  const bool cluster_shape = static_cast<long long>(n / kTileCols) * 2 <= sm_count;
+  const int mma_min_batch = tuning().mma_min_batch > 0 ? tuning().mma_min_batch
+                            : total_packets >= 3072    ? (cluster_shape ? 3 : 2)
+                                                       : 5;
   if (batch >= mma_min_batch && !(cuda_cores_only && batch <= 4)) {
     plan.tensor_cores = true;
     plan.m_tile = batch <= 8 ? 8 : 16;
@@ -299,12 +336,12 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   // finish even on large layers (8192 x 8192: 10.3 against 12.6 us; 8192 x 28672: 25.7 / 26.2).
   const int tiles = n / kTileCols;
   const int groups = k / group_size;
-  const int min_cluster = env_int("FK_W4A16_CLUSTER_MIN") > 0 ? env_int("FK_W4A16_CLUSTER_MIN") : 2;
+  const int min_cluster = tuning().cluster_min > 0 ? tuning().cluster_min : 2;
   if (allow_cluster && cluster_mode_enabled() && cfg.ctas == 0 && tiles * min_cluster <= sm_count) {
     int cluster = sm_count / tiles;
     cluster = cluster >= 8 ? 8 : (cluster >= 4 ? 4 : 2);
-    if (env_int("FK_W4A16_CLUSTER_SIZE") > 0) {
-      cluster = env_int("FK_W4A16_CLUSTER_SIZE");
+    if (tuning().cluster_size > 0) {
+      cluster = tuning().cluster_size;
     }
     cluster = cluster > groups ? groups : cluster;
     if (cluster >= 2) {
@@ -348,7 +385,7 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
 
   // Batches of 1 and 2 may take the warp-level MMA form of the stream kernel (opt-in while it is
   // being measured): same plan, slightly larger ring stages.
-  plan.wmma = plan.m_tile <= 2 && env_int("FK_W4A16_WMMA") != 0;
+  plan.wmma = plan.m_tile <= 2 && tuning().wmma != 0;
   const int ring_stage_bytes = plan.wmma ? wmma_stage_bytes(group_size) : stage_bytes;
   auto smem_plan = [&](int w, int s) {
     return plan.wmma ? wmma_smem_plan(w, s, group_size, plan.m_tile)
@@ -398,14 +435,70 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   return plan;
 }
 
-std::atomic<int> g_variant{-1};  // -1: not set, take FK_W4A16_TC5 from the environment
+std::atomic<int> g_variant{-1};  // -1: not set, take FK_W4A16_TC5 / FK_W4A16_UMMA from the environment
 bool tc5_enabled() {
   const int variant = g_variant.load(std::memory_order_relaxed);
   if (variant >= 0) {
-    return variant == 1;
+    return variant == FK_W4A16_VARIANT_TCGEN05;
   }
   static const bool from_env = env_int("FK_W4A16_TC5") != 0;
   return from_env;
+}
+// 1: every batch size takes the pipelined tcgen05 kernel; 0: none does; -1: the default rule.
+int umma_forced() {
+  const int variant = g_variant.load(std::memory_order_relaxed);
+  if (variant >= 0) {
+    return variant == FK_W4A16_VARIANT_TCGEN05_PIPELINED ? 1 : (variant == FK_W4A16_VARIANT_AUTO ? -1 : 0);
+  }
+  static const int from_env = std::getenv("FK_W4A16_UMMA") == nullptr ? -1 : (env_int("FK_W4A16_UMMA") != 0 ? 1 : 0);
+  return from_env;
+}
+
+// Which problems take the pipelined tcgen05 kernel by default (FK_W4A16_UMMA_MIN_BATCH overrides
+// the batch threshold; 0 there means "never").
+bool umma_wanted(int batch, int n, int k, int group_size) {
+  const int forced = umma_forced();
+  if (forced >= 0) {
+    return forced == 1;
+  }
+  (void)n; (void)k; (void)group_size;
+  const int min_batch = tuning().umma_min_batch < 0 ? kUmmaDefaultMinBatch : tuning().umma_min_batch;
+  return min_batch > 0 && batch >= min_batch;
+}
+
+// Plan of the pipelined tcgen05 kernel: one run of the packet stream per CTA.
+Plan make_umma_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
+                    const LaunchConfig& cfg) {
+  Plan plan;
+  plan.umma = true;
+  const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
+  plan.total_packets = static_cast<uint32_t>(total_packets);
+  plan.m_tile = umma_rows_for_batch(batch);
+  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
+  int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
+  ctas = ctas > 256 ? 256 : ctas;
+  const long long workers = ctas < total_packets ? ctas : total_packets;
+  plan.warps = 1;
+  plan.grid_x = static_cast<int>(workers);
+  plan.active_warps = static_cast<int>(workers);
+  const long long longest_run = (total_packets + workers - 1) / workers;
+  int wanted = cfg.stages > 0 ? cfg.stages : kUmmaMaxStages;
+  wanted = wanted > kUmmaMaxStages ? kUmmaMaxStages : wanted;
+  wanted = wanted > longest_run ? static_cast<int>(longest_run) : wanted;
+  plan.stages = 0;
+  for (int candidate = wanted; candidate >= 1; --candidate) {
+    if (umma_smem_plan(candidate, group_size, plan.m_tile).total <= static_cast<uint32_t>(max_smem)) {
+      plan.stages = candidate;
+      break;
+    }
+  }
+  plan.smem_bytes = umma_smem_plan(plan.stages < 1 ? 1 : plan.stages, group_size, plan.m_tile).total;
+  // one CTA per SM: each allocates all of the SM's tensor memory
+  const size_t floor_bytes = (static_cast<size_t>(max_smem) / 2) + 1024;
+  plan.smem_bytes = plan.smem_bytes < floor_bytes ? floor_bytes : plan.smem_bytes;
+  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
+                       (plan.m_tile * kTileCols) * sizeof(float);
+  return plan;
 }
 
 // Plan of the tcgen05 kernel: one run per warpgroup.
@@ -674,8 +767,36 @@ int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas) {
   return FK_W4A16_OK;
 }
 
+int fk_w4a16_set_tuning(const char* name, int value) {
+  if (name == nullptr) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "name must not be null");
+  }
+  Tuning& t = tuning();
+  const std::string key(name);
+  if (key == "mma_min_batch") {
+    t.mma_min_batch = value;
+  } else if (key == "cluster_min") {
+    t.cluster_min = value;
+  } else if (key == "cluster_size") {
+    t.cluster_size = value;
+  } else if (key == "wmma") {
+    t.wmma = value;
+  } else if (key == "umma_min_batch") {
+    t.umma_min_batch = value;
+  } else if (key == "peer_wait_ms") {
+    if (value <= 0 || value > 10000) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "peer_wait_ms must be between 1 and 10000");
+    }
+    t.peer_wait_ms = value;
+  } else {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown tuning knob: " + key);
+  }
+  return FK_W4A16_OK;
+}
+
 int fk_w4a16_set_variant(int variant) {
-  if (variant != FK_W4A16_VARIANT_AUTO && variant != FK_W4A16_VARIANT_TCGEN05) {
+  if (variant != FK_W4A16_VARIANT_AUTO && variant != FK_W4A16_VARIANT_TCGEN05 &&
+      variant != FK_W4A16_VARIANT_TCGEN05_PIPELINED && variant != FK_W4A16_VARIANT_CLASSIC) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown kernel variant");
   }
   g_variant.store(variant, std::memory_order_relaxed);
@@ -743,9 +864,47 @@ size_t fk_w4a16_workspace_bytes(int batch, int n, int k, int group_size) {
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
   const Plan tc5_plan =
       make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  const size_t a = workspace_bytes_for(plan);
-  const size_t b = workspace_bytes_for(tc5_plan);
-  return a > b ? a : b;
+  const Plan umma_plan =
+      make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
+  size_t need = workspace_bytes_for(plan);
+  need = need > workspace_bytes_for(tc5_plan) ? need : workspace_bytes_for(tc5_plan);
+  need = need > workspace_bytes_for(umma_plan) ? need : workspace_bytes_for(umma_plan);
+  return need;
+}
+
+int fk_w4a16_describe_plan(int batch, int n, int k, int group_size, int dtype, char* text,
+                           size_t capacity) {
+  FK_TRY(check_dimensions(batch, n, k, group_size));
+  FK_TRY(check_dtype(dtype));
+  if (text == nullptr || capacity == 0) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "text must point to a buffer");
+  }
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  const bool use_umma = umma_wanted(batch, n, k, group_size);
+  const Plan plan =
+      use_umma ? make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
+      : tc5_enabled()
+          ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
+          : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
+                      /*allow_cluster=*/true, /*cuda_cores_only=*/false);
+  const char* kernel = plan.umma            ? "w4a16_gemm_umma_kernel"
+                       : plan.tc5           ? "w4a16_gemm_tc5_kernel"
+                       : plan.tensor_cores  ? "w4a16_gemm_mma_kernel"
+                       : plan.wmma          ? "w4a16_gemv_wmma_kernel"
+                       : plan.cluster_size > 1 ? "w4a16_gemv_cluster_kernel"
+                                               : "w4a16_gemv_stream_kernel";
+  std::ostringstream oss;
+  oss << kernel << "<" << group_size << ", " << plan.m_tile << ", "
+      << (dtype == FK_W4A16_DTYPE_BF16 ? "UnpackBF16" : "UnpackF16") << "> grid=" << plan.grid_x << "x"
+      << plan.row_tiles << " cluster=" << plan.cluster_size << " warps=" << plan.warps
+      << " stages=" << plan.stages << " smem=" << plan.smem_bytes;
+  const std::string line = oss.str();
+  if (line.size() + 1 > capacity) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "text buffer is too small");
+  }
+  std::memcpy(text, line.c_str(), line.size() + 1);
+  return FK_W4A16_OK;
 }
 
 int fk_w4a16_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
@@ -814,6 +973,14 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   if (args->residual != nullptr) {
     FK_TRY(check_pointer(args->residual, "residual", 8));
   }
+  if (args->reduce_slots != 0) {
+    if (args->reduce_slots < 0 || args->reduce_slots > FK_W4A16_MAX_PEERS + 1 || args->local_signal == nullptr) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "reduce_slots must be between 1 and 8 and needs the exchange counters (local_signal)");
+    }
+    FK_TRY(check_pointer(args->reduce_input, "reduce_input", 16));
+    FK_TRY(check_pointer(args->reduce_output, "reduce_output", 8));
+  }
 
   DeviceInfo* info = nullptr;
   FK_TRY(device_info(&info));
@@ -830,11 +997,14 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
     }
   }
   // The fused RMSNorm lives in the CUDA-core kernels (stream and cluster).
+  const bool use_umma = !normalise && !small_batch_on_cuda_cores && umma_wanted(batch, n, k, group_size);
   const Plan plan =
-      (tc5_enabled() && !normalise)
+      use_umma
+          ? make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
+      : (tc5_enabled() && !normalise)
           ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
           : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
-                      /*allow_cluster=*/args->local_signal == nullptr,
+                      /*allow_cluster=*/true,
                       /*cuda_cores_only=*/normalise || small_batch_on_cuda_cores);
   if (plan.stages < 1) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch config does not fit in shared memory");
@@ -860,7 +1030,6 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   params.packets = static_cast<const uint8_t*>(args->packets);
   params.out = args->output;
   params.tickets = static_cast<int*>(args->workspace);
-  params.exit_count = static_cast<int*>(args->workspace) + (kTicketCapacity - 1);
   params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(args->workspace) + header_bytes);
   // Pair exchange: one area of m_tile x 128 64-bit words per boundary between neighbouring CTAs.
   params.exchange = nullptr;
@@ -871,6 +1040,7 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
       gated ? static_cast<size_t>(batch) * (n / 2) * sizeof(unsigned long long) : 0;
   const bool wants_exchange =
       with_exchange_area && !plan.tensor_cores && !plan.tc5 && plan.cluster_size == 1 && plan.m_tile <= 4;
+  // (the pipelined tcgen05 kernel finishes split tiles like the packet-stream kernel does)
   if (!wants_exchange || exchange_bytes + gated_bytes > kExchangeBytes) {
     exchange_bytes = 0;  // split tiles take the ticket finish; the area is the epilogue's alone
   }
@@ -903,6 +1073,10 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   params.norm_eps = args->norm_eps;
   params.local_signal = args->local_signal;
   params.wait_value = args->wait_value;
+  params.peer_wait_ns = static_cast<unsigned long long>(tuning().peer_wait_ms) * 1000000ull;
+  params.reduce_input = args->reduce_input;
+  params.reduce_output = args->reduce_output;
+  params.reduce_slots = args->reduce_slots;
   params.m = batch;
   params.n = n;
   params.k = k;
@@ -918,6 +1092,23 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
                                       static_cast<double>(plan.total_packets));
   auto* s = static_cast<cudaStream_t>(args->stream);
   const int max_smem = info->max_smem_optin;
+  if (plan.umma) {
+    if (plan.smem_bytes > static_cast<size_t>(max_smem)) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch needs more shared memory than the device has");
+    }
+    UmmaLaunch launch{};
+    launch.group_size = group_size;
+    launch.rows = plan.m_tile;
+    launch.bf16 = args->dtype == FK_W4A16_DTYPE_BF16;
+    launch.grid_x = plan.grid_x;
+    launch.row_tiles = plan.row_tiles;
+    launch.smem_bytes = plan.smem_bytes;
+    launch.max_smem = max_smem;
+    launch.programmatic = pdl_enabled();
+    launch.stream = s;
+    FK_TRY_CUDA(launch_umma_kernel(params, launch));
+    return FK_W4A16_OK;
+  }
   if (plan.tc5) {
     if (plan.smem_bytes > static_cast<size_t>(max_smem)) {
       return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch needs more shared memory than the device has");
@@ -985,14 +1176,33 @@ int fk_w4a16_gemv(const void* activations, const void* packets, void* output, vo
 
 namespace {
 
-// Device-side address of `ptr` if it is mapped (pinned) host memory, else nullptr.
+// Device-side address of `ptr` if it is mapped (pinned) host memory, else nullptr. The driver
+// query costs about a microsecond, as much as a launch, so answers are remembered per calling
+// thread in a small direct-mapped table keyed by the host address (a registration is stable for
+// as long as the memory stays pinned; a caller that unpins a buffer and pins other memory at the
+// same address with a different mapping must not expect the zero-copy path to notice).
 void* mapped_host_address(const void* ptr) {
+  struct Entry {
+    const void* host = nullptr;
+    void* device = nullptr;
+  };
+  constexpr int kEntries = 64;
+  thread_local Entry table[kEntries];
+  Entry& entry = table[(reinterpret_cast<uintptr_t>(ptr) >> 6) % kEntries];
+  if (entry.host == ptr && ptr != nullptr) {
+    return entry.device;
+  }
   cudaPointerAttributes attrs{};
   if (cudaPointerGetAttributes(&attrs, ptr) != cudaSuccess) {
     (void)cudaGetLastError();
     return nullptr;
   }
-  return attrs.type == cudaMemoryTypeHost ? attrs.devicePointer : nullptr;
+  void* device = attrs.type == cudaMemoryTypeHost ? attrs.devicePointer : nullptr;
+  if (device != nullptr) {
+    entry.host = ptr;
+    entry.device = device;
+  }
+  return device;
 }
 
 bool host_zero_copy_enabled() {

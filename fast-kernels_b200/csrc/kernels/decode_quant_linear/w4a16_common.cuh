@@ -141,6 +141,35 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   return false;
 }
 
+// The same test with a suspend-time hint: the hardware may park the thread for up to `hint_ns`
+// and wakes it when the phase completes, so a waiting warp does not take issue slots from the
+// warps it is waiting for. For kernels whose warps wait on one another (warp-specialised
+// pipelines); a warp that waits only for its own copies loses nothing by polling.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+// Bounded: gives up after kParkedWaitRounds parks of up to kParkedWaitNs each (about a second).
+constexpr uint32_t kParkedWaitNs = 20000;
+constexpr uint32_t kParkedWaitRounds = 1u << 16;
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity) {
+  for (uint32_t round = 0; round < kParkedWaitRounds; ++round) {
+    if (mbar_try_wait_parked(bar, parity, kParkedWaitNs)) {
+      return true;
+    }
+  }
+  return false;
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -211,6 +211,7 @@ __global__ void __launch_bounds__(512, 1)
     }
   }
   trace_mark(5);
+  exchange_complete<E>(p);  // multi-GPU calls: signal every GPU, wait for all of them
 }
 
 }  // namespace fk_w4a16

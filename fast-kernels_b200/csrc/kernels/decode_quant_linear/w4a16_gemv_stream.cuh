@@ -94,13 +94,21 @@ struct GemvParams {
   // round16(norm_weight[k] * round16(x[k] * rsqrt(mean_k(x^2) + norm_eps))) per row.
   const void* norm_weight;  // [k] 16-bit
   float norm_eps;
-  // Exchange completion. When local_signal is set, the last CTA to leave adds 1 (system scope,
-  // after all of this GPU's stores) to local_signal and to every peer_signal, then stays until
-  // local_signal has reached wait_value -- i.e. until every GPU of the group has delivered.
+  // Exchange completion. When local_signal is set, every CTA, once its own stores are done, adds 1
+  // (system scope, released after those stores) to local_signal and to every peer_signal; the
+  // kernel does not complete before local_signal has reached wait_value x (CTAs of the grid),
+  // i.e. before every CTA of every GPU of the group has delivered. Every GPU of the group must
+  // therefore run the same launch shape (same problem on the same kind of device).
   unsigned int* peer_signal[kMaxPeers];
   unsigned int* local_signal;
   unsigned int wait_value;
-  int* exit_count;         // zero between calls; counts CTAs that have finished
+  unsigned long long peer_wait_ns;  // the wait gives up after this long and sets the status word
+  // Optional fused reduction behind the exchange (a K-split layer's sum over GPUs), or
+  // reduce_slots == 0: once everything has arrived, out16[m][n] = round16(sum over s <
+  // reduce_slots of reduce_input[s][m][n]), slots added in index order, each CTA a slice.
+  const float* reduce_input;        // [reduce_slots][m][n] fp32 in THIS GPU's memory
+  void* reduce_output;              // [m][n] 16-bit
+  int reduce_slots;
   int m, n, k;
   int num_groups;          // k / G
   int num_tiles;           // n / 128
@@ -580,6 +588,104 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 }
 
 // ---------------------------------------------------------------------------------------------
+// Exchange completion of a multi-GPU call (no-op when local_signal is null). Every thread of the
+// CTA calls it once, after the CTA's last output store.
+//
+// Signalling is per CTA, not per GPU: after a CTA barrier, thread 0 executes ONE system-scope
+// fence -- cumulative over the barrier, so it covers every thread's peer stores; a fence in every
+// thread costs tens of microseconds, system-scope fences of one SM do not overlap -- and then
+// adds 1 to the counter of every GPU with fire-and-forget reductions. No exit ticket, no "last
+// CTA": the slowest CTA's stores are the only thing the other GPUs ever wait for.
+// Who waits: without the fused reduction one thread of the grid (CTA 0) holds the kernel open
+// until the local counter shows every CTA of every GPU; with it, every CTA waits and then adds
+// its slice of the partial sums. Waits are bounded (peer_wait_ns), report through the status word
+// and need every CTA of the grid to be resident, which the launch plans guarantee (at most one
+// CTA per SM).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_system(unsigned int* counter) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+}
+__device__ __forceinline__ unsigned int load_counter_system(const unsigned int* counter) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+template <class E>
+__device__ __forceinline__ void exchange_complete(const GemvParams& p) {
+  if (p.local_signal == nullptr) {
+    return;
+  }
+  __shared__ int arrived_flag;
+  __syncthreads();
+  const unsigned int ctas_total = gridDim.x * gridDim.y;
+  const unsigned int target = p.wait_value * ctas_total;
+  const bool reduce = p.reduce_slots > 0;
+  const bool waiter = reduce || (blockIdx.x == 0 && blockIdx.y == 0);
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int peer = 0; peer < p.num_peers; ++peer) {
+      red_add_system(p.peer_signal[peer]);
+    }
+    red_add_system(p.local_signal);
+    if (waiter) {
+      bool arrived = false;
+      const unsigned long long start = global_timer_ns();
+      for (;;) {
+        const unsigned int seen = load_counter_system(p.local_signal);
+        if (static_cast<int>(seen - target) >= 0) {
+          arrived = true;
+          break;
+        }
+        if (global_timer_ns() - start > p.peer_wait_ns) {
+          break;
+        }
+        __nanosleep(40);
+      }
+      if (!arrived) {
+        atomicExch(p.status, static_cast<int>(kStatusPeerWaitTimeout));
+      }
+      __threadfence_system();
+      arrived_flag = arrived ? 1 : 0;
+    }
+  }
+  if (!reduce) {
+    return;
+  }
+  __syncthreads();
+  if (arrived_flag == 0) {
+    return;
+  }
+  // this CTA's slice of the [m][n] outputs, in units of 4 elements
+  const long long units = (static_cast<long long>(p.m) * p.n) >> 2;
+  const long long cta = (static_cast<long long>(blockIdx.y) * gridDim.x) + blockIdx.x;
+  const long long per_cta = (units + ctas_total - 1) / ctas_total;
+  const long long begin = cta * per_cta;
+  long long end = begin + per_cta;
+  end = end < units ? end : units;
+  const long long slot_units = units;
+  for (long long u = begin + threadIdx.x; u < end; u += blockDim.x) {
+    float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < p.reduce_slots; ++s) {
+      const float4 part = __ldcg(reinterpret_cast<const float4*>(p.reduce_input) + (s * slot_units) + u);
+      total.x += part.x;
+      total.y += part.y;
+      total.z += part.z;
+      total.w += part.w;
+    }
+    uint2 packed;
+    packed.x = static_cast<uint32_t>(E::from_float(total.x)) | (static_cast<uint32_t>(E::from_float(total.y)) << 16);
+    packed.y = static_cast<uint32_t>(E::from_float(total.z)) | (static_cast<uint32_t>(E::from_float(total.w)) << 16);
+    reinterpret_cast<uint2*>(p.reduce_output)[u] = packed;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // The finish shared by the GEMV kernels, run by every warp of a CTA after the CTA-wide barrier that
 // ends the runs: adds the per-warp partial-sum slots of each tile in warp order, stores tiles
 // that lie wholly inside the CTA's packet range, hands tiles shared with neighbouring CTAs to the
@@ -785,39 +891,7 @@ __device__ __forceinline__ void finish_cta(const GemvParams& p, const float* hea
   }
 
   // ---- exchange completion (multi-GPU calls only) ------------------------------------------
-  if (p.local_signal != nullptr) {
-    // One system-scope fence per CTA, by the thread that then counts the CTA as done: the barrier
-    // orders every thread's peer stores before it, and the fence is cumulative. (A fence in every
-    // thread costs tens of microseconds: system-scope fences of one SM do not overlap.)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      const unsigned int ctas_total = gridDim.x * gridDim.y;
-      const int finished = atomicAdd(p.exit_count, 1);
-      if (finished == static_cast<int>(ctas_total) - 1) {
-        __threadfence_system();
-        *p.exit_count = 0;
-        for (int peer = 0; peer < p.num_peers; ++peer) {
-          atomicAdd_system(p.peer_signal[peer], 1u);
-        }
-        atomicAdd_system(p.local_signal, 1u);
-        // Bounded wait for the other GPUs' deliveries (about two seconds at most).
-        bool arrived = false;
-        for (uint32_t spin = 0; spin < kPeerWaitLimit; ++spin) {
-          const unsigned int seen = *reinterpret_cast<volatile unsigned int*>(p.local_signal);
-          if (static_cast<int>(seen - p.wait_value) >= 0) {
-            arrived = true;
-            break;
-          }
-          __nanosleep(200);
-        }
-        if (!arrived) {
-          atomicExch(p.status, static_cast<int>(kStatusPeerWaitTimeout));
-        }
-        __threadfence_system();
-      }
-    }
-  }
+  exchange_complete<E>(p);
 }
 
 // Shared-memory plan of the stream kernel, used by host and device alike.

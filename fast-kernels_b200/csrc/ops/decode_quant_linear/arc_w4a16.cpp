@@ -29,8 +29,16 @@ void* as_ptr(std::uintptr_t value) { return reinterpret_cast<void*>(value); }
 
 // The reference's arc_w4a16_forward has no scratch parameter, so this layer keeps one workspace
 // per (device, stream): calls on one stream are ordered and can share it, calls on different
-// streams may overlap and must not. Buffers are allocated on first use (cudaMalloc: make that
-// first call outside any stream capture), only ever grow, and live until the process ends.
+// streams may overlap and must not. The rule for callers:
+//   * the FIRST call on a (device, stream) pair allocates the pair's workspace (cudaMalloc, one
+//     buffer of kFixedWorkspaceBytes, enough for every layer shape at batches up to 16) -- make
+//     that call outside stream capture; every later call allocates nothing and can be captured;
+//   * a problem that needs more than that (batches far above 16) makes the buffer grow: the
+//     stream is synchronised, the old buffer freed, a larger one allocated. Never under capture:
+//     there the call fails with std::runtime_error instead.
+// Buffers live until the process ends.
+constexpr std::size_t kFixedWorkspaceBytes = std::size_t{16} << 20;
+
 struct OwnedWorkspace {
   void* ptr = nullptr;
   std::size_t bytes = 0;
@@ -45,22 +53,44 @@ OwnedWorkspace workspace_for(std::size_t need, cudaStream_t stream) {
   }
   std::lock_guard<std::mutex> lock(mutex);
   OwnedWorkspace& slot = table[{device, stream}];
-  if (slot.bytes < need) {
-    // Round up generously so shape changes rarely reallocate. The old buffer is left alive:
-    // kernels already enqueued may still be using it.
-    const std::size_t bytes = need < (std::size_t{4} << 20) ? (std::size_t{4} << 20) : need * 2;
-    void* fresh = nullptr;
-    cudaError_t err = cudaMalloc(&fresh, bytes);
+  if (slot.bytes >= need) {
+    return slot;
+  }
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) {
+    (void)cudaGetLastError();
+    capture = cudaStreamCaptureStatusNone;
+  }
+  if (capture != cudaStreamCaptureStatusNone) {
+    throw std::runtime_error(
+        "arc_w4a16_forward: this stream's workspace is not allocated yet (or too small) and the "
+        "stream is being captured; make one call with this problem size outside capture first");
+  }
+  if (slot.ptr != nullptr) {
+    // Kernels already enqueued on this stream may still use the old buffer.
+    cudaError_t err = cudaStreamSynchronize(stream);
     if (err == cudaSuccess) {
-      err = cudaMemsetAsync(fresh, 0, bytes, stream);
+      err = cudaFree(slot.ptr);
     }
     if (err != cudaSuccess) {
-      throw std::runtime_error(std::string("workspace allocation failed: ") +
-                               cudaGetErrorString(err));
+      throw std::runtime_error(std::string("workspace release failed: ") + cudaGetErrorString(err));
     }
-    slot.ptr = fresh;
-    slot.bytes = bytes;
+    slot = OwnedWorkspace{};
   }
+  const std::size_t bytes = need <= kFixedWorkspaceBytes ? kFixedWorkspaceBytes : need + (need / 2);
+  void* fresh = nullptr;
+  cudaError_t err = cudaMalloc(&fresh, bytes);
+  if (err == cudaSuccess) {
+    err = cudaMemsetAsync(fresh, 0, bytes, stream);
+    if (err != cudaSuccess) {
+      (void)cudaFree(fresh);
+    }
+  }
+  if (err != cudaSuccess) {
+    throw std::runtime_error(std::string("workspace allocation failed: ") + cudaGetErrorString(err));
+  }
+  slot.ptr = fresh;
+  slot.bytes = bytes;
   return slot;
 }
 

@@ -25,6 +25,8 @@ EPILOGUE_NONE = 0
 EPILOGUE_SILU_MUL = 1
 VARIANT_AUTO = 0
 VARIANT_TCGEN05 = 1
+VARIANT_TCGEN05_PIPELINED = 2
+VARIANT_CLASSIC = 3
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfk_w4a16.so"
 
@@ -63,6 +65,9 @@ class GemvArgs(ctypes.Structure):
         ("epilogue", _c_int),
         ("norm_weight", _c_void_p),
         ("norm_eps", ctypes.c_float),
+        ("reduce_input", _c_void_p),
+        ("reduce_output", _c_void_p),
+        ("reduce_slots", _c_int),
     ]
 
 
@@ -85,6 +90,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
          _c_int, _c_int, _c_void_p],
     ),
     "fk_w4a16_set_variant": (_c_int, [_c_int]),
+    "fk_w4a16_describe_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_char_p, ctypes.c_size_t]),
+    "fk_w4a16_set_tuning": (_c_int, [ctypes.c_char_p, _c_int]),
     "fk_w4a16_gemv_host": (
         _c_int,
         [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_size_t, _c_int, _c_int,
@@ -167,3 +174,10 @@ def device_status() -> int:
     status = _c_int(0)
     check(load_library().fk_w4a16_device_status(ctypes.byref(status)))
     return int(status.value)
+
+
+def describe_plan(batch: int, n: int, k: int, group_size: int, dtype: int) -> str:
+    """One line naming the kernel (with template arguments) and launch geometry for a problem."""
+    text = ctypes.create_string_buffer(256)
+    check(load_library().fk_w4a16_describe_plan(batch, n, k, group_size, dtype, text, len(text)))
+    return text.value.decode()

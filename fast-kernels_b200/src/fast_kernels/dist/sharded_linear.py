@@ -13,9 +13,10 @@ Two exchanges:
 * ``exchange="nccl"``: ``all_gather_into_tensor`` / ``all_reduce`` on the group, enqueued on the
   GEMV's stream. Works on any backend (the CPU tests run it over gloo).
 * ``exchange="peer"`` (CUDA, one node): the GEMV kernel itself stores every finished tile into all
-  ranks' buffers through peer-mapped symmetric memory while it is still streaming weights, then
-  signals each rank and waits (bounded) until all ranks have delivered -- one kernel does compute
-  and exchange, no collective call. Results live in a double-buffered symmetric buffer: the tensor
+  ranks' buffers through peer-mapped symmetric memory while it is still streaming weights; every
+  CTA then signals every rank and the kernel waits (bounded) until all CTAs of all ranks have
+  delivered; a row split's sum over ranks happens in the same kernel -- one launch does compute,
+  exchange and reduction, no collective call. Results live in a double-buffered symmetric buffer: the tensor
   a call returns stays valid until the second-next call on this layer.
 
 One process per GPU; all ranks must call ``forward`` the same number of times in the same order.
@@ -222,16 +223,15 @@ class ShardedW4A16Linear:
             args.peer_signals[i] = ptrs[r]
         args.local_signal = ptrs[self.rank]
         args.wait_value = (self._calls * self.world) & 0xFFFFFFFF
-        capi.check(lib.fk_w4a16_gemv_ex(args))
-
         view = peer["buffer"][slot_offset:slot_offset + peer["slot"]]
         if not want_f32:
+            capi.check(lib.fk_w4a16_gemv_ex(args))
             return view[: m * self.n * 2].view(self.dtype).view(m, self.n)
-        partials = view[: self.world * m * self.n * 4].view(torch.float32).view(self.world, m, self.n)
-        if self.world == 1:
-            return partials[0].to(self.dtype)
+        # K-split: the kernel itself adds the partials of all ranks, in rank order, once the
+        # counters show that every rank has delivered -- one launch for GEMV, exchange and sum
         out = torch.empty((m, self.n), dtype=self.dtype, device=self.device)
-        code = capi.DTYPE_BF16 if self.dtype == torch.bfloat16 else capi.DTYPE_F16
-        capi.check(lib.fk_w4a16_reduce_partials(partials.data_ptr(), out.data_ptr(), m, self.n, self.world,
-                                                code, int(torch.cuda.current_stream(self.device).cuda_stream)))
+        args.reduce_input = ptrs[self.rank] + slot_offset
+        args.reduce_output = out.data_ptr()
+        args.reduce_slots = self.world
+        capi.check(lib.fk_w4a16_gemv_ex(args))
         return out

@@ -108,11 +108,15 @@ FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* pa
  *     receive the same tiles by plain stores over NVLink while the kernel runs, so the exchange
  *     overlaps the computation tile by tile;
  *   - local_signal / peer_signals / wait_value: 32-bit counters in device memory, one per GPU of
- *     the group. When the call's last output has been written everywhere, each counter is
- *     incremented once (system scope), and the kernel does not complete before local_signal has
- *     reached wait_value (bounded: after about two seconds it gives up and sets the device status
- *     word). With wait_value = calls_so_far * group_size, kernels queued after this call on the
- *     same stream see every GPU's contribution. Leave local_signal NULL for single-GPU use.
+ *     the group. Every CTA of the kernel, once its own stores are done everywhere, adds 1 (system
+ *     scope, released after those stores) to each counter, and the kernel does not complete before
+ *     local_signal has reached wait_value x (CTAs of its grid) -- bounded: after two seconds
+ *     ("peer_wait_ms" of fk_w4a16_set_tuning) it gives up and sets the device status word. With
+ *     wait_value = calls_so_far * (GPUs in the group), kernels queued after this call on the same
+ *     stream see every GPU's contribution. Every GPU of the group must run the same problem shape
+ *     on the same kind of device (the counters count CTAs). Leave local_signal NULL for single-GPU use.
+ *   - reduce_input / reduce_output / reduce_slots: a K-split layer's sum over GPUs, fused behind the
+ *     exchange: see the fields.
  *   - residual, epilogue, norm_weight / norm_eps: see the fields.
  * Zero-initialise the struct; unset fields then mean "default". */
 #define FK_W4A16_MAX_PEERS 7
@@ -150,6 +154,15 @@ typedef struct fk_w4a16_gemv_args {
    * two roundings of the usual module. norm_weight: [k] of the 16-bit type. batch <= 4. */
   const void* norm_weight;
   float norm_eps;
+  /* Fused reduction behind the exchange, or reduce_slots = 0. A K-split layer writes its unrounded
+   * fp32 partial [batch, n] into slot `rank` of a [reduce_slots][batch][n] fp32 buffer on every GPU
+   * (output / peer_outputs with output_f32). With these fields set, the kernel itself -- once the
+   * counters show that every GPU has delivered -- adds the reduce_slots partials found in
+   * reduce_input (this GPU's buffer, slot 0) in slot order and writes round16 of the sum to
+   * reduce_output [batch, n]: no second launch. Needs local_signal. */
+  const float* reduce_input;
+  void* reduce_output;
+  int reduce_slots;
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 
@@ -216,6 +229,24 @@ FK_W4A16_API int fk_w4a16_device_status(int* status);
  * ring stages per warp (1..8, 0 = auto) and CTAs in the grid (0 = one per SM). Process-wide. */
 FK_W4A16_API int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int ctas);
 
+/* Writes a one-line description of the launch fk_w4a16_gemv would make for a problem on the current
+ * device -- kernel name with its template arguments, grid, cluster size, warps, ring stages,
+ * shared memory -- into text[capacity] (host pointer). For benchmarks and profiles that attribute
+ * time to kernels; no counterpart in the reference. */
+FK_W4A16_API int fk_w4a16_describe_plan(int batch, int n, int k, int group_size, int dtype, char* text,
+                           size_t capacity);
+
+/* Launch-plan thresholds, process-wide, for tuning and tests (no counterpart in the reference).
+ * Each knob starts from an environment variable that is read once, at the library's first
+ * planning call: "mma_min_batch" (FK_W4A16_MMA_MIN_BATCH: smallest batch that takes the mma.sync
+ * kernel, 0 = built-in rule), "cluster_min" / "cluster_size" (FK_W4A16_CLUSTER_MIN / _SIZE),
+ * "wmma" (FK_W4A16_WMMA: batches 1-2 on the warp-level mma.sync form of the stream kernel),
+ * "umma_min_batch" (FK_W4A16_UMMA_MIN_BATCH: smallest batch that takes the pipelined tcgen05
+ * kernel, 0 = never, -1 = built-in default), "peer_wait_ms" (FK_W4A16_PEER_WAIT_MS: how long a
+ * multi-GPU call waits for the other GPUs before it gives up, default 2000). Results never depend
+ * on them beyond the order of fp32 additions. */
+FK_W4A16_API int fk_w4a16_set_tuning(const char* name, int value);
+
 /* Kernel variant of the fused GEMV, process-wide, for measurements and tests (no counterpart in
  * the reference). AUTO picks per problem between the CUDA-core stream kernel, its cluster form and
  * the mma.sync kernel (batch > 4); TCGEN05 forces the tcgen05 / tensor-memory kernel for every
@@ -223,6 +254,8 @@ FK_W4A16_API int fk_w4a16_set_launch_config(int warps_per_cta, int stages, int c
  * variable FK_W4A16_TC5=1 selects TCGEN05 when this function was never called. */
 #define FK_W4A16_VARIANT_AUTO 0
 #define FK_W4A16_VARIANT_TCGEN05 1
+#define FK_W4A16_VARIANT_TCGEN05_PIPELINED 2 /* the warp-specialised tcgen05 kernel for every batch */
+#define FK_W4A16_VARIANT_CLASSIC 3           /* never a tcgen05 kernel: CUDA cores and mma.sync only */
 FK_W4A16_API int fk_w4a16_set_variant(int variant);
 
 #ifdef __cplusplus

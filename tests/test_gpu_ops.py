@@ -178,3 +178,46 @@ def test_vendor_subject_and_cpp_launcher_without_workspace(dtype) -> None:
                                      1024, 128, 8704, stream)
         _assert_matches(out, cpu, 128)
         assert native.arc_w4a16_device_status() == 0
+
+
+def test_native_forward_can_be_captured_after_one_warm_up_call() -> None:
+    """The reference's arc_w4a16_forward takes no scratch, so the launcher layer owns one workspace
+    per (device, stream). Its rule: the first call on a stream allocates (outside capture); every
+    later call allocates nothing -- so it can be recorded into a CUDA graph -- and a first call
+    made DURING capture fails with a RuntimeError instead of allocating."""
+    native = native_module()
+    group, n, k = 128, 1024, 2048
+    cpu = _inputs(77, 1, n, k, group, 0.05, 0.1)
+    activations, q_u8, alpha, beta = (t.cuda() for t in cpu)
+    packets = pack_arc_w4a16_packets(q_u8, alpha, beta, group_size=group)
+    stride = packets.shape[1]
+    out = torch.zeros((1, n), dtype=torch.float16, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+
+    def call(stream: torch.cuda.Stream) -> None:
+        native.arc_w4a16_forward(activations_ptr=activations.data_ptr(), packets_ptr=packets.data_ptr(),
+                                 group_sums_ptr=0, output_ptr=out.data_ptr(), batch=1, n=n, k=k,
+                                 group_size=group, packet_stride_bytes=stride, stream_ptr=stream.cuda_stream)
+
+    with torch.cuda.stream(side):
+        call(side)  # warm-up: allocates this stream's workspace
+        side.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        out.zero_()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            call(side)
+        graph.replay()
+        side.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before  # nothing was allocated for the capture
+    _assert_matches(out, cpu, group)
+
+    fresh = torch.cuda.Stream()
+    fresh.wait_stream(torch.cuda.current_stream())
+    graph2 = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="outside capture"):
+        with torch.cuda.stream(fresh):
+            with torch.cuda.graph(graph2, stream=fresh):
+                call(fresh)
+    torch.cuda.synchronize()

@@ -417,15 +417,25 @@ def test_gemv_host_buffers_match_device_call() -> None:
                                           3, shape.n, shape.k, 128, 8704, 1, stream_ptr()))
 
 
-def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
+def _grid_ctas(batch: int, n: int, k: int, group: int, code: int) -> int:
+    """CTAs of the launch fk_w4a16_gemv makes for a problem ("... grid=AxB ...")."""
+    text = capi.describe_plan(batch, n, k, group, code)
+    a, b = text.split(" grid=")[1].split(" ")[0].split("x")
+    return int(a) * int(b)
+
+
+@pytest.mark.parametrize(("n", "k"), [(128 * 6, 128 * 5), (128 * 100, 128 * 9)])  # cluster / stream kernel
+def test_gemv_ex_output_placement_fp32_and_peer_stores(n: int, k: int) -> None:
     """fk_w4a16_gemv_ex: fp32 partial outputs, a slice of a wider matrix, a second destination
-    and the completion counters -- here with both destinations on this GPU."""
+    and the completion counters -- here with both destinations on this GPU. Every CTA adds one to
+    every counter; the kernel completes once its own counter shows wait_value x CTAs."""
     lib = capi.load_library()
-    shape = LayerShape("t", 128 * 6, 128 * 5, batch=2, dtype="bf16", zero_point=None)
+    shape = LayerShape("t", n, k, batch=2, dtype="bf16", zero_point=None)
     problem = make_problem(shape, seed=808)
-    q, alpha, beta, act = (problem[k].cuda() for k in ("q_u8", "alpha", "beta", "activations"))
+    q, alpha, beta, act = (problem[k_].cuda() for k_ in ("q_u8", "alpha", "beta", "activations"))
     packets = capi_pack(capi, q, alpha, beta, 128)
     plain = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    ctas = _grid_ctas(2, shape.n, shape.k, 128, 1)
     ld, col0 = shape.n * 3, shape.n
     signals = torch.zeros(64, dtype=torch.int32, device="cuda")
     for want_f32 in (0, 1):
@@ -443,11 +453,11 @@ def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
         args.peer_outputs[0] = mirror.data_ptr()
         args.peer_signals[0] = signals.data_ptr() + 4
         args.local_signal = signals.data_ptr()
-        args.wait_value = want_f32 + 1  # the counter after this call's own increment
+        args.wait_value = want_f32 + 1  # calls so far x (GPUs in the group = 1)
         args.stream = stream_ptr()
         capi.check(lib.fk_w4a16_gemv_ex(args))
         torch.cuda.synchronize()
-        assert signals[0].item() == want_f32 + 1 and signals[1].item() == want_f32 + 1
+        assert signals[0].item() == (want_f32 + 1) * ctas and signals[1].item() == (want_f32 + 1) * ctas
         for buf in (wide, mirror):
             assert (buf[:, :col0] == -7.0).all() and (buf[:, col0 + shape.n:] == -7.0).all()
         assert torch.equal(wide, mirror)
@@ -459,6 +469,94 @@ def test_gemv_ex_output_placement_fp32_and_peer_stores() -> None:
     with pytest.raises(ValueError, match="output_ld"):
         args.output_col0 = ld
         capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
+@pytest.mark.parametrize(("n", "k"), [(128 * 6, 128 * 5), (128 * 100, 128 * 9)])
+def test_gemv_ex_fused_reduction_behind_the_exchange(n: int, k: int) -> None:
+    """reduce_slots: a K-split layer's sum over GPUs inside the GEMV launch. One GPU plays one of
+    two ranks: its partial goes to slot 0 of a [2][batch][n] fp32 buffer, slot 1 holds what the
+    other rank would have delivered; the kernel waits for its own CTAs' signals, then writes
+    round16(slot 0 + slot 1)."""
+    lib = capi.load_library()
+    shape = LayerShape("t", n, k, batch=2, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=909)
+    q, alpha, beta, act = (problem[k_].cuda() for k_ in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    y32 = torch.empty((2, n), dtype=torch.float32, device="cuda")
+    _gemv_ex(lib, act, packets, y32, shape, 1, f32=1)
+    gen = torch.Generator().manual_seed(4)
+    other = torch.randn((2, n), generator=gen).cuda()
+    slots = torch.full((2, 2, n), float("nan"), dtype=torch.float32, device="cuda")
+    slots[1] = other
+    signals = torch.zeros(8, dtype=torch.int32, device="cuda")
+    for call in (1, 2):  # twice: the counter keeps counting
+        slots[0].fill_(float("nan"))
+        out = torch.full((2, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        args = capi.GemvArgs()
+        ws = WS.get(capi, 2, n, k, 128)
+        args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), slots.data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = 2, n, k, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.output_f32 = 1
+        args.local_signal = signals.data_ptr()
+        args.wait_value = call
+        args.reduce_input, args.reduce_output, args.reduce_slots = slots.data_ptr(), out.data_ptr(), 2
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+        torch.cuda.synchronize()
+        assert torch.equal(slots[0], y32)
+        assert torch.equal(out, (y32 + other).to(torch.bfloat16))
+    args.local_signal = 0
+    with pytest.raises(ValueError, match="reduce_slots"):
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+
+
+def test_peer_wait_gives_up_and_reports_through_the_status_word() -> None:
+    """Failure detection without a fault: a call whose counter can never reach its target (it is
+    told to wait for one more group-wide delivery than will ever come) returns after the bounded
+    wait -- shortened to 20 ms here -- with device status 2; reading the status clears it, and after
+    re-initialising the workspace the same buffers serve a normal call."""
+    lib = capi.load_library()
+    shape = LayerShape("t", 128 * 6, 128 * 5, batch=1, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=606)
+    q, alpha, beta, act = (problem[k_].cuda() for k_ in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    plain = capi_gemv(capi, WS, act, packets, shape.n, shape.k, 128, 1)
+    signals = torch.zeros(8, dtype=torch.int32, device="cuda")
+    out = torch.zeros((1, shape.n), dtype=torch.bfloat16, device="cuda")
+    ws = WS.get(capi, 1, shape.n, shape.k, 128)
+
+    def call(wait_value: int) -> None:
+        args = capi.GemvArgs()
+        args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), out.data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = 1, shape.n, shape.k, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.local_signal = signals.data_ptr()
+        args.wait_value = wait_value
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+
+    capi.check(lib.fk_w4a16_set_tuning(b"peer_wait_ms", 20))
+    try:
+        call(2)  # only one delivery (this call's own) will ever arrive
+        torch.cuda.synchronize()
+        assert capi.device_status() == 2  # kStatusPeerWaitTimeout
+        assert capi.device_status() == 0  # reading it cleared it
+        assert torch.equal(out, plain)    # this GPU's own outputs were complete all the same
+        capi.check(lib.fk_w4a16_workspace_init(ws.data_ptr(), ws.numel(), stream_ptr()))
+        out.zero_()
+        call(2)  # the counter now holds two rounds of signals: a normal call
+        torch.cuda.synchronize()
+        assert capi.device_status() == 0
+        assert torch.equal(out, plain)
+    finally:
+        capi.check(lib.fk_w4a16_set_tuning(b"peer_wait_ms", 2000))
+    with pytest.raises(ValueError, match="peer_wait_ms"):
+        capi.check(lib.fk_w4a16_set_tuning(b"peer_wait_ms", 0))
+    with pytest.raises(ValueError, match="unknown tuning knob"):
+        capi.check(lib.fk_w4a16_set_tuning(b"no_such_knob", 1))
 
 
 def _gemv_ex(lib, act, packets, out, shape, code, *, f32=0, residual=None):
@@ -701,12 +799,46 @@ def test_tcgen05_variant_on_a_layer_shape_and_bad_variant() -> None:
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("group", [32, 64, 128])
 @pytest.mark.parametrize("batch", [1, 2])
-def test_warp_mma_variant_matches_the_oracle(group: int, batch: int, dtype: str, monkeypatch) -> None:
-    """FK_W4A16_WMMA=1: the stream kernel with its inner product on mma.sync (batches 1 and 2)."""
-    monkeypatch.setenv("FK_W4A16_WMMA", "1")
-    shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
-                       zero_point=None)
-    _check_gemv(make_problem(shape, seed=777 + batch), shape, oracle.dtype_code(dtype))
-    big = LayerShape("gate_up", 28672, 4096, batch=batch, dtype=dtype, zero_point=None)
-    if group == 128:
-        _check_gemv(make_problem(big, seed=778), big, oracle.dtype_code(dtype))
+def test_warp_mma_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
+    """Tuning knob "wmma" (FK_W4A16_WMMA=1): the stream kernel with its inner product on mma.sync
+    (batches 1 and 2)."""
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_tuning(b"wmma", 1))
+    try:
+        shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
+                           zero_point=None)
+        _check_gemv(make_problem(shape, seed=777 + batch), shape, oracle.dtype_code(dtype))
+        big = LayerShape("gate_up", 28672, 4096, batch=batch, dtype=dtype, zero_point=None)
+        if group == 128:
+            _check_gemv(make_problem(big, seed=778), big, oracle.dtype_code(dtype))
+    finally:
+        capi.check(lib.fk_w4a16_set_tuning(b"wmma", 0))
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 8, 16, 19])
+def test_pipelined_tcgen05_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
+    """The warp-specialised tcgen05 / tensor-memory kernel meets the same bar as the other kernels
+    for every group size, type and batch (more than 16 rows: 16 at a time)."""
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05_PIPELINED))
+    try:
+        shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
+                           zero_point=None)
+        _check_gemv(make_problem(shape, seed=5150 + batch), shape, oracle.dtype_code(dtype))
+        assert capi.device_status() == 0
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+
+
+@pytest.mark.parametrize(("n", "k", "batch"), [(4096, 4096, 1), (6144, 4096, 2), (4096, 14336, 4),
+                                                 (28672, 4096, 8), (13824, 5120, 16)])
+def test_pipelined_tcgen05_variant_on_layer_shapes(n: int, k: int, batch: int) -> None:
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05_PIPELINED))
+    try:
+        shape = LayerShape("t", n, k, batch=batch, dtype="bf16", zero_point=None)
+        _check_gemv(make_problem(shape, seed=99), shape, oracle.dtype_code("bf16"))
+    finally:
+        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))

@@ -24,7 +24,7 @@ pytestmark = pytest.mark.gpu
 def _gemv_cuda_cores(ws: Workspace, act, packets, n, k, group, code):
     """The workspace-taking entry point on the kernels the static one uses: the launch plan is the
     same, so the bits must agree. (For batch 3-4 on large layers fk_w4a16_gemv itself would pick
-    the tensor-core kernel; FK_W4A16_MMA_MIN_BATCH=5 in the environment keeps it off.)"""
+    the tensor-core kernel; the tuning knob "mma_min_batch" = 5 keeps it off.)"""
     lib = capi.load_library()
     batch = act.shape[0]
     out = torch.full((batch, n), float("nan"), dtype=act.dtype, device=act.device)
@@ -43,8 +43,18 @@ def _prepare(shape: LayerShape, seed: int):
 
 
 @pytest.mark.parametrize(("dtype", "batch"), [("bf16", 1), ("fp16", 2), ("bf16", 3), ("bf16", 4)])
-def test_static_scratch_entry_point_matches_the_workspace_one_twice(dtype: str, batch: int, monkeypatch) -> None:
-    monkeypatch.setenv("FK_W4A16_MMA_MIN_BATCH", "5")
+def test_static_scratch_entry_point_matches_the_workspace_one_twice(dtype: str, batch: int) -> None:
+    lib = capi.load_library()
+    capi.check(lib.fk_w4a16_set_tuning(b"mma_min_batch", 5))
+    capi.check(lib.fk_w4a16_set_tuning(b"umma_min_batch", 0))
+    try:
+        _static_against_workspace(dtype, batch)
+    finally:
+        capi.check(lib.fk_w4a16_set_tuning(b"mma_min_batch", 0))
+        capi.check(lib.fk_w4a16_set_tuning(b"umma_min_batch", -1))
+
+
+def _static_against_workspace(dtype: str, batch: int) -> None:
     code = oracle.dtype_code(dtype)
     # 100 tiles of 9 packets over 148 CTAs: the packet-stream kernel with most tiles split over two
     # or three CTAs, i.e. the ticket finish on the shared array; then the 8B gate_up layer (224
