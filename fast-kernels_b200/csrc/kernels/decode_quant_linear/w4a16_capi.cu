@@ -21,7 +21,6 @@
 #include "w4a16_gemv_cluster.cuh"
 #include "w4a16_gemv_wmma.cuh"
 #include "w4a16_launch.h"
-#include "w4a16_tc5_plan.cuh"
 #include "w4a16_umma_plan.cuh"
 #include "w4a16_prep.cuh"
 
@@ -255,7 +254,6 @@ struct Plan {
   int cluster_size = 1;       // > 1: the cluster kernel, one cluster of this many CTAs per tile
   bool tensor_cores = false;  // batch > 4: the MMA kernel, rows in tiles of 8 or 16
   bool wmma = false;          // batch <= 2: the stream kernel with its inner product on mma.sync
-  bool tc5 = false;           // the tcgen05 kernel: `warps` counts warpgroups, rows in {1,2,4,8,16}
   bool umma = false;          // the pipelined tcgen05 kernel: one run per CTA, rows in {1,2,4,8,16}
   size_t staged_bytes = 0;    // its pre-staged activations, behind the scratch slots
 };
@@ -435,22 +433,14 @@ Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_sm
   return plan;
 }
 
-std::atomic<int> g_variant{-1};  // -1: not set, take FK_W4A16_TC5 / FK_W4A16_UMMA from the environment
-bool tc5_enabled() {
-  const int variant = g_variant.load(std::memory_order_relaxed);
-  if (variant >= 0) {
-    return variant == FK_W4A16_VARIANT_TCGEN05;
-  }
-  static const bool from_env = env_int("FK_W4A16_TC5") != 0;
-  return from_env;
-}
-// 1: every batch size takes the pipelined tcgen05 kernel; 0: none does; -1: the default rule.
+std::atomic<int> g_variant{-1};  // -1: not set, take FK_W4A16_TC5 from the environment
+// 1: every batch size takes the tcgen05 kernel; 0: none does; -1: the default rule.
 int umma_forced() {
   const int variant = g_variant.load(std::memory_order_relaxed);
   if (variant >= 0) {
-    return variant == FK_W4A16_VARIANT_TCGEN05_PIPELINED ? 1 : (variant == FK_W4A16_VARIANT_AUTO ? -1 : 0);
+    return variant == FK_W4A16_VARIANT_TCGEN05 ? 1 : (variant == FK_W4A16_VARIANT_AUTO ? -1 : 0);
   }
-  static const int from_env = std::getenv("FK_W4A16_UMMA") == nullptr ? -1 : (env_int("FK_W4A16_UMMA") != 0 ? 1 : 0);
+  static const int from_env = std::getenv("FK_W4A16_TC5") == nullptr ? -1 : (env_int("FK_W4A16_TC5") != 0 ? 1 : 0);
   return from_env;
 }
 
@@ -495,47 +485,6 @@ Plan make_umma_plan(int batch, int n, int k, int group_size, int sm_count, int m
   plan.smem_bytes = umma_smem_plan(plan.stages < 1 ? 1 : plan.stages, group_size, plan.m_tile).total;
   // one CTA per SM: each allocates all of the SM's tensor memory
   const size_t floor_bytes = (static_cast<size_t>(max_smem) / 2) + 1024;
-  plan.smem_bytes = plan.smem_bytes < floor_bytes ? floor_bytes : plan.smem_bytes;
-  plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
-                       (plan.m_tile * kTileCols) * sizeof(float);
-  return plan;
-}
-
-// Plan of the tcgen05 kernel: one run per warpgroup.
-Plan make_tc5_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
-                   const LaunchConfig& cfg) {
-  Plan plan;
-  plan.tc5 = true;
-  const long long total_packets = static_cast<long long>(n / kTileCols) * (k / group_size);
-  plan.total_packets = static_cast<uint32_t>(total_packets);
-  plan.m_tile = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : (batch <= 8 ? 8 : 16)));
-  plan.row_tiles = (batch + plan.m_tile - 1) / plan.m_tile;
-  int groups = tc5_groups_for_rows(plan.m_tile);
-  if (cfg.warps > 0 && cfg.warps < groups) {
-    groups = cfg.warps;
-  }
-  int ctas = cfg.ctas > 0 ? cfg.ctas : sm_count;
-  ctas = ctas > 256 ? 256 : ctas;
-  long long workers = static_cast<long long>(ctas) * groups;
-  workers = workers > total_packets ? total_packets : workers;
-  groups = static_cast<int>((workers + ctas - 1) / ctas);
-  plan.warps = groups;
-  plan.grid_x = static_cast<int>((workers + groups - 1) / groups);
-  plan.active_warps = static_cast<int>(workers);
-  const long long longest_run = (total_packets + workers - 1) / workers;
-  int wanted = cfg.stages > 0 ? cfg.stages : 4;
-  wanted = wanted > kMaxStages ? kMaxStages : wanted;
-  wanted = wanted > longest_run ? static_cast<int>(longest_run) : wanted;
-  plan.stages = 0;
-  for (int candidate = wanted; candidate >= 1; --candidate) {
-    if (tc5_smem_plan(groups, candidate, group_size, plan.m_tile).total <= static_cast<uint32_t>(max_smem)) {
-      plan.stages = candidate;
-      break;
-    }
-  }
-  plan.smem_bytes = tc5_smem_plan(groups, plan.stages < 1 ? 1 : plan.stages, group_size, plan.m_tile).total;
-  // at most two CTAs per SM: each holds half of the SM's tensor memory
-  const size_t floor_bytes = (static_cast<size_t>(max_smem) / 3) + 1024;
   plan.smem_bytes = plan.smem_bytes < floor_bytes ? floor_bytes : plan.smem_bytes;
   plan.scratch_bytes = static_cast<size_t>(plan.row_tiles) * plan.grid_x * 2 *
                        (plan.m_tile * kTileCols) * sizeof(float);
@@ -796,7 +745,7 @@ int fk_w4a16_set_tuning(const char* name, int value) {
 
 int fk_w4a16_set_variant(int variant) {
   if (variant != FK_W4A16_VARIANT_AUTO && variant != FK_W4A16_VARIANT_TCGEN05 &&
-      variant != FK_W4A16_VARIANT_TCGEN05_PIPELINED && variant != FK_W4A16_VARIANT_CLASSIC) {
+      variant != FK_W4A16_VARIANT_CLASSIC) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown kernel variant");
   }
   g_variant.store(variant, std::memory_order_relaxed);
@@ -862,12 +811,9 @@ size_t fk_w4a16_workspace_bytes(int batch, int n, int k, int group_size) {
   }
   const Plan plan =
       make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
-  const Plan tc5_plan =
-      make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
   const Plan umma_plan =
       make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config());
   size_t need = workspace_bytes_for(plan);
-  need = need > workspace_bytes_for(tc5_plan) ? need : workspace_bytes_for(tc5_plan);
   need = need > workspace_bytes_for(umma_plan) ? need : workspace_bytes_for(umma_plan);
   return need;
 }
@@ -884,12 +830,9 @@ int fk_w4a16_describe_plan(int batch, int n, int k, int group_size, int dtype, c
   const bool use_umma = umma_wanted(batch, n, k, group_size);
   const Plan plan =
       use_umma ? make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
-      : tc5_enabled()
-          ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
-          : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
+               : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
                       /*allow_cluster=*/true, /*cuda_cores_only=*/false);
   const char* kernel = plan.umma            ? "w4a16_gemm_umma_kernel"
-                       : plan.tc5           ? "w4a16_gemm_tc5_kernel"
                        : plan.tensor_cores  ? "w4a16_gemm_mma_kernel"
                        : plan.wmma          ? "w4a16_gemv_wmma_kernel"
                        : plan.cluster_size > 1 ? "w4a16_gemv_cluster_kernel"
@@ -1001,8 +944,6 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   const Plan plan =
       use_umma
           ? make_umma_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
-      : (tc5_enabled() && !normalise)
-          ? make_tc5_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config())
           : make_plan(batch, n, k, group_size, info->sm_count, info->max_smem_optin, launch_config(),
                       /*allow_cluster=*/true,
                       /*cuda_cores_only=*/normalise || small_batch_on_cuda_cores);
@@ -1039,7 +980,7 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   const size_t gated_bytes =
       gated ? static_cast<size_t>(batch) * (n / 2) * sizeof(unsigned long long) : 0;
   const bool wants_exchange =
-      with_exchange_area && !plan.tensor_cores && !plan.tc5 && plan.cluster_size == 1 && plan.m_tile <= 4;
+      with_exchange_area && !plan.tensor_cores && plan.cluster_size == 1 && plan.m_tile <= 4;
   // (the pipelined tcgen05 kernel finishes split tiles like the packet-stream kernel does)
   if (!wants_exchange || exchange_bytes + gated_bytes > kExchangeBytes) {
     exchange_bytes = 0;  // split tiles take the ticket finish; the area is the epilogue's alone
@@ -1107,24 +1048,6 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
     launch.programmatic = pdl_enabled();
     launch.stream = s;
     FK_TRY_CUDA(launch_umma_kernel(params, launch));
-    return FK_W4A16_OK;
-  }
-  if (plan.tc5) {
-    if (plan.smem_bytes > static_cast<size_t>(max_smem)) {
-      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "launch needs more shared memory than the device has");
-    }
-    Tc5Launch launch{};
-    launch.group_size = group_size;
-    launch.rows = plan.m_tile;
-    launch.bf16 = args->dtype == FK_W4A16_DTYPE_BF16;
-    launch.grid_x = plan.grid_x;
-    launch.row_tiles = plan.row_tiles;
-    launch.groups = plan.warps;
-    launch.smem_bytes = plan.smem_bytes;
-    launch.max_smem = max_smem;
-    launch.programmatic = pdl_enabled();
-    launch.stream = s;
-    FK_TRY_CUDA(launch_tc5_kernel(params, launch));
     return FK_W4A16_OK;
   }
   if (plan.tensor_cores) {

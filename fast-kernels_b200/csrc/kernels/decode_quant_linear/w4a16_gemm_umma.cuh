@@ -30,7 +30,7 @@
 // operands_ready[p] (unpackers + stagers -> issuer), mma_done[p] (commit -> epilogue, and "A, B
 // are free again" for unpackers and stagers), d_free[p] (epilogue -> issuer).
 //
-// Operand mapping (unchanged from the plain tcgen05 kernel it replaces): a K = 16 step takes the
+// Operand mapping: a K = 16 step takes the
 // pairs of one kind from four consecutive word-rows -- for bf16, G/32 steps of bf16 x bf16 (pairs
 // (0,4), (2,6): 128 + q against the raw activation) and G/32 steps of fp16 x fp16 (pairs (1,5),
 // (3,7): 1024 + 16 q against fp16(a / 16)); for fp16 all steps are of the second kind. No weight

@@ -597,10 +597,10 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
 // adds 1 to the counter of every GPU with fire-and-forget reductions. No exit ticket, no "last
 // CTA": the slowest CTA's stores are the only thing the other GPUs ever wait for.
 // Who waits: without the fused reduction one thread of the grid (CTA 0) holds the kernel open
-// until the local counter shows every CTA of every GPU; with it, every CTA waits and then adds
-// its slice of the partial sums. Waits are bounded (peer_wait_ns), report through the status word
-// and need every CTA of the grid to be resident, which the launch plans guarantee (at most one
-// CTA per SM).
+// until the local counter shows every CTA of every GPU; with it, the first few CTAs wait and then
+// share the sum of the partials. Waits are bounded (peer_wait_ns) and report through the status
+// word; the waiting CTAs never hold back the signalling ones, so no CTA needs another to be
+// resident.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void red_add_system(unsigned int* counter) {
   asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
@@ -610,11 +610,16 @@ __device__ __forceinline__ unsigned int load_counter_system(const unsigned int* 
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
   return v;
 }
+__device__ __forceinline__ void fence_acq_rel_system() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+constexpr unsigned int kReduceCtas = 8;
 
 template <class E>
 __device__ __forceinline__ void exchange_complete(const GemvParams& p) {
@@ -626,9 +631,13 @@ __device__ __forceinline__ void exchange_complete(const GemvParams& p) {
   const unsigned int ctas_total = gridDim.x * gridDim.y;
   const unsigned int target = p.wait_value * ctas_total;
   const bool reduce = p.reduce_slots > 0;
-  const bool waiter = reduce || (blockIdx.x == 0 && blockIdx.y == 0);
+  // The fused reduction is small (batch x n outputs): a handful of CTAs wait and share it, the
+  // others leave at once, so that the next kernel in the stream can move in behind them.
+  const unsigned int cta_index = (blockIdx.y * gridDim.x) + blockIdx.x;
+  const unsigned int reducers = ctas_total < kReduceCtas ? ctas_total : kReduceCtas;
+  const bool waiter = reduce ? cta_index < reducers : cta_index == 0;
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    fence_acq_rel_system();  // release: this CTA's stores, local and remote, before the signals
     for (int peer = 0; peer < p.num_peers; ++peer) {
       red_add_system(p.peer_signal[peer]);
     }
@@ -650,11 +659,11 @@ __device__ __forceinline__ void exchange_complete(const GemvParams& p) {
       if (!arrived) {
         atomicExch(p.status, static_cast<int>(kStatusPeerWaitTimeout));
       }
-      __threadfence_system();
+      fence_acq_rel_system();  // acquire: the other GPUs' stores behind their signals
       arrived_flag = arrived ? 1 : 0;
     }
   }
-  if (!reduce) {
+  if (!reduce || !waiter) {
     return;
   }
   __syncthreads();
@@ -663,8 +672,8 @@ __device__ __forceinline__ void exchange_complete(const GemvParams& p) {
   }
   // this CTA's slice of the [m][n] outputs, in units of 4 elements
   const long long units = (static_cast<long long>(p.m) * p.n) >> 2;
-  const long long cta = (static_cast<long long>(blockIdx.y) * gridDim.x) + blockIdx.x;
-  const long long per_cta = (units + ctas_total - 1) / ctas_total;
+  const long long cta = cta_index;
+  const long long per_cta = (units + reducers - 1) / reducers;
   const long long begin = cta * per_cta;
   long long end = begin + per_cta;
   end = end < units ? end : units;

@@ -9,22 +9,6 @@ namespace fk_w4a16 {
 
 struct GemvParams;
 
-struct Tc5Launch {
-  int group_size;   // 32, 64 or 128
-  int rows;         // rows per pass: 1, 2, 4, 8 or 16
-  bool bf16;
-  int grid_x;
-  int row_tiles;
-  int groups;       // warpgroups per CTA
-  size_t smem_bytes;
-  int max_smem;     // opt-in limit of the device
-  bool programmatic;  // launch with programmatic stream serialisation
-  cudaStream_t stream;
-};
-
-// The tcgen05 / tensor-memory kernel (w4a16_gemm_tc5.cuh).
-cudaError_t launch_tc5_kernel(const GemvParams& params, const Tc5Launch& launch);
-
 struct UmmaLaunch {
   int group_size;   // 32, 64 or 128
   int rows;         // rows per pass: 1, 2, 4, 8 or 16

@@ -25,8 +25,7 @@ EPILOGUE_NONE = 0
 EPILOGUE_SILU_MUL = 1
 VARIANT_AUTO = 0
 VARIANT_TCGEN05 = 1
-VARIANT_TCGEN05_PIPELINED = 2
-VARIANT_CLASSIC = 3
+VARIANT_CLASSIC = 2
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfk_w4a16.so"
 

@@ -249,13 +249,13 @@ FK_W4A16_API int fk_w4a16_set_tuning(const char* name, int value);
 
 /* Kernel variant of the fused GEMV, process-wide, for measurements and tests (no counterpart in
  * the reference). AUTO picks per problem between the CUDA-core stream kernel, its cluster form and
- * the mma.sync kernel (batch > 4); TCGEN05 forces the tcgen05 / tensor-memory kernel for every
- * batch size -- same results, slower on decode shapes (its header says why). The environment
- * variable FK_W4A16_TC5=1 selects TCGEN05 when this function was never called. */
+ * the mma.sync kernel; TCGEN05 forces the warp-specialised tcgen05 / tensor-memory kernel for every
+ * batch size -- same results, slower on decode shapes (its header says why); CLASSIC never uses
+ * it. The environment variable FK_W4A16_TC5=1 selects TCGEN05 when this function was never
+ * called. */
 #define FK_W4A16_VARIANT_AUTO 0
 #define FK_W4A16_VARIANT_TCGEN05 1
-#define FK_W4A16_VARIANT_TCGEN05_PIPELINED 2 /* the warp-specialised tcgen05 kernel for every batch */
-#define FK_W4A16_VARIANT_CLASSIC 3           /* never a tcgen05 kernel: CUDA cores and mma.sync only */
+#define FK_W4A16_VARIANT_CLASSIC 2
 FK_W4A16_API int fk_w4a16_set_variant(int variant);
 
 #ifdef __cplusplus

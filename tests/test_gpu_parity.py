@@ -769,35 +769,6 @@ def test_gemm_tensor_core_layer_shapes(n: int, k: int, batch: int) -> None:
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("group", [32, 64, 128])
-@pytest.mark.parametrize("batch", [1, 2, 3, 8, 16, 19])
-def test_tcgen05_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
-    """The tcgen05 / tensor-memory kernel (opt-in) meets the same bar as the default kernels."""
-    lib = capi.load_library()
-    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
-    try:
-        shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
-                           zero_point=None)
-        _check_gemv(make_problem(shape, seed=4242 + batch), shape, oracle.dtype_code(dtype))
-        assert capi.device_status() == 0
-    finally:
-        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
-
-
-def test_tcgen05_variant_on_a_layer_shape_and_bad_variant() -> None:
-    lib = capi.load_library()
-    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
-    try:
-        for shape in (LayerShape("o_proj", 4096, 4096, dtype="bf16", zero_point=None),
-                      LayerShape("down_proj", 4096, 14336, batch=4, dtype="bf16", zero_point=None)):
-            _check_gemv(make_problem(shape, seed=99), shape, oracle.dtype_code("bf16"))
-    finally:
-        capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
-    with pytest.raises(ValueError, match="variant"):
-        capi.check(lib.fk_w4a16_set_variant(7))
-
-
-@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
-@pytest.mark.parametrize("group", [32, 64, 128])
 @pytest.mark.parametrize("batch", [1, 2])
 def test_warp_mma_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
     """Tuning knob "wmma" (FK_W4A16_WMMA=1): the stream kernel with its inner product on mma.sync
@@ -818,11 +789,11 @@ def test_warp_mma_variant_matches_the_oracle(group: int, batch: int, dtype: str)
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("group", [32, 64, 128])
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 8, 16, 19])
-def test_pipelined_tcgen05_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
+def test_tcgen05_variant_matches_the_oracle(group: int, batch: int, dtype: str) -> None:
     """The warp-specialised tcgen05 / tensor-memory kernel meets the same bar as the other kernels
     for every group size, type and batch (more than 16 rows: 16 at a time)."""
     lib = capi.load_library()
-    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05_PIPELINED))
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
     try:
         shape = LayerShape("t", 128 * 5, group * 9, group_size=group, batch=batch, dtype=dtype,
                            zero_point=None)
@@ -834,11 +805,13 @@ def test_pipelined_tcgen05_variant_matches_the_oracle(group: int, batch: int, dt
 
 @pytest.mark.parametrize(("n", "k", "batch"), [(4096, 4096, 1), (6144, 4096, 2), (4096, 14336, 4),
                                                  (28672, 4096, 8), (13824, 5120, 16)])
-def test_pipelined_tcgen05_variant_on_layer_shapes(n: int, k: int, batch: int) -> None:
+def test_tcgen05_variant_on_layer_shapes(n: int, k: int, batch: int) -> None:
     lib = capi.load_library()
-    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05_PIPELINED))
+    capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_TCGEN05))
     try:
         shape = LayerShape("t", n, k, batch=batch, dtype="bf16", zero_point=None)
         _check_gemv(make_problem(shape, seed=99), shape, oracle.dtype_code("bf16"))
     finally:
         capi.check(lib.fk_w4a16_set_variant(capi.VARIANT_AUTO))
+    with pytest.raises(ValueError, match="variant"):
+        capi.check(lib.fk_w4a16_set_variant(7))
