@@ -42,23 +42,23 @@ class LayerShape:
         )
 
 
-# BASELINE configs[1]: the Llama-3-8B decode layer set at M=1 (the headline workload).
+# The Llama-3-8B decode layer set at M=1 (the headline workload).
 LLAMA3_8B_LAYERS = (
     LayerShape("qkv", 6144, 4096),
     LayerShape("o_proj", 4096, 4096),
     LayerShape("gate_up", 28672, 4096),
     LayerShape("down_proj", 4096, 14336),
 )
-# configs[0]: the single reference case.
+# The single CPU-runnable case of the reference: 4096 x 4096, fp16, seed 0.
 REFERENCE_CASE = LayerShape("ref_4096", 4096, 4096, dtype="fp16")
-# configs[2]: batched sweep.
+# Batched decode sweep on a 70B-style MLP up projection, per-group uint4 zero points.
 BATCH_SWEEP = tuple(
     LayerShape(f"mlp_up_m{m}", 28672, 8192, batch=m, zero_point=None) for m in (1, 2, 4, 8, 16)
 )
-# configs[3]: sharded layers.
+# Layers large enough to shard over the GPUs of a node (N-split, K-split).
 SHARDED_COLUMN = LayerShape("gate_up_70b", 57344, 8192)
 SHARDED_ROW = LayerShape("down_70b", 8192, 28672)
-# configs[4]: edge and large shapes.
+# Edge and large shapes: a 13B MLP at three group sizes (fp16, asymmetric zeros), an LM head.
 EDGE_SHAPES = tuple(
     LayerShape(f"mlp13b_g{g}", 13824, 5120, group_size=g, dtype="fp16", scale_range=(0.001, 0.05),
                zero_point=None)
