@@ -399,6 +399,40 @@ def _e2e(torch, layers: LayerSet, steps: int, device) -> dict:
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
 
+def _chain_leg(torch, capi, layers: LayerSet, device, step_bytes: int, peak_gbs: float) -> dict:
+    """The layer set through fk_w4a16_gemv_chain: each decoder layer's four GEMVs as ONE persistent
+    launch (grid-wide barriers inside instead of kernel boundaries), 32 launches per step, replayed
+    as a CUDA graph like the per-call step. Reported beside the per-call figure, never instead."""
+    lib = layers.lib
+    need = int(lib.fk_w4a16_chain_workspace_bytes(1, 128))
+    workspace = torch.zeros(need, dtype=torch.uint8, device=device)
+    arrays = []
+    for base in range(0, len(layers.calls), 4):
+        array = (capi.ChainStep * 4)()
+        for slot, (shape, act, packets, out) in zip(array, layers.calls[base:base + 4]):
+            slot.activations, slot.packets, slot.output = act.data_ptr(), packets.data_ptr(), out.data_ptr()
+            slot.n, slot.k = shape.n, shape.k
+        arrays.append(array)
+
+    def enqueue() -> None:
+        stream = layers.stream_ptr()
+        for array in arrays:
+            capi.check(lib.fk_w4a16_gemv_chain(array, 4, workspace.data_ptr(), workspace.numel(), 1, 128,
+                                               layers.stride, capi.DTYPE_BF16, stream))
+
+    enqueue()
+    torch.cuda.synchronize(device)
+    graph = _capture(torch, device, enqueue)
+    for _ in range(3):
+        graph.replay()
+    seconds = min(_time_graph(torch, graph, 5, device) for _ in range(3)) / 5
+    gbs = step_bytes / seconds / 1e9
+    return {"api": "fk_w4a16_gemv_chain: 4 GEMVs per launch, 32 launches per step",
+            "ms_per_step": seconds * 1e3, "us_per_layer": seconds * 1e6 / len(arrays),
+            "us_per_gemv": seconds * 1e6 / len(layers.calls), "achieved_gbs": gbs, "frac_of_peak": gbs / peak_gbs,
+            "kernel": "w4a16_gemv_chain_kernel<128, 1, UnpackBF16>"}
+
+
 def _cpu_baseline_leg() -> dict:
     from oracle import w4a16_oracle as oracle
 
@@ -805,6 +839,9 @@ def run_ours(args) -> int:
                           "algorithmic_bytes": shape.algorithmic_bytes(),
                           "kernel": capi.describe_plan(1, shape.n, shape.k, 128, capi.DTYPE_BF16)})
 
+    # the same step as 32 chains of 4 GEMVs each (one persistent launch per decoder layer)
+    chain = _chain_leg(torch, capi, layers, device, step_bytes, peak_gbs)
+
     e2e_steps = max(2, min(args.steps, 20))
     e2e = _e2e(torch, layers, e2e_steps, device)
     e2e_seconds = e2e["seconds"]
@@ -900,6 +937,7 @@ def run_ours(args) -> int:
             "gpu_launches": calls_per_step * args.steps,
             "clocks": clocks.summary(),
             "pack": pack,
+            "layer_chain": chain,
         }
         if sharded is not None:
             line["sharded_layers"] = {

@@ -19,6 +19,7 @@
 #include "w4a16_gemv_stream.cuh"
 #include "w4a16_gemm_mma.cuh"
 #include "w4a16_gemv_cluster.cuh"
+#include "w4a16_gemv_chain.cuh"
 #include "w4a16_gemv_wmma.cuh"
 #include "w4a16_launch.h"
 #include "w4a16_umma_plan.cuh"
@@ -221,6 +222,7 @@ struct Tuning {
   int umma_min_batch = -1; // FK_W4A16_UMMA_MIN_BATCH: smallest batch for the pipelined tcgen05 kernel
                            // (-1 = built-in default, 0 = never)
   int peer_wait_ms = 2000; // FK_W4A16_PEER_WAIT_MS: how long a multi-GPU call waits for the other GPUs
+  int cluster = 1;         // FK_W4A16_CLUSTER: 0 keeps layers with few tiles off the cluster kernel
 };
 Tuning g_tuning;
 std::once_flag g_tuning_once;
@@ -235,6 +237,8 @@ Tuning& tuning() {
     if (env_int("FK_W4A16_PEER_WAIT_MS") > 0) {
       g_tuning.peer_wait_ms = env_int("FK_W4A16_PEER_WAIT_MS");
     }
+    const char* cluster = std::getenv("FK_W4A16_CLUSTER");
+    g_tuning.cluster = cluster == nullptr || std::atoi(cluster) != 0 ? 1 : 0;
   });
   return g_tuning;
 }
@@ -268,13 +272,7 @@ size_t mma_smem_bytes(int warps, int stages, int group, int mt) {
 
 // `sm_count` and `max_smem` describe the device; the plan is a pure function of its arguments
 // so that fk_w4a16_workspace_bytes() and fk_w4a16_gemv() always agree.
-bool cluster_mode_enabled() {
-  static const bool enabled = [] {
-    const char* value = std::getenv("FK_W4A16_CLUSTER");
-    return value == nullptr || std::atoi(value) != 0;
-  }();
-  return enabled;
-}
+bool cluster_mode_enabled() { return tuning().cluster != 0; }
 
 Plan make_plan(int batch, int n, int k, int group_size, int sm_count, int max_smem,
                const LaunchConfig& cfg, bool allow_cluster = false, bool cuda_cores_only = false) {
@@ -585,6 +583,17 @@ int launch_cluster(const GemvParams& params, const Plan& plan, int max_smem, cud
 }
 
 template <int G, int M_TILE, class E>
+int launch_chain(const ChainParams& params, int grid, int warps, size_t smem_bytes, int max_smem,
+                 cudaStream_t stream) {
+  auto kernel = w4a16_gemv_chain_kernel<G, M_TILE, UnpackModeFor<E>>;
+  static std::once_flag optin_flags[kMaxDevices];
+  FK_TRY(ensure_smem_optin(kernel, optin_flags, smem_bytes, max_smem));
+  FK_TRY_CUDA(launch_kernel(kernel, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), smem_bytes, stream,
+                            params));
+  return FK_W4A16_OK;
+}
+
+template <int G, int M_TILE, class E>
 int launch_wmma(const GemvParams& params, const Plan& plan, int max_smem, cudaStream_t stream) {
   if constexpr (M_TILE <= 2) {
     auto kernel = w4a16_gemv_wmma_kernel<G, M_TILE, UnpackModeFor<E>>;
@@ -732,6 +741,8 @@ int fk_w4a16_set_tuning(const char* name, int value) {
     t.wmma = value;
   } else if (key == "umma_min_batch") {
     t.umma_min_batch = value;
+  } else if (key == "cluster") {
+    t.cluster = value != 0 ? 1 : 0;
   } else if (key == "peer_wait_ms") {
     if (value <= 0 || value > 10000) {
       return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "peer_wait_ms must be between 1 and 10000");
@@ -958,7 +969,7 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
   }
   const int num_tiles = n / kTileCols;
-  if (static_cast<long long>(plan.row_tiles) * num_tiles > kTicketCapacity - 1) {
+  if (static_cast<long long>(plan.row_tiles) * num_tiles > kTicketCapacity - 2) {
     return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n * batch exceeds the ticket area of a workspace");
   }
 
@@ -1256,6 +1267,149 @@ int fk_w4a16_gemv_static(const void* activations, const void* packets, void* out
   args.dtype = dtype;
   args.stream = stream;
   return gemv_impl(&args, /*with_exchange_area=*/false, /*small_batch_on_cuda_cores=*/true);
+}
+
+namespace {
+// Warps per CTA and ring depth of the chain kernel for (group size, rows per pass): as many warps
+// as fit with a two-deep ring each, then the deepest ring (at most 4) that still fits.
+void chain_geometry(int group_size, int m_tile, int max_smem, int* warps_out, int* stages_out) {
+  const int per_warp = (2 * packet_stride(group_size)) + (2 * m_tile * kTileCols * 4) +
+                       (m_tile * group_size * 2) + 16;
+  int warps = (max_smem - 256) / per_warp;
+  warps = warps > kMaxWarps ? kMaxWarps : (warps < 1 ? 1 : warps);
+  int stages = 2;
+  for (int candidate = 4; candidate >= 2; --candidate) {
+    if (stream_smem_plan(warps, candidate, group_size, m_tile).total <= static_cast<uint32_t>(max_smem)) {
+      stages = candidate;
+      break;
+    }
+  }
+  *warps_out = warps;
+  *stages_out = stages;
+}
+}  // namespace
+
+size_t fk_w4a16_chain_workspace_bytes(int batch, int group_size) {
+  if (batch <= 0 || batch > 4 || !group_supported(group_size)) {
+    return 0;
+  }
+  DeviceInfo* info = nullptr;
+  if (device_info(&info) != FK_W4A16_OK) {
+    return 0;
+  }
+  const size_t scratch = static_cast<size_t>(info->sm_count) * 2 * (m_tile_for_batch(batch) * kTileCols) * sizeof(float);
+  return kHeaderBytes + ((scratch + 255) & ~size_t{255});
+}
+
+int fk_w4a16_gemv_chain(const fk_w4a16_chain_step* steps, int count, void* workspace,
+                        size_t workspace_bytes, int batch, int group_size, int packet_stride_bytes,
+                        int dtype, void* stream) {
+  if (steps == nullptr || count < 1 || count > FK_W4A16_MAX_CHAIN_STEPS) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "a chain has between 1 and 8 steps");
+  }
+  if (batch > 4) {
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "a chain takes batches of at most 4");
+  }
+  FK_TRY(check_dtype(dtype));
+  FK_TRY(check_pointer(workspace, "workspace", 256));
+  DeviceInfo* info = nullptr;
+  FK_TRY(device_info(&info));
+  for (int i = 0; i < count; ++i) {
+    FK_TRY(check_dimensions(batch, steps[i].n, steps[i].k, group_size));
+  }
+  FK_TRY(check_stride(group_size, packet_stride_bytes));
+  const size_t need = fk_w4a16_chain_workspace_bytes(batch, group_size);
+  if (workspace_bytes < need) {
+    std::ostringstream oss;
+    oss << "workspace_bytes=" << workspace_bytes << " is smaller than the required " << need;
+    return fail(FK_W4A16_ERR_INVALID_ARGUMENT, oss.str());
+  }
+  const int m_tile = m_tile_for_batch(batch);
+  int warps = 0;
+  int stages = 0;
+  chain_geometry(group_size, m_tile, info->max_smem_optin, &warps, &stages);
+  const int grid = info->sm_count;
+  const size_t smem_bytes = stream_smem_plan(warps, stages, group_size, m_tile).total;
+
+  ChainParams chain{};
+  chain.count = count;
+  chain.barrier = reinterpret_cast<unsigned int*>(static_cast<int*>(workspace) + (kTicketCapacity - 2));
+  chain.exit_count = reinterpret_cast<unsigned int*>(static_cast<int*>(workspace) + (kTicketCapacity - 1));
+  chain.barrier_wait_ns = static_cast<unsigned long long>(tuning().peer_wait_ms) * 1000000ull;
+  const size_t exchange_bytes =
+      static_cast<size_t>(grid) * m_tile * kTileCols * sizeof(unsigned long long);
+  for (int i = 0; i < count; ++i) {
+    const fk_w4a16_chain_step& step = steps[i];
+    FK_TRY(check_pointer(step.activations, "activations", 16));
+    FK_TRY(check_pointer(step.packets, "packets", 16));
+    FK_TRY(check_pointer(step.output, "output", 8));
+    if (step.epilogue != FK_W4A16_EPILOGUE_NONE && step.epilogue != FK_W4A16_EPILOGUE_SILU_MUL) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "unknown epilogue");
+    }
+    const bool gated = step.epilogue == FK_W4A16_EPILOGUE_SILU_MUL;
+    if (gated && (step.n % (2 * kTileCols)) != 0) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "the SiLU-and-multiply epilogue needs n to be a multiple of 256 ([gate; up] halves of whole tiles)");
+    }
+    const size_t gated_bytes = gated ? static_cast<size_t>(batch) * (step.n / 2) * sizeof(unsigned long long) : 0;
+    if (exchange_bytes + gated_bytes > kExchangeBytes) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "the SiLU-and-multiply epilogue of this step does not fit the workspace header's exchange area");
+    }
+    if (step.residual != nullptr) {
+      FK_TRY(check_pointer(step.residual, "residual", 8));
+    }
+    if (step.norm_weight != nullptr) {
+      FK_TRY(check_pointer(step.norm_weight, "norm_weight", 16));
+      if (!(step.norm_eps >= 0.0f)) {
+        return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "the fused RMSNorm needs a non-negative norm_eps");
+      }
+    }
+    const int num_tiles = step.n / kTileCols;
+    if (num_tiles > kTicketCapacity - 2) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT, "n exceeds the ticket area of a workspace");
+    }
+    const long long total_packets = static_cast<long long>(num_tiles) * (step.k / group_size);
+    long long workers = static_cast<long long>(grid) * warps;
+    workers = workers > total_packets ? total_packets : workers;
+
+    GemvParams& params = chain.step[i];
+    params.act = step.activations;
+    params.packets = static_cast<const uint8_t*>(step.packets);
+    params.out = step.output;
+    params.tickets = static_cast<int*>(workspace);
+    params.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kHeaderBytes);
+    params.exchange = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(workspace) + kTicketBytes);
+    params.gated = gated ? reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(workspace) + kTicketBytes +
+                                                                 exchange_bytes)
+                         : nullptr;
+    params.status = info->status_word;
+    params.out_ld = gated ? step.n / 2 : step.n;
+    params.out_col0 = 0;
+    params.out_f32 = 0;
+    params.num_peers = 0;
+    params.residual = step.residual;
+    params.norm_weight = step.norm_weight;
+    params.norm_eps = step.norm_eps;
+    params.local_signal = nullptr;
+    params.m = batch;
+    params.n = step.n;
+    params.k = step.k;
+    params.num_groups = step.k / group_size;
+    params.num_tiles = num_tiles;
+    params.active_warps = static_cast<int>(workers);
+    params.stages = stages;
+    params.total_packets = static_cast<uint32_t>(total_packets);
+    params.run_base = params.total_packets / static_cast<uint32_t>(workers);
+    params.run_rem = params.total_packets % static_cast<uint32_t>(workers);
+    params.run_magic = ((uint64_t{1} << 40) / static_cast<uint64_t>(workers)) + 1;
+    params.run_inv = static_cast<float>(static_cast<double>(workers) / static_cast<double>(total_packets));
+  }
+  auto* s = static_cast<cudaStream_t>(stream);
+  return dispatch(group_size, m_tile, dtype, [&](auto g, auto mt, auto e) {
+    return launch_chain<decltype(g)::value, decltype(mt)::value, decltype(e)>(chain, grid, warps, smem_bytes,
+                                                                               info->max_smem_optin, s);
+  });
 }
 
 int fk_w4a16_gemv_split_k(const void* activations, const void* packets, float* partials, int batch,

@@ -246,7 +246,7 @@ __device__ __forceinline__ bool gated_meet(const GemvParams& p, int row, uint32_
 template <class E>
 __device__ __forceinline__ void store_element_at(const GemvParams& p, long long offset, float value) {
   if (p.residual != nullptr) {
-    value += E::to_float(static_cast<const unsigned short*>(p.residual)[offset]);
+    value += E::to_float(__ldcg(static_cast<const unsigned short*>(p.residual) + offset));
   }
   for (int dest = -1; dest < p.num_peers; ++dest) {
     void* out = dest < 0 ? p.out : p.peer_out[dest];
@@ -289,7 +289,9 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
                            (static_cast<long long>(tile) * kTileCols);
   float v[4] = {y[0], y[1], y[2], y[3]};
   if (p.residual != nullptr) {
-    const uint2 r = *(reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(p.residual) + offset) + lane);
+    // L2-coherent load: in a chain of steps inside one launch the residual may be what another SM
+    // wrote a step ago
+    const uint2 r = __ldcg(reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(p.residual) + offset) + lane);
     v[0] += E::to_float(static_cast<unsigned short>(r.x & 0xffffu));
     v[1] += E::to_float(static_cast<unsigned short>(r.x >> 16));
     v[2] += E::to_float(static_cast<unsigned short>(r.y & 0xffffu));
@@ -320,7 +322,7 @@ __device__ __forceinline__ void cta_inverse_rms(const GemvParams& p, int row0, i
       const uint4* row = reinterpret_cast<const uint4*>(static_cast<const unsigned short*>(p.act) +
                                                         (static_cast<size_t>(row0 + m) * p.k));
       for (int i = static_cast<int>(threadIdx.x); i < units; i += static_cast<int>(blockDim.x)) {
-        const uint4 v = __ldg(row + i);
+        const uint4 v = __ldcg(row + i);  // L2-coherent: see the chain kernel
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -363,6 +365,78 @@ __device__ __forceinline__ uint2 normalise4(uint2 raw, uint2 weight, float inv_r
   out.x = one(raw.x & 0xffffu, weight.x & 0xffffu) | (one(raw.x >> 16, weight.x >> 16) << 16);
   out.y = one(raw.y & 0xffffu, weight.y & 0xffffu) | (one(raw.y >> 16, weight.y >> 16) << 16);
   return out;
+}
+
+// One packet's worth of work for a warp: stages the group's activations (`raw`: this lane's four
+// consecutive 16-bit activations per batch row) into the warp's shared-memory buffer `act_addr`,
+// multiplies the packet at shared-memory address `stage` with them and folds scale, offset and the
+// unpack constant into the running sums: y += alpha * (acc - B_g) + beta * S_g.
+template <int G, int M_TILE, class Mode>
+__device__ __forceinline__ void multiply_packet(uint32_t stage, uint32_t act_addr,
+                                                const uint2 (&raw)[M_TILE], int m_act, int lane,
+                                                float (&y)[M_TILE][4]) {
+  using E = typename Mode::Elem;
+  constexpr int kQBytes = packet_q_bytes(G);
+  constexpr int kActBytes = G * 2;
+  constexpr int kWordRows = G / 8;
+  float group_sum[M_TILE];
+  float acc[M_TILE][4][2];
+#pragma unroll
+  for (int m = 0; m < M_TILE; ++m) {
+    float bias = 0.0f;
+    group_sum[m] = 0.0f;
+    if (m < m_act) {
+      stage_activations<G, Mode>(raw[m], act_addr + (m * kActBytes), lane, group_sum[m], bias);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      acc[m][c][0] = -bias;
+      acc[m][c][1] = 0.0f;
+    }
+  }
+  __syncwarp();
+
+#pragma unroll 4
+  for (int r = 0; r < kWordRows; ++r) {
+    const uint4 wq = lds128(stage + (r * (kTileCols * 4)) + (lane * 16));
+    NibblePairs u[4];
+    u[0] = Mode::unpack(wq.x);
+    u[1] = Mode::unpack(wq.y);
+    u[2] = Mode::unpack(wq.z);
+    u[3] = Mode::unpack(wq.w);
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+      const uint4 a = lds128(act_addr + (m * kActBytes) + (r * 16));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        Mode::mac(acc[m][c][0], acc[m][c][1], u[c], a);
+      }
+    }
+  }
+
+  {
+    const uint2 a_raw = lds64(stage + kQBytes + (lane * 8));
+    const uint2 b_raw = lds64(stage + kQBytes + (kTileCols * 2) + (lane * 8));
+    float alpha[4];
+    float beta[4];
+    alpha[0] = E::to_float(static_cast<unsigned short>(a_raw.x & 0xffffu));
+    alpha[1] = E::to_float(static_cast<unsigned short>(a_raw.x >> 16));
+    alpha[2] = E::to_float(static_cast<unsigned short>(a_raw.y & 0xffffu));
+    alpha[3] = E::to_float(static_cast<unsigned short>(a_raw.y >> 16));
+    beta[0] = E::to_float(static_cast<unsigned short>(b_raw.x & 0xffffu));
+    beta[1] = E::to_float(static_cast<unsigned short>(b_raw.x >> 16));
+    beta[2] = E::to_float(static_cast<unsigned short>(b_raw.y & 0xffffu));
+    beta[3] = E::to_float(static_cast<unsigned short>(b_raw.y >> 16));
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float dot = acc[m][c][0] + acc[m][c][1];
+        y[m][c] = fmaf(alpha[c], dot, y[m][c]);
+        y[m][c] = fmaf(beta[c], group_sum[m], y[m][c]);
+      }
+    }
+  }
 }
 
 // One warp's pass over packets [p_begin, p_end) of the tile-major packet stream, accumulating
@@ -495,64 +569,7 @@ __device__ __forceinline__ bool consume_packet_run(const GemvParams& p, uint32_t
       load_activations(next_raw);
     }
 
-    float group_sum[M_TILE];
-    float acc[M_TILE][4][2];
-#pragma unroll
-    for (int m = 0; m < M_TILE; ++m) {
-      float bias = 0.0f;
-      group_sum[m] = 0.0f;
-      if (m < m_act) {
-        stage_activations<G, Mode>(raw[m], act_addr + (m * kActBytes), lane, group_sum[m], bias);
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        acc[m][c][0] = -bias;
-        acc[m][c][1] = 0.0f;
-      }
-    }
-    __syncwarp();
-
-#pragma unroll 4
-    for (int r = 0; r < kWordRows; ++r) {
-      const uint4 wq = lds128(stage + (r * (kTileCols * 4)) + (lane * 16));
-      NibblePairs u[4];
-      u[0] = Mode::unpack(wq.x);
-      u[1] = Mode::unpack(wq.y);
-      u[2] = Mode::unpack(wq.z);
-      u[3] = Mode::unpack(wq.w);
-#pragma unroll
-      for (int m = 0; m < M_TILE; ++m) {
-        const uint4 a = lds128(act_addr + (m * kActBytes) + (r * 16));
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          Mode::mac(acc[m][c][0], acc[m][c][1], u[c], a);
-        }
-      }
-    }
-
-    {
-      const uint2 a_raw = lds64(stage + kQBytes + (lane * 8));
-      const uint2 b_raw = lds64(stage + kQBytes + (kTileCols * 2) + (lane * 8));
-      float alpha[4];
-      float beta[4];
-      alpha[0] = E::to_float(static_cast<unsigned short>(a_raw.x & 0xffffu));
-      alpha[1] = E::to_float(static_cast<unsigned short>(a_raw.x >> 16));
-      alpha[2] = E::to_float(static_cast<unsigned short>(a_raw.y & 0xffffu));
-      alpha[3] = E::to_float(static_cast<unsigned short>(a_raw.y >> 16));
-      beta[0] = E::to_float(static_cast<unsigned short>(b_raw.x & 0xffffu));
-      beta[1] = E::to_float(static_cast<unsigned short>(b_raw.x >> 16));
-      beta[2] = E::to_float(static_cast<unsigned short>(b_raw.y & 0xffffu));
-      beta[3] = E::to_float(static_cast<unsigned short>(b_raw.y >> 16));
-#pragma unroll
-      for (int m = 0; m < M_TILE; ++m) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float dot = acc[m][c][0] + acc[m][c][1];
-          y[m][c] = fmaf(alpha[c], dot, y[m][c]);
-          y[m][c] = fmaf(beta[c], group_sum[m], y[m][c]);
-        }
-      }
-    }
+    multiply_packet<G, M_TILE, Mode>(stage, act_addr, raw, m_act, lane, y);
 
     // The whole warp is done reading this buffer: hand it back to the copy engine.
     __syncwarp();

@@ -70,6 +70,25 @@ class GemvArgs(ctypes.Structure):
     ]
 
 
+MAX_CHAIN_STEPS = 8
+
+
+class ChainStep(ctypes.Structure):
+    """struct fk_w4a16_chain_step (include/fk_w4a16.h)."""
+
+    _fields_ = [
+        ("activations", _c_void_p),
+        ("packets", _c_void_p),
+        ("output", _c_void_p),
+        ("n", _c_int),
+        ("k", _c_int),
+        ("residual", _c_void_p),
+        ("epilogue", _c_int),
+        ("norm_weight", _c_void_p),
+        ("norm_eps", ctypes.c_float),
+    ]
+
+
 # name -> (restype, argtypes); mirrors include/fk_w4a16.h one to one.
 SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "fk_w4a16_last_error": (ctypes.c_char_p, []),
@@ -89,6 +108,11 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
          _c_int, _c_int, _c_void_p],
     ),
     "fk_w4a16_set_variant": (_c_int, [_c_int]),
+    "fk_w4a16_chain_workspace_bytes": (_c_size_t, [_c_int, _c_int]),
+    "fk_w4a16_gemv_chain": (
+        _c_int,
+        [ctypes.POINTER(ChainStep), _c_int, _c_void_p, _c_size_t, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    ),
     "fk_w4a16_describe_plan": (_c_int, [_c_int, _c_int, _c_int, _c_int, _c_int, ctypes.c_char_p, ctypes.c_size_t]),
     "fk_w4a16_set_tuning": (_c_int, [ctypes.c_char_p, _c_int]),
     "fk_w4a16_gemv_host": (

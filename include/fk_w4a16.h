@@ -166,6 +166,35 @@ typedef struct fk_w4a16_gemv_args {
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 
+/* A chain of GEMVs in ONE persistent launch (no counterpart in the reference, whose Python caller
+ * launches two or three kernels per GEMV). Step i + 1 may read what step i wrote -- a decoder's
+ * o_proj -> gate/up -> down_proj -> next qkv with the fused residual / SiLU-and-multiply / RMSNorm
+ * options in between -- and the results are those of the same steps issued one after another as
+ * fk_w4a16_gemv_ex calls on the stream. What the chain saves is what lies between two launches
+ * (grid completion, CTA launch, first copies: several microseconds per call at decode sizes): the
+ * grid stays resident, steps are separated by a grid-wide barrier inside the kernel, and every warp
+ * starts copying its share of the next step's weights as soon as it has consumed its share of the
+ * current one. All steps share batch (at most 4), group size, packet stride and element type.
+ * Workspace: fk_w4a16_chain_workspace_bytes(batch, group_size) bytes, zero-filled once
+ * (fk_w4a16_workspace_init), reusable, one per chain running at a time. The kernel needs
+ * every SM of the device for itself while it runs (one CTA per SM, all resident: they wait for one
+ * another); its waits are bounded ("peer_wait_ms") and report through the device status word. */
+#define FK_W4A16_MAX_CHAIN_STEPS 8
+typedef struct fk_w4a16_chain_step {
+  const void* activations; /* [batch, k] */
+  const void* packets;     /* the layer's ARC packets */
+  void* output;            /* [batch, n], or [batch, n/2] with the SiLU-and-multiply epilogue */
+  int n, k;
+  const void* residual;    /* as in fk_w4a16_gemv_args, or NULL */
+  int epilogue;            /* FK_W4A16_EPILOGUE_* */
+  const void* norm_weight; /* as in fk_w4a16_gemv_args, or NULL */
+  float norm_eps;
+} fk_w4a16_chain_step;
+FK_W4A16_API size_t fk_w4a16_chain_workspace_bytes(int batch, int group_size);
+FK_W4A16_API int fk_w4a16_gemv_chain(const fk_w4a16_chain_step* steps, int count, void* workspace,
+                        size_t workspace_bytes, int batch, int group_size, int packet_stride_bytes,
+                        int dtype, void* stream);
+
 /* fk_w4a16_gemv for callers that cannot hand over scratch memory. This entry point has no
  * counterpart in the reference. It is meant for hosts where device allocation is off the table
  * once start-up is over: a serving process that has already handed all free device memory to its
@@ -241,6 +270,7 @@ FK_W4A16_API int fk_w4a16_describe_plan(int batch, int n, int k, int group_size,
  * planning call: "mma_min_batch" (FK_W4A16_MMA_MIN_BATCH: smallest batch that takes the mma.sync
  * kernel, 0 = built-in rule), "cluster_min" / "cluster_size" (FK_W4A16_CLUSTER_MIN / _SIZE),
  * "wmma" (FK_W4A16_WMMA: batches 1-2 on the warp-level mma.sync form of the stream kernel),
+ * "cluster" (FK_W4A16_CLUSTER: 0 keeps every layer off the cluster kernel),
  * "umma_min_batch" (FK_W4A16_UMMA_MIN_BATCH: smallest batch that takes the pipelined tcgen05
  * kernel, 0 = never, -1 = built-in default), "peer_wait_ms" (FK_W4A16_PEER_WAIT_MS: how long a
  * multi-GPU call waits for the other GPUs before it gives up, default 2000). Results never depend
