@@ -210,7 +210,8 @@ def test_native_forward_can_be_captured_after_one_warm_up_call() -> None:
             call(side)
         graph.replay()
         side.synchronize()
-        assert torch.cuda.mem_get_info()[0] == free_before  # nothing was allocated for the capture
+        # nothing was allocated for the capture (torch may hand cached blocks back meanwhile)
+        assert torch.cuda.mem_get_info()[0] >= free_before
     _assert_matches(out, cpu, group)
 
     fresh = torch.cuda.Stream()

@@ -104,7 +104,7 @@ def test_static_scratch_entry_point_leaves_free_memory_alone() -> None:
         capi.check(lib.fk_w4a16_gemv_static(act.data_ptr(), packets.data_ptr(), out.data_ptr(), 2, shape.n,
                                             shape.k, 128, 8704, 1, stream_ptr()))
     torch.cuda.synchronize()
-    assert torch.cuda.mem_get_info()[0] == before
+    assert torch.cuda.mem_get_info()[0] >= before  # never less: the calls allocated nothing
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit() -> None:
