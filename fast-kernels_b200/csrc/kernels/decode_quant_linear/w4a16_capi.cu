@@ -927,6 +927,31 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   if (args->residual != nullptr) {
     FK_TRY(check_pointer(args->residual, "residual", 8));
   }
+  if (args->ll_epoch_counter != nullptr) {
+    FK_TRY(check_pointer(args->ll_epoch_counter, "ll_epoch_counter", 8));
+    if (args->ll_epoch != 0 || args->ll_parity_words < 0 || (args->ll_parity_words % 2) != 0) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "with ll_epoch_counter, ll_epoch must be 0 and ll_parity_words a non-negative even number");
+    }
+  }
+  if (args->ll_epoch != 0 || args->ll_epoch_counter != nullptr) {
+    if (args->local_signal != nullptr || args->reduce_slots != 0 || gated) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "the flag-in-data exchange (ll_epoch) excludes the counter exchange, reduce_slots and the "
+                  "SiLU-and-multiply epilogue");
+    }
+    if (args->ll_slots < 1 || args->ll_slots > FK_W4A16_MAX_PEERS + 1 || args->ll_slot_cols < 1 ||
+        (args->ll_slot_cols % 4) != 0) {
+      return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
+                  "ll_slots must be between 1 and 8 and ll_slot_cols a positive multiple of 4");
+    }
+    FK_TRY(check_pointer(args->ll_input, "ll_input", 16));
+    FK_TRY(check_pointer(args->ll_output, "ll_output", 2));
+    FK_TRY(check_pointer(args->output, "output", 16));
+    for (int peer = 0; peer < args->num_peers; ++peer) {
+      FK_TRY(check_pointer(args->peer_outputs[peer], "peer_outputs[i]", 16));
+    }
+  }
   if (args->reduce_slots != 0) {
     if (args->reduce_slots < 0 || args->reduce_slots > FK_W4A16_MAX_PEERS + 1 || args->local_signal == nullptr) {
       return fail(FK_W4A16_ERR_INVALID_ARGUMENT,
@@ -1029,6 +1054,15 @@ int gemv_impl(const fk_w4a16_gemv_args* args, bool with_exchange_area, bool smal
   params.reduce_input = args->reduce_input;
   params.reduce_output = args->reduce_output;
   params.reduce_slots = args->reduce_slots;
+  params.ll_epoch = args->ll_epoch;
+  params.ll_epoch_counter = args->ll_epoch_counter;
+  params.ll_ticket = args->ll_epoch_counter != nullptr ? args->ll_epoch_counter + 1 : nullptr;
+  params.ll_parity_words = args->ll_parity_words;
+  params.ll_input = static_cast<const unsigned long long*>(args->ll_input);
+  params.ll_output = args->ll_output;
+  params.ll_slots = args->ll_slots;
+  params.ll_slot_cols = args->ll_slot_cols;
+  params.ll_reduce = args->ll_reduce != 0 ? 1 : 0;
   params.m = batch;
   params.n = n;
   params.k = k;

@@ -109,6 +109,28 @@ struct GemvParams {
   const float* reduce_input;        // [reduce_slots][m][n] fp32 in THIS GPU's memory
   void* reduce_output;              // [m][n] 16-bit
   int reduce_slots;
+  // Flag-in-data exchange, or ll_epoch == 0. Outputs are then written -- to `out` and to every
+  // peer_out -- as 8-byte words {fp32 value, ll_epoch}: an 8-byte store is atomic, so a word whose
+  // flag shows this call's epoch carries this call's value, and the exchange needs no fence, no
+  // counter and no round trip. ll_input is this GPU's receive area [ll_slots][m][ll_slot_cols]
+  // words (one slot per GPU of the group, its own included); once a word has arrived, the first
+  // few CTAs turn it into the final 16-bit output: ll_reduce == 0 concatenates the slots' columns
+  // (an N-split), ll_reduce == 1 adds the slots in order (a K-split).
+  // The epoch is either given (ll_epoch) or kept on the device (ll_epoch_counter: the epoch of a
+  // call is *counter + 1, and the last receiving CTA adds 1 when the call is complete), which is
+  // what lets a captured call be replayed: nothing about the exchange is baked into the launch.
+  // With the counter, the receive area alternates between two copies ll_parity_words apart
+  // (epoch & 1), here and in every peer_out, so that a GPU that runs one call ahead cannot
+  // overwrite words that a peer has not read yet.
+  unsigned int ll_epoch;
+  unsigned int* ll_epoch_counter;   // device word, zero before the first call; or null
+  unsigned int* ll_ticket;          // device word, zero between calls (counts finished receivers)
+  long long ll_parity_words;
+  const unsigned long long* ll_input;
+  void* ll_output;                  // [m][ll_slots * ll_slot_cols] or [m][ll_slot_cols] 16-bit
+  int ll_slots;
+  int ll_slot_cols;
+  int ll_reduce;
   int m, n, k;
   int num_groups;          // k / G
   int num_tiles;           // n / 128
@@ -198,9 +220,29 @@ __device__ __forceinline__ void stage_activations(uint2 raw, uint32_t act_addr, 
   b_out = warp_sum(b);
 }
 
+// Epoch of this call in the flag-in-data exchange; 0 when that exchange is off.
+__device__ __forceinline__ unsigned int ll_epoch_now(const GemvParams& p) {
+  if (p.ll_epoch_counter != nullptr) {
+    return __ldcg(p.ll_epoch_counter) + 1u;
+  }
+  return p.ll_epoch;
+}
+
+// A flag-in-data word: value in the low half, the call's epoch in the high half.
+__device__ __forceinline__ unsigned long long ll_word(float value, unsigned int epoch) {
+  return (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(value);
+}
+
 template <class E>
 __device__ __forceinline__ void store_tile_row_to(void* out, int out_f32, long long elem_offset,
-                                                  int lane, const float (&y)[4]) {
+                                                  int lane, const float (&y)[4], unsigned int ll_epoch = 0) {
+  if (ll_epoch != 0) {
+    // four 8-byte words as two 16-byte stores; each word is valid on its own
+    auto* dst = reinterpret_cast<ulonglong2*>(static_cast<unsigned long long*>(out) + elem_offset) + (lane * 2);
+    dst[0] = make_ulonglong2(ll_word(y[0], ll_epoch), ll_word(y[1], ll_epoch));
+    dst[1] = make_ulonglong2(ll_word(y[2], ll_epoch), ll_word(y[3], ll_epoch));
+    return;
+  }
   if (out_f32 != 0) {
     auto* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + elem_offset) + lane;
     *dst = make_float4(y[0], y[1], y[2], y[3]);
@@ -248,9 +290,13 @@ __device__ __forceinline__ void store_element_at(const GemvParams& p, long long 
   if (p.residual != nullptr) {
     value += E::to_float(__ldcg(static_cast<const unsigned short*>(p.residual) + offset));
   }
+  const unsigned int epoch = ll_epoch_now(p);
+  const long long ll_offset = offset + ((epoch & 1u) != 0 ? p.ll_parity_words : 0);
   for (int dest = -1; dest < p.num_peers; ++dest) {
     void* out = dest < 0 ? p.out : p.peer_out[dest];
-    if (p.out_f32 != 0) {
+    if (epoch != 0) {
+      static_cast<unsigned long long*>(out)[ll_offset] = ll_word(value, epoch);
+    } else if (p.out_f32 != 0) {
       static_cast<float*>(out)[offset] = value;
     } else {
       static_cast<unsigned short*>(out)[offset] = E::from_float(value);
@@ -297,9 +343,11 @@ __device__ __forceinline__ void store_tile_row(const GemvParams& p, int row, uin
     v[2] += E::to_float(static_cast<unsigned short>(r.y & 0xffffu));
     v[3] += E::to_float(static_cast<unsigned short>(r.y >> 16));
   }
-  store_tile_row_to<E>(p.out, p.out_f32, offset, lane, v);
+  const unsigned int epoch = ll_epoch_now(p);
+  const long long placed = offset + ((epoch & 1u) != 0 ? p.ll_parity_words : 0);
+  store_tile_row_to<E>(p.out, p.out_f32, placed, lane, v, epoch);
   for (int peer = 0; peer < p.num_peers; ++peer) {
-    store_tile_row_to<E>(p.peer_out[peer], p.out_f32, offset, lane, v);
+    store_tile_row_to<E>(p.peer_out[peer], p.out_f32, placed, lane, v, epoch);
   }
 }
 
@@ -638,8 +686,93 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 constexpr unsigned int kReduceCtas = 8;
 
+__device__ __forceinline__ unsigned long long load_word_system(const unsigned long long* word) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(word) : "memory");
+  return v;
+}
+
+// The receiving side of the flag-in-data exchange: every CTA of the grid, once its own work is
+// done, takes a share of this GPU's final outputs, waits for the words they are made of to show
+// the call's epoch and writes them in the 16-bit type. A thread has one or two outputs; the loads
+// of all the words of an output (one per slot for a K-split) are issued together and only the
+// missing ones are polled again (bounded by peer_wait_ns). Polling with a few threads instead --
+// each walking many words one L2 round trip after the other -- cost microseconds.
+template <class E>
+__device__ __forceinline__ void ll_receive(const GemvParams& p) {
+  const unsigned int ctas_total = gridDim.x * gridDim.y;
+  const unsigned int cta_index = (blockIdx.y * gridDim.x) + blockIdx.x;
+  const unsigned int epoch = ll_epoch_now(p);  // read before any waiting: it moves when the call is complete
+  const unsigned long long* input = p.ll_input + ((epoch & 1u) != 0 ? p.ll_parity_words : 0);
+  const long long slot_words = static_cast<long long>(p.m) * p.ll_slot_cols;
+  const long long out_cols = p.ll_reduce != 0 ? p.ll_slot_cols : static_cast<long long>(p.ll_slots) * p.ll_slot_cols;
+  const long long total = static_cast<long long>(p.m) * out_cols;
+  const unsigned long long start = global_timer_ns();
+  bool gave_up = false;
+  auto* out = static_cast<unsigned short*>(p.ll_output);
+  for (long long e = (static_cast<long long>(cta_index) * blockDim.x) + threadIdx.x; e < total;
+       e += static_cast<long long>(ctas_total) * blockDim.x) {
+    const long long row = e / out_cols;
+    const long long col = e - (row * out_cols);
+    const unsigned long long* word[kMaxPeers + 1];
+    unsigned long long seen[kMaxPeers + 1];
+    int words = 1;
+    if (p.ll_reduce != 0) {
+      words = p.ll_slots;
+#pragma unroll
+      for (int s = 0; s < kMaxPeers + 1; ++s) {
+        word[s] = input + (s * slot_words) + (row * p.ll_slot_cols) + col;
+      }
+    } else {
+      const long long s = col / p.ll_slot_cols;
+      word[0] = input + (s * slot_words) + (row * p.ll_slot_cols) + (col - (s * p.ll_slot_cols));
+    }
+#pragma unroll
+    for (int s = 0; s < kMaxPeers + 1; ++s) {
+      if (s < words) {
+        seen[s] = load_word_system(word[s]);
+      }
+    }
+    float value = 0.0f;
+#pragma unroll
+    for (int s = 0; s < kMaxPeers + 1; ++s) {  // slots in order: the sum is reproducible
+      if (s < words) {
+        while (static_cast<unsigned int>(seen[s] >> 32) != epoch && !gave_up) {
+          if (global_timer_ns() - start > p.peer_wait_ns) {
+            gave_up = true;
+            break;
+          }
+          seen[s] = load_word_system(word[s]);
+        }
+        value += __uint_as_float(static_cast<unsigned int>(seen[s]));
+      }
+    }
+    out[e] = E::from_float(value);
+  }
+  if (gave_up) {
+    atomicExch(p.status, static_cast<int>(kStatusPeerWaitTimeout));
+  }
+  if (p.ll_epoch_counter != nullptr) {
+    // The last CTA to finish closes the call: every word has been read and every CTA has read the
+    // epoch, so the counter may move on.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(p.ll_ticket, 1u) == ctas_total - 1) {
+        *p.ll_ticket = 0u;
+        *p.ll_epoch_counter = epoch;
+        __threadfence();
+      }
+    }
+  }
+}
+
 template <class E>
 __device__ __forceinline__ void exchange_complete(const GemvParams& p) {
+  if (p.ll_epoch != 0 || p.ll_epoch_counter != nullptr) {
+    ll_receive<E>(p);
+    return;
+  }
   if (p.local_signal == nullptr) {
     return;
   }

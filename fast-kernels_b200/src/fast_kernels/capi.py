@@ -67,6 +67,14 @@ class GemvArgs(ctypes.Structure):
         ("reduce_input", _c_void_p),
         ("reduce_output", _c_void_p),
         ("reduce_slots", _c_int),
+        ("ll_epoch", ctypes.c_uint),
+        ("ll_epoch_counter", _c_void_p),
+        ("ll_parity_words", ctypes.c_longlong),
+        ("ll_input", _c_void_p),
+        ("ll_output", _c_void_p),
+        ("ll_slots", _c_int),
+        ("ll_slot_cols", _c_int),
+        ("ll_reduce", _c_int),
     ]
 
 

@@ -13,11 +13,12 @@ Two exchanges:
 * ``exchange="nccl"``: ``all_gather_into_tensor`` / ``all_reduce`` on the group, enqueued on the
   GEMV's stream. Works on any backend (the CPU tests run it over gloo).
 * ``exchange="peer"`` (CUDA, one node): the GEMV kernel itself stores every finished tile into all
-  ranks' buffers through peer-mapped symmetric memory while it is still streaming weights; every
-  CTA then signals every rank and the kernel waits (bounded) until all CTAs of all ranks have
-  delivered; a row split's sum over ranks happens in the same kernel -- one launch does compute,
-  exchange and reduction, no collective call. Results live in a double-buffered symmetric buffer: the tensor
-  a call returns stays valid until the second-next call on this layer.
+  ranks' receive areas through peer-mapped symmetric memory while it is still streaming weights,
+  as 8-byte words that carry the call's epoch beside the value (an 8-byte store is atomic, so
+  there is nothing to fence and nothing to signal); the kernel's first CTAs turn the words into
+  the final 16-bit result as they arrive (bounded wait) -- side by side for a column split, added
+  in rank order for a row split. One launch does compute, exchange and reduction, no collective
+  call, and because the call count lives on the device a captured call can be replayed.
 
 One process per GPU; all ranks must call ``forward`` the same number of times in the same order.
 """
@@ -180,10 +181,9 @@ class ShardedW4A16Linear:
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm
 
-        if self.mode == "column":
-            slot = self.max_batch * self.n * 2
-        else:
-            slot = self.world * self.max_batch * self.n * 4
+        # receive area: one slot of 8-byte words {fp32 value, epoch} per rank, two areas (epoch parity)
+        cols = self.n_local if self.mode == "column" else self.n
+        slot = self.world * self.max_batch * cols * 8
         slot = (slot + 255) & ~255
         total = self._SIGNAL_BYTES + 2 * slot
         group = self.group if self.group is not None else dist.group.WORLD
@@ -200,38 +200,35 @@ class ShardedW4A16Linear:
         }
 
     def _forward_peer(self, local_act: Any) -> Any:
+        """Flag-in-data exchange: every result travels as an 8-byte word {fp32 value, call epoch}
+        into slot `rank` of every rank's receive area; the kernel's first CTAs assemble the final
+        16-bit output from the words as they arrive -- concatenated (column split) or added in
+        rank order (row split). No fence, no counters, one launch. The call count lives on the
+        device (first words of the symmetric buffer), so a captured call can be replayed."""
         torch = _torch()
         from fast_kernels import capi
 
         lib = capi.load_library()
         peer = self._peer
         m = local_act.shape[0]
-        slot_offset = self._SIGNAL_BYTES + (self._calls % 2) * peer["slot"]
+        cols = self.n_local if self.mode == "column" else self.n
+        area_offset = self._SIGNAL_BYTES  # the even-epoch area; the odd one lies `slot` bytes behind
+        slot_offset = area_offset + self.rank * m * cols * 8
         ptrs = peer["ptrs"]
         others = [r for r in range(self.world) if r != self.rank]
-        want_f32 = self.mode == "row"
-        # where this rank's results land inside a destination's slot
-        shard_offset = self.rank * m * self.n * 4 if want_f32 else 0
-
-        args = self._gemv_args(local_act, peer["buffer"], want_f32)
-        args.output = ptrs[self.rank] + slot_offset + shard_offset
-        args.output_ld = self.n
-        args.output_col0 = 0 if want_f32 else self.rank * self.n_local
+        out = torch.empty((m, self.n), dtype=self.dtype, device=self.device)
+        args = self._gemv_args(local_act, out, False)
+        args.output = ptrs[self.rank] + slot_offset
+        args.output_ld = cols
         args.num_peers = len(others)
         for i, r in enumerate(others):
-            args.peer_outputs[i] = ptrs[r] + slot_offset + shard_offset
-            args.peer_signals[i] = ptrs[r]
-        args.local_signal = ptrs[self.rank]
-        args.wait_value = (self._calls * self.world) & 0xFFFFFFFF
-        view = peer["buffer"][slot_offset:slot_offset + peer["slot"]]
-        if not want_f32:
-            capi.check(lib.fk_w4a16_gemv_ex(args))
-            return view[: m * self.n * 2].view(self.dtype).view(m, self.n)
-        # K-split: the kernel itself adds the partials of all ranks, in rank order, once the
-        # counters show that every rank has delivered -- one launch for GEMV, exchange and sum
-        out = torch.empty((m, self.n), dtype=self.dtype, device=self.device)
-        args.reduce_input = ptrs[self.rank] + slot_offset
-        args.reduce_output = out.data_ptr()
-        args.reduce_slots = self.world
+            args.peer_outputs[i] = ptrs[r] + slot_offset
+        args.ll_epoch_counter = ptrs[self.rank]
+        args.ll_parity_words = peer["slot"] // 8
+        args.ll_input = ptrs[self.rank] + area_offset
+        args.ll_output = out.data_ptr()
+        args.ll_slots = self.world
+        args.ll_slot_cols = cols
+        args.ll_reduce = 1 if self.mode == "row" else 0
         capi.check(lib.fk_w4a16_gemv_ex(args))
         return out

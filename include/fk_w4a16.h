@@ -114,9 +114,13 @@ FK_W4A16_API int fk_w4a16_gemv_host(const void* host_activations, const void* pa
  *     ("peer_wait_ms" of fk_w4a16_set_tuning) it gives up and sets the device status word. With
  *     wait_value = calls_so_far * (GPUs in the group), kernels queued after this call on the same
  *     stream see every GPU's contribution. Every GPU of the group must run the same problem shape
- *     on the same kind of device (the counters count CTAs). Leave local_signal NULL for single-GPU use.
+ *     on the same kind of device (the counters count CTAs). wait_value is fixed per call, so a call
+ *     recorded into a CUDA graph cannot be replayed with these counters: the ll_* exchange below
+ *     keeps its call count on the device for that. Leave local_signal NULL for single-GPU use.
  *   - reduce_input / reduce_output / reduce_slots: a K-split layer's sum over GPUs, fused behind the
  *     exchange: see the fields.
+ *   - ll_epoch and the ll_* fields: the same exchange with the flag inside every stored word
+ *     instead of counters: see the fields.
  *   - residual, epilogue, norm_weight / norm_eps: see the fields.
  * Zero-initialise the struct; unset fields then mean "default". */
 #define FK_W4A16_MAX_PEERS 7
@@ -163,6 +167,33 @@ typedef struct fk_w4a16_gemv_args {
   const float* reduce_input;
   void* reduce_output;
   int reduce_slots;
+  /* Flag-in-data exchange, or ll_epoch = 0: the lowest-latency way to share a sharded layer's
+   * result. With ll_epoch != 0, `output` and `peer_outputs` are arrays of 8-byte words laid out
+   * like an fp32 output (output_ld / output_col0 count words), and every result is written as
+   * {fp32 value, ll_epoch}: an 8-byte store is atomic, so a word whose flag shows this call's epoch
+   * carries this call's value -- no fence, no counter, no round trip over NVLink. ll_input is this
+   * GPU's receive area, [ll_slots][batch][ll_slot_cols] words, one slot per GPU of the group (its
+   * own included: point `output` at it); the kernel's first CTAs wait (bounded, "peer_wait_ms") for
+   * each word and write ll_output (16-bit): [batch][ll_slots * ll_slot_cols], the slots' columns
+   * side by side (ll_reduce = 0, an N-split), or [batch][ll_slot_cols], the slots added in order
+   * and rounded once (ll_reduce = 1, a K-split). The epoch comes from the caller (ll_epoch: a
+   * different value, never 0, for every call that writes the same receive area; alternate between
+   * two areas so that a GPU that runs ahead cannot overwrite words its peers have not read yet) or
+   * lives on the device: with ll_epoch_counter -- two consecutive 32-bit words in this GPU's
+   * memory, zero before the first call -- a call's epoch is the counter plus one, the kernel adds
+   * one when the call is complete, and the receive areas of odd epochs (`output`, every
+   * peer_output and ll_input alike) lie ll_parity_words words behind those of even ones. Nothing
+   * about the exchange is then baked into the launch, so a call recorded into a CUDA graph can be
+   * replayed. Every GPU of the group must make the same calls in the same order. Excludes
+   * local_signal, reduce_slots and the SiLU-and-multiply epilogue. */
+  unsigned int ll_epoch;
+  unsigned int* ll_epoch_counter;
+  long long ll_parity_words;
+  const void* ll_input;
+  void* ll_output;
+  int ll_slots;
+  int ll_slot_cols;
+  int ll_reduce;
 } fk_w4a16_gemv_args;
 FK_W4A16_API int fk_w4a16_gemv_ex(const fk_w4a16_gemv_args* args);
 

@@ -512,6 +512,90 @@ def test_gemv_ex_fused_reduction_behind_the_exchange(n: int, k: int) -> None:
         capi.check(lib.fk_w4a16_gemv_ex(args))
 
 
+def _ll_words(values: torch.Tensor, epoch: int) -> torch.Tensor:
+    """fp32 values -> 8-byte words {value, epoch} as an int64 tensor."""
+    bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    return bits | (epoch << 32)
+
+
+@pytest.mark.parametrize(("n", "k"), [(128 * 6, 128 * 5), (128 * 100, 128 * 9)])  # cluster / stream kernel
+@pytest.mark.parametrize("reduce", [0, 1])
+def test_gemv_ex_flag_in_data_exchange(n: int, k: int, reduce: int) -> None:
+    """The ll_* exchange with one GPU playing rank 0 of two: its results go out as 8-byte words
+    {fp32 value, epoch} into slot 0 of its own receive area, slot 1 holds the words the other rank
+    would have stored, and the kernel's first CTAs assemble the final output -- the two slots'
+    columns side by side (an N-split) or their sum (a K-split). With the epoch kept on the device:
+    three calls in a row alternate between the two receive areas, and the calls are recorded into
+    a CUDA graph and replayed."""
+    lib = capi.load_library()
+    batch = 2
+    shape = LayerShape("t", n, k, batch=batch, dtype="bf16", zero_point=None)
+    problem = make_problem(shape, seed=1212)
+    q, alpha, beta, act = (problem[k_].cuda() for k_ in ("q_u8", "alpha", "beta", "activations"))
+    packets = capi_pack(capi, q, alpha, beta, 128)
+    y32 = torch.empty((batch, n), dtype=torch.float32, device="cuda")
+    _gemv_ex(lib, act, packets, y32, shape, 1, f32=1)
+    gen = torch.Generator().manual_seed(8)
+    other = torch.randn((batch, n), generator=gen).cuda()
+    want = (y32 + other).to(torch.bfloat16) if reduce else torch.cat([y32, other], dim=1).to(torch.bfloat16)
+
+    slot_words = batch * n
+    area_words = 2 * slot_words
+    control = torch.zeros(4, dtype=torch.int32, device="cuda")          # epoch counter, ticket
+    areas = torch.zeros((2, 2, batch, n), dtype=torch.int64, device="cuda")  # [parity][slot][m][n]
+    out = torch.full(want.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = WS.get(capi, batch, n, k, 128)
+
+    def call() -> None:
+        args = capi.GemvArgs()
+        args.activations, args.packets, args.output = act.data_ptr(), packets.data_ptr(), areas.data_ptr()
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.batch, args.n, args.k, args.group_size = batch, n, k, 128
+        args.packet_stride_bytes, args.dtype = 8704, 1
+        args.ll_epoch_counter = control.data_ptr()
+        args.ll_parity_words = area_words
+        args.ll_input, args.ll_output = areas.data_ptr(), out.data_ptr()
+        args.ll_slots, args.ll_slot_cols, args.ll_reduce = 2, n, reduce
+        args.stream = stream_ptr()
+        capi.check(lib.fk_w4a16_gemv_ex(args))
+
+    for epoch in (1, 2, 3):
+        areas[epoch & 1, 1] = _ll_words(other, epoch)  # what the other rank stores for this call
+        out.fill_(float("nan"))
+        call()
+        torch.cuda.synchronize()
+        assert control[0].item() == epoch and control[1].item() == 0
+        assert torch.equal(out, want), epoch
+        mine = areas[epoch & 1, 0]
+        assert torch.equal((mine >> 32).to(torch.int32), torch.full_like(mine, epoch, dtype=torch.int32))
+        assert torch.equal((mine & 0xFFFFFFFF).to(torch.int32).view(torch.float32), y32)
+    # recorded once, replayed twice: epochs 4/5 while recording is not run, then 4 and 5
+    areas[0, 1] = _ll_words(other, 4)
+    areas[1, 1] = _ll_words(other, 5)
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            call()
+    torch.cuda.current_stream().wait_stream(side)
+    for epoch in (4, 5):
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert control[0].item() == epoch
+        assert torch.equal(out, want), epoch
+    # a word that never arrives: bounded wait, status 2, the context stays usable
+    capi.check(lib.fk_w4a16_set_tuning(b"peer_wait_ms", 20))
+    try:
+        areas[0, 1] = 0
+        call()  # epoch 6 expects slot 1 of area 0
+        torch.cuda.synchronize()
+        assert capi.device_status() == 2
+    finally:
+        capi.check(lib.fk_w4a16_set_tuning(b"peer_wait_ms", 2000))
+
+
 def test_peer_wait_gives_up_and_reports_through_the_status_word() -> None:
     """Failure detection without a fault: a call whose counter can never reach its target (it is
     told to wait for one more group-wide delivery than will ever come) returns after the bounded
