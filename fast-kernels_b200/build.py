@@ -5,6 +5,7 @@
 
 Outputs land next to the Python package so that a snapshot of the tree carries them:
     src/fast_kernels/lib/libfk_w4a16.so      C-ABI library (CUDA kernels, sm_100a)
+    src/fast_kernels/lib/libfk_page_decode.so  C-ABI library of the paged-KV decode attention
     src/fast_kernels/_native*.so             pybind11 module with the reference's binding names
 """
 
@@ -71,6 +72,32 @@ def build_library(force: bool = False) -> Path:
     return target
 
 
+def build_page_decode_library(force: bool = False) -> Path:
+    """libfk_page_decode.so: the paged-KV decode attention kernels and the extern "C" entry points
+    of include/fk_page_decode.h. One translation unit per (head_dim, page_size), compiled in
+    parallel."""
+    kernel_dir = CSRC / "kernels" / "clustered_page_decode"
+    sources = sorted(kernel_dir.glob("*.cu"))
+    deps = (sources + sorted(kernel_dir.glob("*.cuh")) + sorted(kernel_dir.glob("*.h")) + sorted(kernel_dir.glob("*.inc"))
+            + [REPO / "include" / "fk_page_decode.h", CSRC / "kernels" / "decode_quant_linear" / "w4a16_common.cuh"])
+    target = LIB_DIR / "libfk_page_decode.so"
+    if not force and _newer(target, deps):
+        return target
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    cuda_lib = Path(_nvcc()).resolve().parent.parent / "lib64"
+    _run(
+        [
+            _nvcc(), *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+            "--threads", "0", "-Xptxas", "-v",
+            "-I", REPO / "include", "-I", kernel_dir,
+            "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+            "-Xlinker", f"-rpath,{cuda_lib}",
+            "-o", target, *sources,
+        ]
+    )
+    return target
+
+
 def build_python_module_without_cuda(out_dir: Path) -> Path:
     """A `_native` module built WITHOUT CUDA into `out_dir`: same names and keyword arguments,
     every op raises RuntimeError("fast-kernels was built without CUDA support"), and
@@ -93,6 +120,7 @@ def build_python_module_without_cuda(out_dir: Path) -> Path:
             "-o", target,
             CSRC / "bindings" / "python_module.cpp",
             CSRC / "ops" / "decode_quant_linear" / "arc_w4a16_nocuda.cpp",
+            CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode_nocuda.cpp",
         ]
     )
     return target
@@ -105,11 +133,14 @@ def build_python_module(force: bool = False) -> Path:
     sources = [
         CSRC / "bindings" / "python_module.cpp",
         CSRC / "ops" / "decode_quant_linear" / "arc_w4a16.cpp",
+        CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode.cpp",
     ]
-    deps = sources + [CSRC / "ops" / "decode_quant_linear" / "arc_w4a16.h", REPO / "include" / "fk_w4a16.h"]
+    deps = sources + [CSRC / "ops" / "decode_quant_linear" / "arc_w4a16.h", REPO / "include" / "fk_w4a16.h",
+                      CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode.h",
+                      REPO / "include" / "fk_page_decode.h"]
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
     target = PKG / f"_native{suffix}"
-    if not force and _newer(target, deps) and _newer(target, [LIB_DIR / "libfk_w4a16.so"]):
+    if not force and _newer(target, deps) and _newer(target, [LIB_DIR / "libfk_w4a16.so", LIB_DIR / "libfk_page_decode.so"]):
         return target
     cxx = shutil.which("g++") or "g++"
     version = subprocess.run([cxx, "-dumpfullversion"], capture_output=True, text=True).stdout.strip()
@@ -129,7 +160,7 @@ def build_python_module(force: bool = False) -> Path:
             "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
             "-I", CSRC, "-I", REPO / "include", "-I", cuda_root / "include",
             "-o", target, *sources,
-            f"-L{LIB_DIR}", "-lfk_w4a16", f"-L{cuda_root / 'lib64'}", "-lcudart",
+            f"-L{LIB_DIR}", "-lfk_w4a16", "-lfk_page_decode", f"-L{cuda_root / 'lib64'}", "-lcudart",
             "-Wl,-rpath,$ORIGIN/lib", f"-Wl,-rpath,{cuda_root / 'lib64'}",
         ]
     )
@@ -164,6 +195,7 @@ def build_oracle(force: bool = False) -> None:
 
 def build_all(force: bool = False, oracle: bool = False) -> None:
     build_library(force)
+    build_page_decode_library(force)
     if (CSRC / "bindings" / "python_module.cpp").exists():
         build_python_module(force)
     if oracle:

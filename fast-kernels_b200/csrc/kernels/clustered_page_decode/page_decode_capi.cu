@@ -1,0 +1,370 @@
+// extern "C" entry points of include/fk_page_decode.h: validation, launch plan, launch.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "fk_page_decode.h"
+#include "page_decode_launch.h"
+
+namespace fk_page_decode {
+
+__device__ int g_page_decode_status = 0;
+
+namespace {
+
+thread_local std::string t_last_error;
+
+int fail(int code, const std::string& message) {
+  t_last_error = message;
+  return code;
+}
+
+int fail_cuda(const char* what, cudaError_t err) {
+  return fail(FK_PAGE_DECODE_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+constexpr int kMaxDevices = 64;
+constexpr size_t kTicketBytes = 64 * 1024;      // fixed header: one counter per task
+constexpr int kMaxTicketTasks = kTicketBytes / 4;
+constexpr int kWorkspaceBlocks = 1024;          // partial results the documented size has room for
+constexpr int kSharedBudget = 220 * 1024;       // of the 227 KB a block may use
+
+struct DeviceInfo {
+  bool known = false;
+  int sm_count = 0;
+  int* status = nullptr;
+};
+
+// Filled on first use per device; a failed query is retried by the next call.
+int device_info(DeviceInfo* out) {
+  static std::mutex mutex;
+  static DeviceInfo table[kMaxDevices];
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) {
+    return fail_cuda("cudaGetDevice", err);
+  }
+  if (device < 0 || device >= kMaxDevices) {
+    return fail(FK_PAGE_DECODE_ERR_CUDA, "device ordinal out of range");
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  DeviceInfo& slot = table[device];
+  if (!slot.known) {
+    int sms = 0;
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (err != cudaSuccess) {
+      return fail_cuda("cudaDeviceGetAttribute", err);
+    }
+    void* status = nullptr;
+    err = cudaGetSymbolAddress(&status, g_page_decode_status);
+    if (err != cudaSuccess) {
+      return fail_cuda("cudaGetSymbolAddress", err);
+    }
+    slot.sm_count = sms;
+    slot.status = static_cast<int*>(status);
+    slot.known = true;
+  }
+  *out = slot;
+  return FK_PAGE_DECODE_OK;
+}
+
+std::atomic<int> g_warps_override{0};
+std::atomic<int> g_stages_override{0};
+
+struct Plan {
+  Variant variant;
+  int head_tiles = 0;
+  int tasks = 0;
+  int splits = 1;
+  int warps = 0;
+  int stages = 0;
+  int shared_bytes = 0;
+  size_t workspace_need = 0;
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int smallest_tile_for(int heads) { return heads <= 1 ? 1 : heads <= 2 ? 2 : heads <= 4 ? 4 : 8; }
+
+size_t partial_floats(int group_tile, int head_dim) { return static_cast<size_t>(group_tile) * (head_dim + 2); }
+
+// Mirrors the checks of the reference's launcher (clustered_page_decode.cu:1095-1131), then plans.
+int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = true) {
+  if (a.batch <= 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "page decode received empty inputs");
+  }
+  if (a.num_runs < 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "num_runs must be non-negative");
+  }
+  if (a.head_dim != 64 && a.head_dim != 128) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "page decode only supports head_dim 64 or 128");
+  }
+  if (a.page_size != 16 && a.page_size != 32) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "page decode only supports page_size 16 or 32");
+  }
+  if (a.num_q_heads % a.num_kv_heads != 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "num_q_heads must be divisible by num_kv_heads");
+  }
+  if (a.group_tile != 0 && a.group_tile != 1 && a.group_tile != 2 && a.group_tile != 4 && a.group_tile != 8) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "group_tile must be one of {1, 2, 4, 8} (or 0)");
+  }
+  if (a.kv_format != FK_PAGE_DECODE_KV_BF16 && a.kv_format != FK_PAGE_DECODE_KV_FP8_E4M3 &&
+      a.kv_format != FK_PAGE_DECODE_KV_INT8) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "unsupported kv_format");
+  }
+  if (a.splits < 0 || a.splits > kMaxSplits) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "splits must be in [0, 64]");
+  }
+  if (a.max_pages_hint < 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "max_pages_hint must be non-negative");
+  }
+  if (a.query == nullptr || a.key_pages == nullptr || a.value_pages == nullptr || a.output == nullptr ||
+      a.request_run_offsets == nullptr || a.seq_lens == nullptr) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "query, pages, output, request_run_offsets and seq_lens must not be NULL");
+  }
+  if (a.num_runs > 0 && (a.run_base_pages == nullptr || a.run_page_counts == nullptr ||
+                         a.run_logical_starts == nullptr || a.run_last_page_lens == nullptr)) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "the run arrays must not be NULL when num_runs > 0");
+  }
+  if (a.kv_format != FK_PAGE_DECODE_KV_BF16 && (a.key_scales == nullptr || a.value_scales == nullptr)) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "quantised pages need key_scales and value_scales");
+  }
+  // bulk copies start at page boundaries: 16-byte aligned as soon as the bases are
+  if (!aligned16(a.query) || !aligned16(a.key_pages) || !aligned16(a.value_pages) || !aligned16(a.output) ||
+      (a.kv_format != FK_PAGE_DECODE_KV_BF16 && !aligned16(a.value_scales))) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "query, pages, value_scales and output must be 16-byte aligned");
+  }
+  if (!std::isfinite(a.softmax_scale) || !(a.rope_theta > 0.0f) || !std::isfinite(a.rope_theta)) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "softmax_scale must be finite and rope_theta positive");
+  }
+
+  DeviceInfo info;
+  if (const int code = device_info(&info); code != FK_PAGE_DECODE_OK) {
+    return code;
+  }
+  const int group = a.num_q_heads / a.num_kv_heads;
+  const int wanted = a.group_tile == 0 ? 8 : a.group_tile;
+  Plan out;
+  out.variant = Variant{a.head_dim, a.page_size, a.kv_format, a.keys_are_rotated != 0,
+                        smallest_tile_for(std::min(wanted, group))};
+  const int gt = out.variant.group_tile;
+  out.head_tiles = (group + gt - 1) / gt;
+  const long long tasks = static_cast<long long>(a.batch) * a.num_kv_heads * out.head_tiles;
+  if (tasks > (1LL << 30)) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "too many (request, kv head, head tile) tasks");
+  }
+  out.tasks = static_cast<int>(tasks);
+
+  // ring: as many warps as fit with `stages` buffers each
+  out.stages = g_stages_override.load() > 0 ? g_stages_override.load() : 2;
+  int warps = g_warps_override.load() > 0 ? std::min(g_warps_override.load(), kMaxWarps) : kMaxWarps;
+  while (warps > 1 && variant_shared_bytes(out.variant, warps, out.stages) > kSharedBudget) {
+    --warps;
+  }
+  out.warps = warps;
+  out.shared_bytes = variant_shared_bytes(out.variant, warps, out.stages);
+  if (out.shared_bytes < 0 || out.shared_bytes > 227 * 1024) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "launch configuration does not fit shared memory");
+  }
+
+  int splits = a.splits;
+  if (splits == 0) {
+    splits = std::max(1, info.sm_count / out.tasks);
+    if (a.max_pages_hint > 0) {
+      splits = std::min(splits, std::max(1, a.max_pages_hint / warps));
+    }
+    splits = std::min(splits, kMaxSplits);
+  }
+  if (out.tasks > kMaxTicketTasks) {
+    if (a.splits > 1) {
+      return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "splits > 1 supports at most 16384 tasks");
+    }
+    splits = 1;
+  }
+  out.splits = splits;
+  out.workspace_need =
+      splits == 1 ? 0 : kTicketBytes + static_cast<size_t>(out.tasks) * splits * partial_floats(gt, a.head_dim) * 4;
+  if (out.workspace_need > 0 && check_workspace) {
+    if (a.workspace == nullptr || a.workspace_bytes < out.workspace_need) {
+      char text[160];
+      std::snprintf(text, sizeof text, "workspace too small: %zu bytes needed for %d tasks x %d splits, %zu given",
+                    out.workspace_need, out.tasks, splits, a.workspace == nullptr ? size_t{0} : a.workspace_bytes);
+      return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, text);
+    }
+    if (!aligned16(a.workspace)) {
+      return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
+    }
+  }
+  *plan = out;
+  return FK_PAGE_DECODE_OK;
+}
+
+}  // namespace
+
+int variant_shared_bytes(const Variant& v, int warps, int stages) {
+  if (v.head_dim == 64 && v.page_size == 16) {
+    return shared_bytes_d64_p16(v.kv_format, v.keys_are_rotated, v.group_tile, warps, stages);
+  }
+  if (v.head_dim == 64 && v.page_size == 32) {
+    return shared_bytes_d64_p32(v.kv_format, v.keys_are_rotated, v.group_tile, warps, stages);
+  }
+  if (v.head_dim == 128 && v.page_size == 16) {
+    return shared_bytes_d128_p16(v.kv_format, v.keys_are_rotated, v.group_tile, warps, stages);
+  }
+  if (v.head_dim == 128 && v.page_size == 32) {
+    return shared_bytes_d128_p32(v.kv_format, v.keys_are_rotated, v.group_tile, warps, stages);
+  }
+  return -1;
+}
+
+int variant_stage_bytes(const Variant& v) {
+  if (v.head_dim == 64 && v.page_size == 16) return stage_bytes_d64_p16(v.kv_format);
+  if (v.head_dim == 64 && v.page_size == 32) return stage_bytes_d64_p32(v.kv_format);
+  if (v.head_dim == 128 && v.page_size == 16) return stage_bytes_d128_p16(v.kv_format);
+  if (v.head_dim == 128 && v.page_size == 32) return stage_bytes_d128_p32(v.kv_format);
+  return -1;
+}
+
+cudaError_t launch_variant(const Variant& v, const DecodeParams& params, int blocks, int warps, int stages,
+                           cudaStream_t stream) {
+  if (v.head_dim == 64 && v.page_size == 16) {
+    return launch_d64_p16(v.kv_format, v.keys_are_rotated, v.group_tile, params, blocks, warps, stages, stream);
+  }
+  if (v.head_dim == 64 && v.page_size == 32) {
+    return launch_d64_p32(v.kv_format, v.keys_are_rotated, v.group_tile, params, blocks, warps, stages, stream);
+  }
+  if (v.head_dim == 128 && v.page_size == 16) {
+    return launch_d128_p16(v.kv_format, v.keys_are_rotated, v.group_tile, params, blocks, warps, stages, stream);
+  }
+  if (v.head_dim == 128 && v.page_size == 32) {
+    return launch_d128_p32(v.kv_format, v.keys_are_rotated, v.group_tile, params, blocks, warps, stages, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fk_page_decode
+
+using namespace fk_page_decode;
+
+extern "C" {
+
+FK_PAGE_DECODE_API const char* fk_page_decode_last_error(void) { return t_last_error.c_str(); }
+
+FK_PAGE_DECODE_API size_t fk_page_decode_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim) {
+  if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || (head_dim != 64 && head_dim != 128)) {
+    fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "workspace_bytes: batch and head counts must be positive, head_dim 64 or 128");
+    return 0;
+  }
+  // the fixed ticket header plus kWorkspaceBlocks partial results of the widest head tile: more
+  // than any automatic plan uses (at most one block per SM shares a task with others)
+  return kTicketBytes + static_cast<size_t>(kWorkspaceBlocks) * partial_floats(8, head_dim) * 4;
+}
+
+FK_PAGE_DECODE_API int fk_page_decode_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (workspace == nullptr || workspace_bytes < kTicketBytes) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "workspace_init: workspace is NULL or smaller than its header");
+  }
+  const cudaError_t err = cudaMemsetAsync(workspace, 0, kTicketBytes, static_cast<cudaStream_t>(stream));
+  return err == cudaSuccess ? FK_PAGE_DECODE_OK : fail_cuda("cudaMemsetAsync", err);
+}
+
+FK_PAGE_DECODE_API int fk_page_decode_forward(const fk_page_decode_args* args) {
+  if (args == nullptr) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "args must not be NULL");
+  }
+  const fk_page_decode_args& a = *args;
+  Plan plan;
+  if (const int code = make_plan(a, &plan); code != FK_PAGE_DECODE_OK) {
+    return code;
+  }
+  DeviceInfo info;
+  if (const int code = device_info(&info); code != FK_PAGE_DECODE_OK) {
+    return code;
+  }
+  DecodeParams params{};
+  params.query = static_cast<const uint16_t*>(a.query);
+  params.key_pages = static_cast<const uint8_t*>(a.key_pages);
+  params.value_pages = static_cast<const uint8_t*>(a.value_pages);
+  params.key_scales = a.key_scales;
+  params.value_scales = a.value_scales;
+  params.run_base_pages = a.run_base_pages;
+  params.run_page_counts = a.run_page_counts;
+  params.run_logical_starts = a.run_logical_starts;
+  params.run_last_page_lens = a.run_last_page_lens;
+  params.request_run_offsets = a.request_run_offsets;
+  params.seq_lens = a.seq_lens;
+  params.output = static_cast<uint16_t*>(a.output);
+  params.tickets = static_cast<unsigned*>(a.workspace);
+  params.partials = a.workspace == nullptr
+                        ? nullptr
+                        : reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + kTicketBytes);
+  params.status = info.status;
+  params.num_q_heads = a.num_q_heads;
+  params.num_kv_heads = a.num_kv_heads;
+  params.group_size = a.num_q_heads / a.num_kv_heads;
+  params.head_tiles = plan.head_tiles;
+  params.splits = plan.splits;
+  params.stages = plan.stages;
+  params.scale_log2e = static_cast<float>(static_cast<double>(a.softmax_scale) * 1.4426950408889634);
+  for (int i = 0; i < a.head_dim / 2; ++i) {
+    params.inv_freq[i] = static_cast<float>(
+        std::pow(static_cast<double>(a.rope_theta), -2.0 * static_cast<double>(i) / static_cast<double>(a.head_dim)));
+  }
+  const long long blocks = static_cast<long long>(plan.tasks) * plan.splits;
+  if (blocks > 0x7fffffffLL) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "grid too large");
+  }
+  const cudaError_t err = launch_variant(plan.variant, params, static_cast<int>(blocks), plan.warps, plan.stages,
+                                         static_cast<cudaStream_t>(a.stream));
+  return err == cudaSuccess ? FK_PAGE_DECODE_OK : fail_cuda("page decode launch", err);
+}
+
+FK_PAGE_DECODE_API int fk_page_decode_device_status(int* status) {
+  if (status == nullptr) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "status must not be NULL");
+  }
+  DeviceInfo info;
+  if (const int code = device_info(&info); code != FK_PAGE_DECODE_OK) {
+    return code;
+  }
+  int value = 0;
+  cudaError_t err = cudaMemcpy(&value, info.status, sizeof value, cudaMemcpyDeviceToHost);
+  if (err == cudaSuccess && value != 0) {
+    err = cudaMemset(info.status, 0, sizeof value);
+  }
+  if (err != cudaSuccess) {
+    return fail_cuda("device status", err);
+  }
+  *status = value;
+  return FK_PAGE_DECODE_OK;
+}
+
+FK_PAGE_DECODE_API int fk_page_decode_describe_plan(const fk_page_decode_args* args, char* text, size_t capacity) {
+  if (args == nullptr || text == nullptr || capacity == 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "describe_plan: args and text must not be NULL");
+  }
+  Plan plan;
+  if (const int code = make_plan(*args, &plan, false); code != FK_PAGE_DECODE_OK) {
+    return code;
+  }
+  std::snprintf(text, capacity, "kernel=page_decode blocks=%lld tasks=%d splits=%d group_tile=%d warps=%d stages=%d shared=%d",
+                static_cast<long long>(plan.tasks) * plan.splits, plan.tasks, plan.splits, plan.variant.group_tile,
+                plan.warps, plan.stages, plan.shared_bytes);
+  return FK_PAGE_DECODE_OK;
+}
+
+FK_PAGE_DECODE_API int fk_page_decode_set_launch_config(int warps_per_block, int stages) {
+  if (warps_per_block < 0 || warps_per_block > kMaxWarps || stages < 0 || stages > 8) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "warps_per_block must be in [0, 8], stages in [0, 8]");
+  }
+  g_warps_override.store(warps_per_block);
+  g_stages_override.store(stages);
+  return FK_PAGE_DECODE_OK;
+}
+
+}  // extern "C"

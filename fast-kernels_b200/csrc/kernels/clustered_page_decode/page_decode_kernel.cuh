@@ -1,0 +1,688 @@
+// Paged-KV decode attention for sm_100a: one query token per request, grouped-query heads, rotary
+// embedding applied in the kernel, pages of bf16 / e4m3 / int8 keys and values.
+//
+// What it computes is what the reference's two kernels compute
+// (csrc/kernels/clustered_page_decode/clustered_page_decode.cu:111-328 and :330-669): for request b,
+// query head h of kv head j, over the tokens of the request's runs of pages,
+//     logit_t = scale * < R(pos_q) q , R(pos_t) k_t >,   out = sum_t softmax(logit)_t * v_t
+// with pos_q = seq_len - 1, pos_t = logical_page * page_size + token, R the Llama pair rotation
+// (:96-108), quantised elements multiplied by their scale (:74-94: keys one scale per page, kv
+// head and 64-dim block; values one per token and 64-dim block).
+//
+// How it is laid out here:
+//  * A thread block serves one (request, kv head, tile of GT query heads, split s of S): the
+//    flattened list of the request's pages is dealt round-robin over the S blocks, a block's pages
+//    round-robin over its warps. The S partial results (running maximum, denominator, weighted
+//    value sum) meet in global scratch; the block that takes the last ticket adds them in split
+//    order and writes the output, so results do not depend on timing.
+//  * Every warp streams its own pages: a page's keys and values for one kv head are two contiguous
+//    blocks of page_size x head_dim elements (plus the values' scales), fetched by bulk
+//    asynchronous copies into a ring of `stages` buffers per warp, completion on an mbarrier. No
+//    block-wide barrier while pages stream.
+//  * Lane l owns head dimensions [l*EPL, (l+1)*EPL) (EPL = head_dim / 32) of every key, value,
+//    query and accumulator. The rotated, scaled query of the tile's heads sits in registers. Only
+//    the token part of a key's rotation is applied to the key (a table e^{i t theta}, t <
+//    page_size, built once per block); the page part goes to the query:
+//    <R(a) q, R(P + t) k> = <R(a - P) q, R(t) k>. Key scales and the softmax scale ride on the
+//    query as well, value scales on the probabilities.
+//  * Partial dot products of TB tokens x GT heads (32 values per lane) are summed across lanes by
+//    a butterfly that halves the values a lane keeps at every step: one shuffle per value instead
+//    of five, and lane l ends up with the logit of (token l / GT, head l % GT).
+//  * Every wait on a copy is bounded: on a time-out the block sets the status word, gives up on
+//    its pages and still takes part in the barriers and the ticket.
+#pragma once
+
+#include <cuda_fp8.h>
+
+#include "../decode_quant_linear/w4a16_common.cuh"
+
+namespace fk_page_decode {
+
+using fk_w4a16::lds128;
+using fk_w4a16::lds64;
+using fk_w4a16::mbar_expect_tx;
+using fk_w4a16::mbar_init;
+using fk_w4a16::mbar_init_fence;
+using fk_w4a16::mbar_wait_bounded;
+using fk_w4a16::proxy_fence_async;
+using fk_w4a16::smem_addr;
+
+constexpr int kKvBf16 = 0;
+constexpr int kKvFp8 = 1;
+constexpr int kKvInt8 = 2;
+constexpr int kEntryCapacity = 1024;  // pages of one block that are listed in shared memory at a time
+constexpr int kMaxWarps = 8;
+constexpr int kMaxPairs = 64;
+constexpr int kMaxSplits = 64;
+constexpr int kStatusCopyWaitTimeout = 1;
+
+struct DecodeParams {
+  const uint16_t* query;
+  const uint8_t* key_pages;
+  const uint8_t* value_pages;
+  const float* key_scales;
+  const float* value_scales;
+  const int32_t* run_base_pages;
+  const int32_t* run_page_counts;
+  const int32_t* run_logical_starts;
+  const int32_t* run_last_page_lens;
+  const int32_t* request_run_offsets;
+  const int32_t* seq_lens;
+  uint16_t* output;
+  float* partials;    // [task * splits + s][GT][head_dim + 2]: weighted values, maximum, denominator
+  unsigned* tickets;  // [task], zero between calls
+  int* status;
+  int num_q_heads;
+  int num_kv_heads;
+  int group_size;
+  int head_tiles;
+  int splits;
+  int stages;
+  float scale_log2e;  // softmax scale times log2(e): the kernel works with exp2
+  float inv_freq[kMaxPairs];  // theta^(-2 i / head_dim), rounded once from double
+};
+
+__host__ __device__ constexpr int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+// Shared-memory layout, the same arithmetic on host (size) and device (offsets).
+template <int D, int PS, int KV, bool ROT, int GT>
+struct Layout {
+  static constexpr int kElemBytes = KV == kKvBf16 ? 2 : 1;
+  static constexpr bool kQuant = KV != kKvBf16;
+  static constexpr int kDimBlocks = D / 64;
+  static constexpr int kDbq = kQuant ? kDimBlocks : 1;  // copies of a probability (one per value scale)
+  static constexpr int kPageBytes = PS * D * kElemBytes;
+  static constexpr int kVScaleBytes = kQuant ? PS * kDimBlocks * 4 : 0;
+  static constexpr int kStageBytes = round_up(2 * kPageBytes + kVScaleBytes, 128);
+  static constexpr int kEpl = D / 32;
+
+  int bars, entries, kscales, inv_freq, rope, probs, alphas, ring, total;
+
+  __host__ __device__ Layout(int warps, int stages) {
+    int at = 0;
+    bars = at;
+    at += round_up(warps * stages * 8, 128);
+    entries = at;
+    at += kEntryCapacity * 8;
+    kscales = at;
+    at += kQuant ? kEntryCapacity * kDimBlocks * 4 : 0;
+    inv_freq = at;
+    at += kMaxPairs * 4;
+    rope = at;
+    at += ROT ? 0 : PS * 32 * (kEpl / 2) * 8;  // per token and lane: cos, sin of each owned pair
+    probs = at;
+    at += warps * PS * kDbq * GT * 4;
+    alphas = at;
+    at += round_up(warps * GT * 4, 128);
+    ring = at;
+    const int ring_bytes = warps * stages * kStageBytes;
+    const int merge_bytes = warps * GT * (D + 2) * 4;
+    at += ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
+    total = at;
+  }
+};
+
+__device__ __forceinline__ void bulk_copy_plain(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
+// EPL elements of one row of a page, starting at this lane's first dimension, as floats
+// (unscaled: the scale rides on the query or the probability).
+template <int KV, int EPL>
+__device__ __forceinline__ void load_elements(uint32_t addr, float (&x)[EPL]) {
+  if constexpr (KV == kKvBf16) {
+    uint32_t w[EPL / 2];
+    if constexpr (EPL == 4) {
+      const uint2 v = lds64(addr);
+      w[0] = v.x;
+      w[1] = v.y;
+    } else {
+      w[0] = lds32(addr);
+    }
+#pragma unroll
+    for (int i = 0; i < EPL / 2; ++i) {
+      x[2 * i] = __uint_as_float(w[i] << 16);
+      x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+    const uint32_t w = EPL == 4 ? lds32(addr) : lds16(addr);
+    if constexpr (KV == kKvInt8) {
+      // byte + 128 dropped into the mantissa of 2^23: exact, no integer-to-float conversion
+      const uint32_t u = w ^ 0x80808080u;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        x[i] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540u + i)) - 8388736.0f;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) {
+        const __half2_raw h2 =
+            __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w >> (16 * i)) & 0xffffu), __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+      }
+    }
+  }
+}
+
+// Sum over lanes of NV values per lane; lane l is left with the total of value (l % NV) in v[0].
+template <int NV>
+__device__ __forceinline__ void butterfly_sum(float (&v)[NV], int lane) {
+#pragma unroll
+  for (int o = NV / 2; o >= 1; o >>= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float keep = upper ? v[i + o] : v[i];
+      const float give = upper ? v[i] : v[i + o];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+    }
+  }
+#pragma unroll
+  for (int o = NV; o < 32; o <<= 1) {
+    v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+  }
+}
+
+__device__ __forceinline__ float exp2_or_zero(float x) {
+  // exp2f(-inf) is 0 already; the guard is for (-inf) - (-inf), which callers avoid by passing a
+  // finite reference point
+  return exp2f(x);
+}
+
+template <int D, int PS, int KV, bool ROT, int GT>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __grid_constant__ DecodeParams p) {
+  using L = Layout<D, PS, KV, ROT, GT>;
+  constexpr int EPL = L::kEpl;
+  constexpr int EB = L::kElemBytes;
+  constexpr bool QUANT = L::kQuant;
+  constexpr int DB = L::kDimBlocks;
+  constexpr int DBQ = L::kDbq;
+  constexpr int TB = (32 / GT) < PS ? (32 / GT) : PS;  // tokens per butterfly round
+  constexpr int NV = TB * GT;                         // values per lane per round
+  constexpr int NR = PS / TB;                         // rounds per page
+  constexpr int CAP = kEntryCapacity;
+  static_assert(NV <= 32 && (NV & (NV - 1)) == 0);
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int scan_totals[kMaxWarps];
+  __shared__ int last_flag;
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int warps = blockDim.x >> 5;
+  const int threads = blockDim.x;
+  const int stages = p.stages;
+  const L layout(warps, stages);
+
+  const int S = p.splits;
+  const int task = blockIdx.x / S;
+  const int split = blockIdx.x - task * S;
+  const int tasks_per_request = p.num_kv_heads * p.head_tiles;
+  const int request = task / tasks_per_request;
+  const int within = task - request * tasks_per_request;
+  const int kv_head = within / p.head_tiles;
+  const int tile = within - kv_head * p.head_tiles;
+  const int tile_base = tile * GT;
+  const int tile_heads = min(GT, p.group_size - tile_base);
+  const int first_q_head = kv_head * p.group_size + tile_base;
+  const size_t out_base = (static_cast<size_t>(request) * p.num_q_heads + first_q_head) * D;
+
+  const int query_position = p.seq_lens[request] - 1;
+  const int run_begin = p.request_run_offsets[request];
+  const int run_end = p.request_run_offsets[request + 1];
+  if (query_position < 0 || run_begin >= run_end) {
+    if (split == 0) {
+      for (int idx = tid; idx < tile_heads * D; idx += threads) {
+        p.output[out_base + idx] = 0;
+      }
+    }
+    return;  // every block of the task takes this branch: nobody waits for a ticket
+  }
+
+  const uint32_t bars = smem_addr(smem + layout.bars);
+  int2* entries = reinterpret_cast<int2*>(smem + layout.entries);
+  float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
+  float* inv_freq_s = reinterpret_cast<float*>(smem + layout.inv_freq);
+  float* rope = reinterpret_cast<float*>(smem + layout.rope);
+  float* probs = reinterpret_cast<float*>(smem + layout.probs) + warp * (PS * DBQ * GT);
+  float* alphas = reinterpret_cast<float*>(smem + layout.alphas) + warp * GT;
+  const uint32_t ring = smem_addr(smem + layout.ring) + warp * stages * L::kStageBytes;
+  const uint32_t my_bars = bars + warp * stages * 8;
+
+  if (tid < warps * stages) {
+    mbar_init(bars + tid * 8, 1);
+  }
+  if (tid < D / 2) {
+    inv_freq_s[tid] = p.inv_freq[tid];
+  }
+  mbar_init_fence();
+
+  // This lane's part of the tile's queries (bf16 -> fp32; heads past the group are zero).
+  float q_in[GT][EPL];
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      q_in[h][e] = 0.0f;
+    }
+    if (h < tile_heads) {
+      const uint16_t* src = p.query + out_base + static_cast<size_t>(h) * D + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; e += 2) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + e);
+        q_in[h][e] = __uint_as_float(w << 16);
+        q_in[h][e + 1] = __uint_as_float(w & 0xffff0000u);
+      }
+    }
+  }
+
+  float acc[GT][EPL];
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      acc[h][e] = 0.0f;
+    }
+  }
+  // Softmax state of head (lane % GT): the running maximum is the same on all lanes of a head,
+  // the denominator is this lane's share (summed over lanes at the end).
+  float m_run = -INFINITY;
+  float l_run = 0.0f;
+  const int my_head = lane % GT;
+  const int my_token = (lane % NV) / GT;  // within a butterfly round
+  const bool holds_value = lane < NV;
+  const int lane_db = (DB == 2) ? (lane >> 4) : 0;
+
+  const size_t page_head_stride = static_cast<size_t>(L::kPageBytes);
+  uint32_t iteration = 0;  // pages this warp has consumed: stage = iteration % stages
+  bool failed = false;
+
+  auto issue = [&](int entry_index, int stage) {
+    const int2 e = entries[entry_index];
+    const size_t page_head = static_cast<size_t>(e.x) * p.num_kv_heads + kv_head;
+    const uint32_t dst = ring + stage * L::kStageBytes;
+    const uint32_t bar = my_bars + stage * 8;
+    mbar_expect_tx(bar, 2 * L::kPageBytes + L::kVScaleBytes);
+    bulk_copy_plain(dst, p.key_pages + page_head * page_head_stride, L::kPageBytes, bar);
+    bulk_copy_plain(dst + L::kPageBytes, p.value_pages + page_head * page_head_stride, L::kPageBytes, bar);
+    if constexpr (QUANT) {
+      bulk_copy_plain(dst + 2 * L::kPageBytes, p.value_scales + page_head * (PS * DB), L::kVScaleBytes, bar);
+    }
+  };
+
+  float inv_freq_lane[EPL / 2];
+  float q_cos[EPL / 2], q_sin[EPL / 2];  // rotation of the query when the keys come rotated
+
+  int total_pages = 0;
+  for (int round = 0;; ++round) {
+    const int local_base = round * CAP;
+    // ---- list this block's pages: flattened page q of the request belongs to split q % S ----
+    int carry = 0;
+    for (int r0 = run_begin; r0 < run_end; r0 += threads) {
+      const int r = r0 + tid;
+      const bool valid = r < run_end;
+      const int count = valid ? max(p.run_page_counts[r], 0) : 0;
+      const int base = valid ? p.run_base_pages[r] : 0;
+      const int logical_start = valid ? p.run_logical_starts[r] : 0;
+      const int last_len = valid ? min(max(p.run_last_page_lens[r], 0), PS) : 0;
+      int inclusive = count;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, inclusive, o);
+        if (lane >= o) {
+          inclusive += up;
+        }
+      }
+      if (lane == 31) {
+        scan_totals[warp] = inclusive;
+      }
+      __syncthreads();
+      int before = 0, chunk_total = 0;
+      for (int w = 0; w < warps; ++w) {
+        const int v = scan_totals[w];
+        before += w < warp ? v : 0;
+        chunk_total += v;
+      }
+      const int first = carry + before + inclusive - count;
+      if (count > 0) {
+        int q = first + ((split - first % S) + S) % S;
+        for (; q < first + count; q += S) {
+          const int i = (q - split) / S - local_base;
+          if (i >= CAP) {
+            break;
+          }
+          if (i >= 0) {
+            const int off = q - first;
+            entries[i] = make_int2(base + off, ((logical_start + off) << 6) | (off == count - 1 ? last_len : PS));
+          }
+        }
+      }
+      carry += chunk_total;
+      __syncthreads();
+    }
+    total_pages = carry;
+    const int mine = total_pages > split ? (total_pages - split + S - 1) / S : 0;
+    const int in_round = max(0, min(CAP, mine - local_base));
+
+    // ---- first copies of the round, then the per-block tables while they fly ----
+    if (lane == 0 && !failed) {
+      for (int k = 0; k < stages; ++k) {
+        const int entry_index = warp + k * warps;
+        if (entry_index < in_round) {
+          issue(entry_index, (iteration + k) % stages);
+        }
+      }
+    }
+    if (round == 0) {
+      if constexpr (!ROT) {
+        // rope[(t * 32 + lane) * EPL + 2 i + {0, 1}] = cos, sin of t * theta_pair, pair = lane * EPL/2 + i
+        for (int idx = tid; idx < PS * (D / 2); idx += threads) {
+          const int t = idx / (D / 2);
+          const int pair = idx - t * (D / 2);
+          float sn, cs;
+          sincosf(static_cast<float>(t) * inv_freq_s[pair], &sn, &cs);
+          *reinterpret_cast<float2*>(&rope[(t * (D / 2) + pair) * 2]) = make_float2(cs, sn);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) {
+        inv_freq_lane[i] = inv_freq_s[lane * (EPL / 2) + i];
+        if constexpr (ROT) {
+          sincosf(static_cast<float>(query_position) * inv_freq_lane[i], &q_sin[i], &q_cos[i]);
+        }
+      }
+    }
+    if constexpr (QUANT) {
+      for (int idx = tid; idx < in_round * DB; idx += threads) {
+        const int i = idx / DB;
+        const int b = idx - i * DB;
+        const size_t page_head = static_cast<size_t>(entries[i].x) * p.num_kv_heads + kv_head;
+        kscales[idx] = p.key_scales[page_head * DB + b];
+      }
+    }
+    __syncthreads();
+
+    // ---- this warp's pages ----
+    for (int i = warp; i < in_round && !failed; i += warps, ++iteration) {
+      const int stage = iteration % stages;
+      if (!mbar_wait_bounded(my_bars + stage * 8, (iteration / stages) & 1)) {
+        failed = true;
+        if (lane == 0) {
+          atomicExch(p.status, kStatusCopyWaitTimeout);
+        }
+        break;
+      }
+      const int2 entry = entries[i];
+      const int logical_page = entry.y >> 6;
+      const int tokens = entry.y & 63;
+      const uint32_t k_stage = ring + stage * L::kStageBytes;
+      const uint32_t v_stage = k_stage + L::kPageBytes;
+
+      // query of this page: rotation by (a - P), key scale, softmax scale
+      float q_rot[GT][EPL];
+#pragma unroll
+      for (int pi = 0; pi < EPL / 2; ++pi) {
+        float cs, sn;
+        if constexpr (ROT) {
+          cs = q_cos[pi];
+          sn = q_sin[pi];
+        } else {
+          const int delta = query_position - logical_page * PS;
+          sincosf(static_cast<float>(delta) * inv_freq_lane[pi], &sn, &cs);
+        }
+        float factor = p.scale_log2e;
+        if constexpr (QUANT) {
+          factor *= kscales[i * DB + lane_db];
+        }
+        cs *= factor;
+        sn *= factor;
+#pragma unroll
+        for (int h = 0; h < GT; ++h) {
+          q_rot[h][2 * pi] = q_in[h][2 * pi] * cs - q_in[h][2 * pi + 1] * sn;
+          q_rot[h][2 * pi + 1] = q_in[h][2 * pi] * sn + q_in[h][2 * pi + 1] * cs;
+        }
+      }
+
+      // ---- logits: TB tokens x GT heads per butterfly round ----
+      float logit[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        logit[r] = -INFINITY;
+        if (r * TB < tokens) {
+          float vals[NV];
+#pragma unroll
+          for (int tl = 0; tl < TB; ++tl) {
+            const int t = r * TB + tl;
+            float kk[EPL];
+            load_elements<KV, EPL>(k_stage + t * (D * EB) + lane * (EPL * EB), kk);
+            if constexpr (!ROT) {
+              const float* cs_sn = &rope[(t * 32 + lane) * EPL];
+#pragma unroll
+              for (int pi = 0; pi < EPL / 2; ++pi) {
+                const float2 c = *reinterpret_cast<const float2*>(cs_sn + 2 * pi);
+                const float ke = kk[2 * pi], ko = kk[2 * pi + 1];
+                kk[2 * pi] = ke * c.x - ko * c.y;
+                kk[2 * pi + 1] = ke * c.y + ko * c.x;
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < GT; ++h) {
+              float sum = q_rot[h][0] * kk[0];
+#pragma unroll
+              for (int e = 1; e < EPL; ++e) {
+                sum = fmaf(q_rot[h][e], kk[e], sum);
+              }
+              vals[tl * GT + h] = sum;
+            }
+          }
+          butterfly_sum<NV>(vals, lane);
+          const int t = r * TB + my_token;
+          logit[r] = t < tokens ? vals[0] : -INFINITY;
+        }
+      }
+
+      // ---- online softmax for head (lane % GT) ----
+      float page_max = logit[0];
+#pragma unroll
+      for (int r = 1; r < NR; ++r) {
+        page_max = fmaxf(page_max, logit[r]);
+      }
+#pragma unroll
+      for (int o = GT; o < 32; o <<= 1) {
+        page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, o));
+      }
+      const float m_new = fmaxf(m_run, page_max);
+      const float m_ref = m_new == -INFINITY ? 0.0f : m_new;
+      const float alpha = exp2_or_zero(m_run - m_ref);
+      float p_sum = 0.0f;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const float prob = exp2_or_zero(logit[r] - m_ref);
+        p_sum += prob;
+        if (holds_value && r * TB < tokens) {
+          const int t = r * TB + my_token;
+          if constexpr (QUANT) {
+            const float* vs = reinterpret_cast<const float*>(smem + layout.ring) +
+                              ((warp * stages + stage) * L::kStageBytes + 2 * L::kPageBytes) / 4 + t * DB;
+#pragma unroll
+            for (int b = 0; b < DB; ++b) {
+              probs[(t * DBQ + b) * GT + my_head] = prob * vs[b];
+            }
+          } else {
+            probs[t * GT + my_head] = prob;
+          }
+        }
+      }
+      l_run = l_run * alpha + (holds_value ? p_sum : 0.0f);
+      m_run = m_new;
+      if (lane < GT) {
+        alphas[lane] = alpha;
+      }
+      __syncwarp();
+
+      // ---- weighted values ----
+#pragma unroll
+      for (int h = 0; h < GT; ++h) {
+        const float a = alphas[h];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          acc[h][e] *= a;
+        }
+      }
+      const float* prob_row = probs + lane_db * (QUANT ? GT : 0);
+#pragma unroll 4
+      for (int t = 0; t < tokens; ++t) {
+        float vv[EPL];
+        load_elements<KV, EPL>(v_stage + t * (D * EB) + lane * (EPL * EB), vv);
+        float pr[GT];
+        if constexpr (GT >= 4) {
+#pragma unroll
+          for (int h = 0; h < GT; h += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(prob_row + t * (DBQ * GT) + h);
+            pr[h] = q4.x;
+            pr[h + 1] = q4.y;
+            pr[h + 2] = q4.z;
+            pr[h + 3] = q4.w;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < GT; ++h) {
+            pr[h] = prob_row[t * (DBQ * GT) + h];
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < GT; ++h) {
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) {
+            acc[h][e] = fmaf(pr[h], vv[e], acc[h][e]);
+          }
+        }
+      }
+
+      // ---- hand the buffer back ----
+      __syncwarp();
+      const int refill = i + stages * warps;
+      if (lane == 0 && refill < in_round) {
+        proxy_fence_async();
+        issue(refill, stage);
+      }
+    }
+    if (failed) {
+      // Copies that are still in flight write into this block's shared memory: give each a bounded
+      // chance to land before the memory is reused below.
+      for (int k = 1; k < stages; ++k) {
+        (void)mbar_wait_bounded(my_bars + ((iteration + k) % stages) * 8, ((iteration + k) / stages) & 1);
+      }
+    }
+    if (local_base + CAP >= mine) {
+      break;
+    }
+    __syncthreads();  // the list is rewritten for the next round
+  }
+
+  // ---- this warp's result -> shared memory, block result, then the splits ----
+#pragma unroll
+  for (int o = GT; o < 32; o <<= 1) {
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+  }
+  __syncthreads();  // every warp is done with its ring: the merge area overlays it
+  float* merge = reinterpret_cast<float*>(smem + layout.ring);
+  float* merge_m = merge;                     // [warps][GT]
+  float* merge_l = merge + warps * GT;        // [warps][GT]
+  float* merge_acc = merge + 2 * warps * GT;  // [warps][GT][D]
+  if (lane < GT) {
+    merge_m[warp * GT + lane] = m_run;
+    merge_l[warp * GT + lane] = l_run;
+  }
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      merge_acc[(warp * GT + h) * D + lane * EPL + e] = acc[h][e];
+    }
+  }
+  __syncthreads();
+
+  float* my_partial = p.partials + (static_cast<size_t>(task) * S + split) * (GT * (D + 2));
+  for (int idx = tid; idx < tile_heads * D; idx += threads) {
+    const int h = idx / D;
+    const int d = idx - h * D;
+    float m_all = -INFINITY;
+    for (int w = 0; w < warps; ++w) {
+      m_all = fmaxf(m_all, merge_m[w * GT + h]);
+    }
+    const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
+    float l_all = 0.0f, a_all = 0.0f;
+    for (int w = 0; w < warps; ++w) {
+      const float weight = exp2_or_zero(merge_m[w * GT + h] - m_ref);
+      l_all += weight * merge_l[w * GT + h];
+      a_all += weight * merge_acc[(w * GT + h) * D + d];
+    }
+    if (S == 1) {
+      const float y = l_all == 0.0f ? 0.0f : a_all / l_all;
+      p.output[out_base + idx] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
+    } else {
+      my_partial[h * (D + 2) + d] = a_all;
+      if (d == 0) {
+        my_partial[h * (D + 2) + D] = m_all;
+        my_partial[h * (D + 2) + D + 1] = l_all;
+      }
+    }
+  }
+  if (S == 1) {
+    return;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    last_flag = atomicAdd(&p.tickets[task], 1u) == static_cast<unsigned>(S - 1);
+  }
+  __syncthreads();
+  if (!last_flag) {
+    return;
+  }
+  __threadfence();
+  const float* task_partials = p.partials + static_cast<size_t>(task) * S * (GT * (D + 2));
+  for (int idx = tid; idx < tile_heads * D; idx += threads) {
+    const int h = idx / D;
+    const int d = idx - h * D;
+    const float* head_partial = task_partials + h * (D + 2);
+    float m_all = -INFINITY;
+    for (int s = 0; s < S; ++s) {
+      m_all = fmaxf(m_all, __ldcg(head_partial + static_cast<size_t>(s) * (GT * (D + 2)) + D));
+    }
+    const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
+    float l_all = 0.0f, a_all = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < S; ++s) {
+      const float* src = head_partial + static_cast<size_t>(s) * (GT * (D + 2));
+      const float weight = exp2_or_zero(__ldcg(src + D) - m_ref);
+      l_all += weight * __ldcg(src + D + 1);
+      a_all += weight * __ldcg(src + d);
+    }
+    const float y = l_all == 0.0f ? 0.0f : a_all / l_all;
+    p.output[out_base + idx] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
+  }
+  if (tid == 0) {
+    p.tickets[task] = 0;
+  }
+}
+
+}  // namespace fk_page_decode

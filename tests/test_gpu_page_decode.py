@@ -1,0 +1,350 @@
+"""Paged-KV decode attention on the GPU: the kernel through the C ABI and through the
+reference-compatible Python op, against the fp64 oracle, the fixtures the reference's own Python
+produced, and -- where it is built -- the reference's own CUDA kernels.
+
+Tolerances. Against the fp64 oracle ON THE SAME (quantised) DATA: |y - y64| <= 2e-3 + 8e-3 |y64|
+(one bf16 rounding of the output is 2^-9 relative; the arithmetic is fp32). Against the reference's
+PyTorch expectation, which for 8-bit pages is computed from the unquantised pages: the reference's
+own atol = 0.125, rtol = 0.03 (tests/gpu/test_clustered_page_decode.py:156 there)."""
+
+from __future__ import annotations
+
+import ctypes
+import importlib
+
+import numpy as np
+import pytest
+import torch
+from fast_kernels import page_decode_capi as pdc
+from oracle import page_decode_oracle as oracle
+from oracle import reference_page_decode_gpu as refgpu
+from page_decode_testlib import KV_IDS, DeviceCase, case_on_device, load_case, manifest
+
+pytestmark = pytest.mark.gpu
+ops = importlib.import_module("fast_kernels.ops.clustered_page_decode")
+CASES = manifest()
+IDS = [m["name"] for m in CASES]
+ATOL, RTOL = 2e-3, 8e-3
+
+
+def _assert_close_to_oracle(out: torch.Tensor, want: np.ndarray, what: str = "") -> None:
+    got = out.float().cpu().numpy().astype(np.float64)
+    assert np.isfinite(got).all(), what
+    worst, scaled = oracle.max_abs_and_scaled_error(got, want, ATOL, RTOL)
+    assert scaled <= 1.0, f"{what}: max abs error {worst:.3e}, {scaled:.2f} x tolerance"
+
+
+def _status_ok() -> None:
+    torch.cuda.synchronize()
+    assert pdc.device_status() == 0
+
+
+# ---- fixtures: the kernel on the reference's inputs --------------------------------------------------
+@pytest.mark.parametrize("splits", [1, 0, 3])
+@pytest.mark.parametrize("meta", CASES, ids=IDS)
+def test_kernel_on_the_reference_fixtures(meta, splits) -> None:
+    case = load_case(meta["name"])
+    dev = case_on_device(meta, case)
+    out = dev.forward(pdc, splits=splits)
+    _assert_close_to_oracle(out, dev.oracle(oracle), meta["name"])
+    expected = torch.from_numpy(case["expected"].view(np.int16).copy()).view(torch.bfloat16).float()
+    torch.testing.assert_close(out.float().cpu(), expected, atol=1.25e-1, rtol=3e-2)
+    _status_ok()
+
+
+# ---- seeded problems of every shape the kernel is instantiated for -----------------------------------
+def _random_problem(*, batch, q_heads, kv_heads, head_dim, page_size, lens, layout, rotated, seed, fragment=True):
+    generator = torch.Generator().manual_seed(seed)
+    max_len = max(max(lens), 1)
+    query = torch.randn((batch, q_heads, head_dim), generator=generator).to(torch.bfloat16)
+    keys = torch.randn((batch, kv_heads, max_len, head_dim), generator=generator).to(torch.bfloat16)
+    values = torch.randn((batch, kv_heads, max_len, head_dim), generator=generator).to(torch.bfloat16)
+    build = {"bf16_kv": ops.pack_paged_kv_bf16, "int8_kv": ops.quantize_paged_kv_int8,
+             "fp8_kv": ops.quantize_paged_kv_fp8}[layout]
+    cache = build(keys, values, torch.tensor(lens, dtype=torch.int32), page_size=page_size, fragment_pages=fragment,
+                  seed=seed, key_rope_theta=10000.0 if rotated else None)
+    plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads,
+                                          num_kv_heads=kv_heads, head_dim=head_dim, page_size=page_size,
+                                          kv_layout=layout, use_cache=False)
+    return query, cache, plan
+
+
+def _device_case(query, cache, plan) -> DeviceCase:
+    def raw(t):
+        if t.dtype == torch.bfloat16:
+            return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+        return t.contiguous().view(torch.uint8).numpy()
+
+    runs = {name: getattr(plan, f"{name}_cpu").numpy() for name in
+            ("run_base_pages", "run_page_counts", "run_logical_starts", "run_last_page_lens", "request_run_offsets")}
+    return DeviceCase(query=raw(query), key_pages=raw(cache.key_pages), value_pages=raw(cache.value_pages),
+                      key_scales=None if cache.key_scales is None else cache.key_scales.numpy(),
+                      value_scales=None if cache.value_scales is None else cache.value_scales.numpy(),
+                      runs=runs, seq_lens=cache.seq_lens.numpy(), kv_format=KV_IDS[cache.kv_layout],
+                      keys_are_rotated=cache.keys_are_rotated, page_size=cache.page_size)
+
+
+@pytest.mark.parametrize("rotated", [False, True])
+@pytest.mark.parametrize("layout", ["bf16_kv", "fp8_kv", "int8_kv"])
+@pytest.mark.parametrize(("head_dim", "page_size"), [(64, 16), (64, 32), (128, 16), (128, 32)])
+@pytest.mark.parametrize("group", [1, 2, 3, 4, 8, 12])
+def test_every_instantiation_against_the_oracle(group, head_dim, page_size, layout, rotated) -> None:
+    """Group sizes 3 and 12 leave a head tile partly empty; 12 also needs two tiles."""
+    kv_heads = 2
+    lens = [5 * page_size + 3, 1, 2 * page_size]  # ragged, a single token, an exact multiple
+    query, cache, plan = _random_problem(batch=3, q_heads=group * kv_heads, kv_heads=kv_heads, head_dim=head_dim,
+                                         page_size=page_size, lens=lens, layout=layout, rotated=rotated,
+                                         seed=group * 1000 + head_dim + page_size)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    for splits in (1, 2):
+        _assert_close_to_oracle(dev.forward(pdc, splits=splits), want, f"splits={splits}")
+    _status_ok()
+
+
+@pytest.mark.parametrize(("name", "shape"), [
+    # the shapes of the reference's benchmark suite (benchmarks/suites/clustered_page_decode.toml there)
+    ("gqa4_short_page16", dict(batch=4, page_size=16, max_len=256, q_heads=32, kv_heads=8, head_dim=128)),
+    ("gqa4_long_page16", dict(batch=4, page_size=16, max_len=2048, q_heads=32, kv_heads=8, head_dim=128)),
+    ("mqa8_long_page32", dict(batch=2, page_size=32, max_len=4096, q_heads=32, kv_heads=4, head_dim=128)),
+    ("mqa32_long_page32", dict(batch=2, page_size=32, max_len=4096, q_heads=32, kv_heads=1, head_dim=128)),
+    ("gqa2_short_page32_h64", dict(batch=8, page_size=32, max_len=512, q_heads=16, kv_heads=8, head_dim=64)),
+])
+@pytest.mark.parametrize("layout", ["bf16_kv", "int8_kv", "fp8_kv"])
+def test_benchmark_suite_shapes_through_the_python_op(name, shape, layout) -> None:
+    generator = torch.Generator().manual_seed(len(name))
+    lens = torch.randint(max(shape["page_size"], shape["max_len"] - shape["page_size"] + 1), shape["max_len"] + 1,
+                         (shape["batch"],), generator=generator).tolist()
+    query, cache, plan = _random_problem(batch=shape["batch"], q_heads=shape["q_heads"], kv_heads=shape["kv_heads"],
+                                         head_dim=shape["head_dim"], page_size=shape["page_size"], lens=lens,
+                                         layout=layout, rotated=False, seed=7)
+    want = _device_case(query, cache, plan).oracle(oracle)
+    gpu_cache = _cache_to(cache, "cuda")
+    out = ops.clustered_page_decode(query.cuda(), gpu_cache, plan=plan)
+    _assert_close_to_oracle(out, want, name)
+    reference = ops.reference_clustered_page_decode(query.cuda(), gpu_cache)
+    torch.testing.assert_close(out, reference, atol=1.25e-1, rtol=3e-2)
+    _status_ok()
+
+
+def _cache_to(cache, device):
+    def move(t):
+        return None if t is None else t.to(device)
+
+    return ops.PagedKVCache(
+        key_pages=move(cache.key_pages), value_pages=move(cache.value_pages), page_table=cache.page_table,
+        seq_lens=cache.seq_lens, key_scales=move(cache.key_scales), value_scales=move(cache.value_scales),
+        reference_key_pages=move(cache.reference_key_pages), reference_value_pages=move(cache.reference_value_pages),
+        kv_layout=cache.kv_layout, page_size=cache.page_size, num_kv_heads=cache.num_kv_heads, head_dim=cache.head_dim,
+        keys_are_rotated=cache.keys_are_rotated, key_rope_theta=cache.key_rope_theta)
+
+
+# ---- the reference's own GPU tests, restated against this op -----------------------------------------
+def _reference_test_case(layout, force_impl, *, batch, num_q_heads, num_kv_heads, head_dim, max_seq_len, page_size,
+                         cluster_size, key_rope_theta=None):
+    """_assert_case of the reference (tests/gpu/test_clustered_page_decode.py:113-156 there)."""
+    torch.manual_seed(batch + num_q_heads + num_kv_heads + head_dim + max_seq_len + page_size)
+    query = torch.randn((batch, num_q_heads, head_dim), device="cuda").to(torch.bfloat16)
+    keys = torch.randn((batch, num_kv_heads, max_seq_len, head_dim), device="cuda").to(torch.bfloat16)
+    values = torch.randn((batch, num_kv_heads, max_seq_len, head_dim), device="cuda").to(torch.bfloat16)
+    seq_lens = torch.randint(max(page_size, max_seq_len - page_size + 1), max_seq_len + 1, (batch,), dtype=torch.int32)
+    build = {"bf16_kv": ops.pack_paged_kv_bf16, "int8_kv": ops.quantize_paged_kv_int8,
+             "fp8_kv": ops.quantize_paged_kv_fp8}[layout]
+    cache = build(keys, values, seq_lens, page_size=page_size, fragment_pages=True, seed=1, key_rope_theta=key_rope_theta)
+    plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=num_q_heads,
+                                          num_kv_heads=cache.num_kv_heads, head_dim=cache.head_dim,
+                                          page_size=cache.page_size, kv_layout=cache.kv_layout, cluster_size=cluster_size)
+    actual = ops.clustered_page_decode(query, cache, plan=plan, force_impl=force_impl)
+    expected = ops.reference_clustered_page_decode(query, cache)
+    torch.testing.assert_close(actual, expected, atol=1.25e-1, rtol=3e-2)
+    return query, cache
+
+
+SMALL_DIRECT = dict(batch=2, num_q_heads=16, num_kv_heads=4, head_dim=64, max_seq_len=128, page_size=16, cluster_size=1)
+SMALL_CLUSTERED = dict(batch=2, num_q_heads=32, num_kv_heads=1, head_dim=128, max_seq_len=256, page_size=32, cluster_size=2)
+
+
+@pytest.mark.parametrize(("layout", "force_impl", "shape"), [
+    ("bf16_kv", "direct", dict(batch=2, num_q_heads=4, num_kv_heads=4, head_dim=64, max_seq_len=64, page_size=16, cluster_size=1)),
+    ("bf16_kv", "direct", SMALL_DIRECT),
+    ("int8_kv", "clustered", dict(batch=2, num_q_heads=32, num_kv_heads=4, head_dim=128, max_seq_len=256, page_size=32, cluster_size=2)),
+    ("bf16_kv", "clustered", SMALL_CLUSTERED),
+    ("fp8_kv", "clustered", dict(batch=2, num_q_heads=32, num_kv_heads=4, head_dim=128, max_seq_len=256, page_size=32, cluster_size=2)),
+])
+def test_op_matches_the_pytorch_reference(layout, force_impl, shape) -> None:
+    _reference_test_case(layout, force_impl, **shape)
+    _status_ok()
+
+
+@pytest.mark.parametrize("layout", ["bf16_kv", "fp8_kv", "int8_kv"])
+@pytest.mark.parametrize("force_impl", ["direct", "clustered"])
+def test_op_with_keys_rotated_ahead_of_time(layout, force_impl) -> None:
+    shape = SMALL_DIRECT if force_impl == "direct" else SMALL_CLUSTERED
+    _reference_test_case(layout, force_impl, key_rope_theta=10000.0, **shape)
+    _status_ok()
+
+
+def test_op_argument_errors() -> None:
+    query, cache = _reference_test_case("bf16_kv", "direct", key_rope_theta=10000.0, **SMALL_DIRECT)
+    with pytest.raises(ValueError, match="rope_theta must match"):
+        ops.clustered_page_decode(query, cache, rope_theta=5000.0, force_impl="direct")
+    with pytest.raises(ValueError, match="force_impl must be one of"):
+        ops.clustered_page_decode(query, cache, force_impl="fast")
+    with pytest.raises(TypeError, match="query must have dtype"):
+        ops.clustered_page_decode(query.float(), cache)
+    with pytest.raises(ValueError, match="query must be a CUDA tensor"):
+        ops.clustered_page_decode(query.cpu(), cache)
+    with pytest.raises(ValueError, match="head_dim must match"):
+        ops.clustered_page_decode(torch.zeros((2, 16, 128), dtype=torch.bfloat16, device="cuda"), cache)
+    torch.manual_seed(5)
+    wide = torch.randn((1, 32, 128), device="cuda").to(torch.bfloat16)
+    kv = torch.randn((1, 1, 128, 128), device="cuda").to(torch.bfloat16)
+    mqa = ops.pack_paged_kv_bf16(kv, kv, torch.tensor([100], dtype=torch.int32), page_size=32)
+    with pytest.raises(ValueError, match='force_impl="direct" only supports group_size <= 8'):
+        ops.clustered_page_decode(wide, mqa, force_impl="direct")
+
+
+# ---- descriptors the planner never produces, long requests, determinism -------------------------------
+def test_hand_written_runs_empty_requests_and_short_pages() -> None:
+    """Runs in arbitrary order with gaps in the logical numbering, a run whose last page is short in
+    the MIDDLE of a request, a request without runs, one with seq_len 0, and one of zero-length
+    pages: the kernel follows the descriptors exactly as the reference's kernels do."""
+    rng = np.random.default_rng(11)
+    pages, kv_heads, page_size, head_dim = 12, 2, 16, 64
+    keys = oracle.f32_to_bf16_bits(rng.standard_normal((pages, kv_heads, page_size, head_dim)).astype(np.float32))
+    values = oracle.f32_to_bf16_bits(rng.standard_normal((pages, kv_heads, page_size, head_dim)).astype(np.float32))
+    query = oracle.f32_to_bf16_bits(rng.standard_normal((5, 6, head_dim)).astype(np.float32))
+    runs = {
+        "run_base_pages": [7, 2, 10, 0, 5, 4],
+        "run_page_counts": [2, 3, 1, 1, 2, 1],
+        "run_logical_starts": [0, 5, 9, 0, 0, 0],
+        "run_last_page_lens": [9, 16, 1, 16, 7, 0],
+        "request_run_offsets": [0, 3, 3, 4, 5, 6],
+    }
+    dev = DeviceCase(query=query, key_pages=keys, value_pages=values, key_scales=None, value_scales=None,
+                     runs={k: np.asarray(v, dtype=np.int32) for k, v in runs.items()},
+                     seq_lens=np.asarray([150, 40, 0, 23, 1], dtype=np.int32), kv_format=0, keys_are_rotated=False,
+                     page_size=page_size)
+    want = dev.oracle(oracle)
+    assert not want[1].any() and not want[2].any() and not want[4].any()
+    for splits in (1, 0, 5):
+        out = dev.forward(pdc, splits=splits)
+        _assert_close_to_oracle(out, want, f"splits={splits}")
+        assert not out[1].float().abs().sum().item() and not out[2].float().abs().sum().item()
+    _status_ok()
+
+
+def test_request_longer_than_one_block_lists_at_a_time() -> None:
+    """1300 pages in ONE block (splits = 1) exceed the 1024 page entries a block keeps in shared
+    memory, so the list is rebuilt for a second round; with splits the same request takes one."""
+    query, cache, plan = _random_problem(batch=1, q_heads=4, kv_heads=1, head_dim=64, page_size=16, lens=[1300 * 16 - 5],
+                                         layout="bf16_kv", rotated=False, seed=3)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    for splits in (1, 0):
+        _assert_close_to_oracle(dev.forward(pdc, splits=splits), want, f"splits={splits}")
+    _status_ok()
+
+
+def test_results_do_not_depend_on_timing_and_the_workspace_stays_clean() -> None:
+    query, cache, plan = _random_problem(batch=4, q_heads=32, kv_heads=8, head_dim=128, page_size=16,
+                                         lens=[2048, 1999, 1777, 2040], layout="int8_kv", rotated=False, seed=9)
+    dev = _device_case(query, cache, plan)
+    first = dev.forward(pdc)
+    header = dev.workspace[: 64 * 1024].clone()
+    for _ in range(5):
+        assert torch.equal(dev.forward(pdc).view(torch.int16), first.view(torch.int16))
+    torch.cuda.synchronize()
+    assert not header.any().item() and not dev.workspace[: 64 * 1024].any().item()  # tickets are zero again
+    info = pdc.describe_plan(dev.args(pdc, first))
+    assert int(info["splits"]) > 1 and int(info["blocks"]) == int(info["tasks"]) * int(info["splits"])
+    one = dev.forward(pdc, splits=1)
+    assert (one.float() - first.float()).abs().max().item() <= 2e-2  # another order of the same sums
+    _status_ok()
+
+
+def test_call_recorded_into_a_cuda_graph_replays() -> None:
+    query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=32,
+                                         lens=[700, 650], layout="fp8_kv", rotated=True, seed=21)
+    dev = _device_case(query, cache, plan)
+    eager = dev.forward(pdc)
+    out = torch.zeros_like(eager)
+    args = dev.args(pdc, out)
+    stream = torch.cuda.Stream()
+    args.stream = int(stream.cuda_stream)
+    graph = torch.cuda.CUDAGraph()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(graph, stream=stream):
+        pdc.check(pdc.load_library().fk_page_decode_forward(ctypes.byref(args)))
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+    _status_ok()
+
+
+def test_group_tile_and_launch_overrides_keep_the_result() -> None:
+    query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
+                                         lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    lib = pdc.load_library()
+    for tile in (1, 2, 4, 8):
+        _assert_close_to_oracle(dev.forward(pdc, group_tile=tile), want, f"group_tile={tile}")
+    try:
+        for warps, stages in ((1, 1), (3, 2), (8, 3), (4, 4)):
+            pdc.check(lib.fk_page_decode_set_launch_config(warps, stages))
+            _assert_close_to_oracle(dev.forward(pdc), want, f"warps={warps} stages={stages}")
+    finally:
+        pdc.check(lib.fk_page_decode_set_launch_config(0, 0))
+    _status_ok()
+
+
+def test_workspace_that_is_too_small_is_refused() -> None:
+    query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
+                                         lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
+    dev = _device_case(query, cache, plan)
+    out = dev.forward(pdc)
+    args = dev.args(pdc, out, splits=4)
+    args.workspace_bytes = 64 * 1024
+    assert pdc.load_library().fk_page_decode_forward(ctypes.byref(args)) == pdc.ERR_INVALID_ARGUMENT
+    assert "workspace too small" in pdc.load_library().fk_page_decode_last_error().decode()
+    args.splits, args.workspace, args.workspace_bytes = 1, 0, 0  # one block per task needs none
+    pdc.check(pdc.load_library().fk_page_decode_forward(ctypes.byref(args)))
+    _assert_close_to_oracle(out, dev.oracle(oracle))
+    _status_ok()
+
+
+# ---- beside the reference's own CUDA kernels ----------------------------------------------------------
+@pytest.mark.skipif(not refgpu.available(), reason="oracle/_ref/libfk_reference_page_decode.so is not built")
+@pytest.mark.parametrize(("layout", "clustered", "cluster_size", "rotated", "shape"), [
+    ("bf16_kv", 0, 1, False, dict(batch=2, q_heads=16, kv_heads=4, head_dim=64, page_size=16, lens=[128, 117])),
+    ("bf16_kv", 1, 2, False, dict(batch=2, q_heads=32, kv_heads=1, head_dim=128, page_size=32, lens=[256, 230])),
+    ("int8_kv", 1, 2, False, dict(batch=2, q_heads=32, kv_heads=4, head_dim=128, page_size=32, lens=[256, 250])),
+    ("fp8_kv", 1, 4, True, dict(batch=2, q_heads=32, kv_heads=4, head_dim=128, page_size=32, lens=[1024, 1000])),
+    ("int8_kv", 0, 1, True, dict(batch=3, q_heads=8, kv_heads=4, head_dim=64, page_size=32, lens=[70, 33, 96])),
+    ("bf16_kv", 1, 4, False, dict(batch=4, q_heads=32, kv_heads=8, head_dim=128, page_size=16, lens=[2048, 2000, 1500, 2047])),
+])
+def test_beside_the_reference_cuda_kernels(layout, clustered, cluster_size, rotated, shape) -> None:
+    """Both kernels see the same bytes; both are compared with the fp64 oracle. The reference's
+    cluster kernel rounds rotated / dequantised keys and values to bf16 before multiplying
+    (clustered_page_decode.cu:522-525 there), so it is given the looser of the two bounds."""
+    query, cache, plan = _random_problem(**shape, layout=layout, rotated=rotated, seed=17)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    ours = dev.forward(pdc)
+    theirs = torch.full_like(ours, float("nan"))
+    refgpu.forward(query=dev.query, key_pages=dev.key_pages, value_pages=dev.value_pages, key_scales=dev.key_scales,
+                   value_scales=dev.value_scales, runs=dev.runs, seq_lens=dev.seq_lens, output=theirs, batch=dev.batch,
+                   num_q_heads=dev.num_q_heads, num_kv_heads=dev.num_kv_heads, head_dim=dev.head_dim,
+                   page_size=dev.page_size, group_tile=plan.group_tile, use_clustered_kernel=clustered,
+                   cluster_size=cluster_size, kv_format=dev.kv_format, keys_are_rotated=rotated,
+                   softmax_scale=dev.softmax_scale, rope_theta=dev.rope_theta,
+                   stream=int(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    _assert_close_to_oracle(ours, want, "this library")
+    _, scaled = oracle.max_abs_and_scaled_error(theirs.float().cpu().numpy().astype(np.float64), want, 2e-2, 2e-2)
+    assert scaled <= 1.0, "the reference kernel is off the oracle: the oracle or the call is wrong"
+    torch.testing.assert_close(ours, theirs, atol=2e-2, rtol=2e-2)
+    _status_ok()
