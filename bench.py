@@ -749,6 +749,143 @@ def _sharded_layers(torch, dist, capi, device, world: int, rank: int, peak_gbs: 
     return results
 
 
+# ------------------------------------------------------------------------------------------
+# the other half of a decode step: paged-KV attention (the reference's clustered_page_decode suite)
+# ------------------------------------------------------------------------------------------
+PAGE_DECODE_SHAPES = [
+    # benchmarks/suites/clustered_page_decode.toml of the reference: name, batch, page, max_len, q, kv, dim
+    ("gqa4_short_page16", 4, 16, 256, 32, 8, 128),
+    ("gqa4_long_page16", 4, 16, 2048, 32, 8, 128),
+    ("mqa8_long_page32", 2, 32, 4096, 32, 4, 128),
+    ("mqa32_long_page32", 2, 32, 4096, 32, 1, 128),
+    ("gqa2_short_page32_h64", 8, 32, 512, 16, 8, 64),
+    # a serving-sized batch: 32 requests of up to 4096 tokens, Llama-3-8B heads (537 MB of bf16 pages)
+    ("gqa4_batch32_4k_page16", 32, 16, 4096, 32, 8, 128),
+]
+
+
+def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
+    """Per-call device time of the paged-KV decode attention through the C ABI
+    (fk_page_decode_forward) on the shapes of the reference's suite, every page format, page tables
+    fragmented by a seeded permutation; the page copies of one CUDA graph together exceed L2 several
+    times. Each result is checked against the fp64 oracle on request 0. Where the reference's own
+    kernels are built (oracle/_ref), their time on the same inputs stands beside it."""
+    import ctypes
+    import importlib
+
+    import numpy as np
+    from fast_kernels import page_decode_capi as pdc
+    from oracle import page_decode_oracle as pd_oracle
+    from oracle import reference_page_decode_gpu as refgpu
+
+    ops = importlib.import_module("fast_kernels.ops.clustered_page_decode")
+    lib = pdc.load_library()
+    rows = []
+
+    def stream() -> int:  # the capturing stream while a graph is recorded
+        return int(torch.cuda.current_stream(device).cuda_stream)
+
+    for name, batch, page, max_len, q_heads, kv_heads, dim in PAGE_DECODE_SHAPES:
+        generator = torch.Generator().manual_seed(batch + max_len)
+        lens = torch.randint(max(page, max_len - page + 1), max_len + 1, (batch,), generator=generator, dtype=torch.int32)
+        query = torch.randn((batch, q_heads, dim), generator=generator).to(torch.bfloat16).to(device)
+        torch.manual_seed(batch * max_len)
+        keys = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
+        values = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
+        tokens = int(lens.sum())
+        for layout in ("bf16_kv", "fp8_kv", "int8_kv"):
+            if layout != "bf16_kv" and batch >= 32:
+                continue  # the large batch once, in bf16: its 8-bit forms are in the tests
+            build = {"bf16_kv": ops.pack_paged_kv_bf16, "fp8_kv": ops.quantize_paged_kv_fp8,
+                     "int8_kv": ops.quantize_paged_kv_int8}[layout]
+            cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1)
+            plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens,
+                                                  num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim,
+                                                  page_size=page, kv_layout=layout, use_cache=False)
+            descriptors = plan.device_tensors(device)
+            element = 2 if layout == "bf16_kv" else 1
+            algorithmic = tokens * kv_heads * dim * 2 * element + 2 * query.numel() * 2
+            if element == 1:
+                algorithmic += tokens * kv_heads * (dim // 64) * 4 + cache.total_pages * kv_heads * (dim // 64) * 4
+            key_copies = _rotated_copies(torch, cache.key_pages.view(torch.uint8).reshape(-1), 3.0e8)
+            value_copies = _rotated_copies(torch, cache.value_pages.view(torch.uint8).reshape(-1), 3.0e8)
+            workspace = torch.zeros(int(lib.fk_page_decode_workspace_bytes(batch, q_heads, kv_heads, dim)),
+                                    dtype=torch.uint8, device=device)
+            out = torch.empty_like(query)
+
+            def arguments(copy: int):
+                a = pdc.PageDecodeArgs()
+                a.query, a.output = query.data_ptr(), out.data_ptr()
+                a.key_pages, a.value_pages = key_copies[copy].data_ptr(), value_copies[copy].data_ptr()
+                a.key_scales = 0 if cache.key_scales is None else cache.key_scales.data_ptr()
+                a.value_scales = 0 if cache.value_scales is None else cache.value_scales.data_ptr()
+                for field in ("run_base_pages", "run_page_counts", "run_logical_starts", "run_last_page_lens",
+                              "request_run_offsets", "seq_lens"):
+                    setattr(a, field, descriptors[field].data_ptr())
+                a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+                a.batch, a.num_runs, a.num_q_heads, a.num_kv_heads = batch, plan.num_runs, q_heads, kv_heads
+                a.head_dim, a.page_size, a.kv_format = dim, page, ops.KV_FORMAT_IDS[layout]
+                a.max_pages_hint, a.softmax_scale, a.rope_theta = plan.max_pages, 1.0 / dim**0.5, 10000.0
+                a.stream = stream()
+                return a
+
+            def ours(copy: int) -> None:
+                pdc.check(lib.fk_page_decode_forward(ctypes.byref(arguments(copy))))
+
+            us = _time_rotation(torch, device, ours, list(range(len(key_copies))))
+            info = pdc.describe_plan(arguments(0))
+            # request 0 against the fp64 oracle (same bytes; bound: 2e-3 + 8e-3 |y|)
+            first = slice(int(plan.request_run_offsets_cpu[0]), int(plan.request_run_offsets_cpu[1]))
+
+            def raw(t):
+                return (t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16
+                        else t.view(torch.uint8).cpu().numpy())
+
+            want = pd_oracle.page_decode_f64(
+                raw(query[:1]), raw(cache.key_pages), raw(cache.value_pages),
+                None if cache.key_scales is None else cache.key_scales.cpu().numpy(),
+                None if cache.value_scales is None else cache.value_scales.cpu().numpy(),
+                plan.run_base_pages_cpu.numpy()[first], plan.run_page_counts_cpu.numpy()[first],
+                plan.run_logical_starts_cpu.numpy()[first], plan.run_last_page_lens_cpu.numpy()[first],
+                np.asarray([0, first.stop - first.start]), lens.numpy()[:1], kv_format=ops.KV_FORMAT_IDS[layout],
+                keys_are_rotated=False, softmax_scale=1.0 / dim**0.5, rope_theta=10000.0)
+            pdc.check(lib.fk_page_decode_forward(ctypes.byref(arguments(0))))
+            torch.cuda.synchronize(device)
+            worst, scaled = pd_oracle.max_abs_and_scaled_error(out[:1].float().cpu().numpy().astype(np.float64), want,
+                                                               2e-3, 8e-3)
+            row = {"shape": name, "layout": layout, "batch": batch, "tokens": tokens, "us_per_call": us,
+                   "algorithmic_bytes": algorithmic, "gbs": algorithmic / us / 1e3,
+                   "frac": algorithmic / us / 1e3 / peak_gbs, "blocks": int(info["blocks"]),
+                   "splits": int(info["splits"]), "warps": int(info["warps"]), "max_abs_err": worst,
+                   "error_over_bound": scaled, "page_copies": len(key_copies)}
+            if scaled > 1.0:
+                row["failed"] = "result is off the fp64 oracle"
+            if refgpu.available() and layout == "bf16_kv" and batch < 32:
+                group = q_heads // kv_heads
+                modes = [("reference_cluster_us", 1, max(1, plan.cluster_size))]
+                if group <= 8:
+                    modes.append(("reference_direct_us", 0, 1))
+                for key, clustered, cluster_size in modes:
+                    def theirs(copy: int) -> None:
+                        refgpu.forward(query=query, key_pages=key_copies[copy], value_pages=value_copies[copy],
+                                       key_scales=cache.key_scales, value_scales=cache.value_scales,
+                                       runs=descriptors, seq_lens=descriptors["seq_lens"], output=out, batch=batch,
+                                       num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim, page_size=page,
+                                       group_tile=plan.group_tile, use_clustered_kernel=clustered,
+                                       cluster_size=cluster_size, kv_format=0, keys_are_rotated=False,
+                                       softmax_scale=1.0 / dim**0.5, rope_theta=10000.0, stream=stream())
+
+                    row[key] = _time_rotation(torch, device, theirs, list(range(min(8, len(key_copies)))), reps=2)
+            rows.append(row)
+            del key_copies, value_copies
+    if pdc.device_status() != 0:
+        rows.append({"failed": "device status word set: a bounded wait timed out"})
+    return {"note": "paged-KV decode attention (fk_page_decode_forward), device time per call, page copies "
+                    "rotated so that every call reads HBM; frac is of the measured HBM peak",
+            "results": rows}
+
+
+
 def _kernel_table(capi, per_layer: list[dict], ms_per_step: float) -> list[dict]:
     """Per kernel (template instantiation): launches per step, time share and achieved bandwidth,
     from the per-shape timings."""
@@ -868,6 +1005,10 @@ def run_ours(args) -> int:
     if world == 1 and not args.no_extras:
         extra["configs"] = _configs_leg(torch, capi, device, peak_gbs)
         extra["reference_gpu"] = _reference_gpu_leg(torch, capi, device)
+        try:
+            extra["page_decode"] = _page_decode_leg(torch, device, peak_gbs)
+        except Exception as exc:  # the headline above is measured already: report, do not lose it
+            extra["page_decode"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0:
         ms_per_step = seconds * 1e3 / args.steps

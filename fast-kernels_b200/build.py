@@ -190,7 +190,7 @@ def build_oracle(force: bool = False) -> None:
     _run(args)
     reference = reference_checkout()
     if reference is not None:
-        _run(["make", "-C", str(oracle_dir), "ref", f"REF={reference}"])
+        _run(["make", "-C", str(oracle_dir), "ref", "ref_page_decode", f"REF={reference}"])
 
 
 def build_all(force: bool = False, oracle: bool = False) -> None:

@@ -10,19 +10,20 @@
 // head and 64-dim block; values one per token and 64-dim block).
 //
 // How it is laid out here:
-//  * A thread block serves one (request, kv head, tile of GT query heads, split s of S): the
-//    flattened list of the request's pages is dealt round-robin over the S blocks, a block's pages
-//    round-robin over its warps. The S partial results (running maximum, denominator, weighted
+//  * The unit of work is 16 tokens of one page (a page of 32 tokens is two units). A thread block
+//    serves one (request, kv head, tile of GT query heads, split s of S): the flattened list of
+//    the request's units is dealt round-robin over the S blocks, a block's units round-robin over
+//    its warps. The S partial results (running maximum, denominator, weighted
 //    value sum) meet in global scratch; the block that takes the last ticket adds them in split
 //    order and writes the output, so results do not depend on timing.
-//  * Every warp streams its own pages: a page's keys and values for one kv head are two contiguous
-//    blocks of page_size x head_dim elements (plus the values' scales), fetched by bulk
-//    asynchronous copies into a ring of `stages` buffers per warp, completion on an mbarrier. No
-//    block-wide barrier while pages stream.
+//  * Every warp streams its own units: a unit's keys and values for one kv head are two contiguous
+//    blocks of 16 x head_dim elements (plus the values' scales), fetched by bulk asynchronous
+//    copies into a ring of `stages` buffers per warp, completion on an mbarrier. No block-wide
+//    barrier while units stream.
 //  * Lane l owns head dimensions [l*EPL, (l+1)*EPL) (EPL = head_dim / 32) of every key, value,
 //    query and accumulator. The rotated, scaled query of the tile's heads sits in registers. Only
-//    the token part of a key's rotation is applied to the key (a table e^{i t theta}, t <
-//    page_size, built once per block); the page part goes to the query:
+//    the token part of a key's rotation is applied to the key (a table e^{i t theta}, t < 16,
+//    built once per block); the unit's part goes to the query:
 //    <R(a) q, R(P + t) k> = <R(a - P) q, R(t) k>. Key scales and the softmax scale ride on the
 //    query as well, value scales on the probabilities.
 //  * Partial dot products of TB tokens x GT heads (32 values per lane) are summed across lanes by
@@ -50,11 +51,17 @@ using fk_w4a16::smem_addr;
 constexpr int kKvBf16 = 0;
 constexpr int kKvFp8 = 1;
 constexpr int kKvInt8 = 2;
-constexpr int kEntryCapacity = 1024;  // pages of one block that are listed in shared memory at a time
-constexpr int kMaxWarps = 8;
+constexpr int kUnitTokens = 16;       // tokens per unit of work; pages hold one or two units
+constexpr int kEntryCapacity = 1024;  // units of one block that are listed in shared memory at a time
+constexpr int kMaxWarpsWide = 8;      // head tiles of 8: ~208 registers per thread
+constexpr int kMaxWarpsNarrow = 12;   // head tiles of 1, 2, 4: up to ~160 registers per thread
 constexpr int kMaxPairs = 64;
 constexpr int kMaxSplits = 64;
 constexpr int kStatusCopyWaitTimeout = 1;
+
+__host__ __device__ constexpr int max_warps_for(int group_tile) {
+  return group_tile >= 8 ? kMaxWarpsWide : kMaxWarpsNarrow;
+}
 
 struct DecodeParams {
   const uint16_t* query;
@@ -69,13 +76,14 @@ struct DecodeParams {
   const int32_t* request_run_offsets;
   const int32_t* seq_lens;
   uint16_t* output;
-  float* partials;    // [task * splits + s][GT][head_dim + 2]: weighted values, maximum, denominator
+  float* partials;    // [task * splits + s][GT][head_dim + 4]: weighted values, maximum, denominator, pad
   unsigned* tickets;  // [task], zero between calls
   int* status;
   int num_q_heads;
   int num_kv_heads;
   int group_size;
   int head_tiles;
+  int page_size;      // 16 or 32
   int splits;
   int stages;
   float scale_log2e;  // softmax scale times log2(e): the kernel works with exp2
@@ -85,15 +93,15 @@ struct DecodeParams {
 __host__ __device__ constexpr int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Shared-memory layout, the same arithmetic on host (size) and device (offsets).
-template <int D, int PS, int KV, bool ROT, int GT>
+template <int D, int KV, bool ROT, int GT>
 struct Layout {
   static constexpr int kElemBytes = KV == kKvBf16 ? 2 : 1;
   static constexpr bool kQuant = KV != kKvBf16;
   static constexpr int kDimBlocks = D / 64;
   static constexpr int kDbq = kQuant ? kDimBlocks : 1;  // copies of a probability (one per value scale)
-  static constexpr int kPageBytes = PS * D * kElemBytes;
-  static constexpr int kVScaleBytes = kQuant ? PS * kDimBlocks * 4 : 0;
-  static constexpr int kStageBytes = round_up(2 * kPageBytes + kVScaleBytes, 128);
+  static constexpr int kUnitBytes = kUnitTokens * D * kElemBytes;
+  static constexpr int kVScaleBytes = kQuant ? kUnitTokens * kDimBlocks * 4 : 0;
+  static constexpr int kStageBytes = round_up(2 * kUnitBytes + kVScaleBytes, 128);
   static constexpr int kEpl = D / 32;
 
   int bars, entries, kscales, inv_freq, rope, probs, alphas, ring, total;
@@ -109,14 +117,16 @@ struct Layout {
     inv_freq = at;
     at += kMaxPairs * 4;
     rope = at;
-    at += ROT ? 0 : PS * 32 * (kEpl / 2) * 8;  // per token and lane: cos, sin of each owned pair
+    at += ROT ? 0 : kUnitTokens * D * 4;  // per token and pair: cos, sin
     probs = at;
-    at += warps * PS * kDbq * GT * 4;
+    at += warps * kUnitTokens * kDbq * GT * 4;
     alphas = at;
     at += round_up(warps * GT * 4, 128);
     ring = at;
     const int ring_bytes = warps * stages * kStageBytes;
-    const int merge_bytes = warps * GT * (D + 2) * 4;
+    // after the stream: per-warp results [warps][GT][D + 2], then (last block of a task) the
+    // splits' maxima and weights [GT][kMaxSplits] twice
+    const int merge_bytes = warps * GT * (D + 2) * 4 + 2 * GT * kMaxSplits * 4;
     at += ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
     total = at;
   }
@@ -199,28 +209,24 @@ __device__ __forceinline__ void butterfly_sum(float (&v)[NV], int lane) {
   }
 }
 
-__device__ __forceinline__ float exp2_or_zero(float x) {
-  // exp2f(-inf) is 0 already; the guard is for (-inf) - (-inf), which callers avoid by passing a
-  // finite reference point
-  return exp2f(x);
-}
-
-template <int D, int PS, int KV, bool ROT, int GT>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __grid_constant__ DecodeParams p) {
-  using L = Layout<D, PS, KV, ROT, GT>;
+template <int D, int KV, bool ROT, int GT>
+__global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(const __grid_constant__ DecodeParams p) {
+  using L = Layout<D, KV, ROT, GT>;
   constexpr int EPL = L::kEpl;
   constexpr int EB = L::kElemBytes;
   constexpr bool QUANT = L::kQuant;
   constexpr int DB = L::kDimBlocks;
   constexpr int DBQ = L::kDbq;
-  constexpr int TB = (32 / GT) < PS ? (32 / GT) : PS;  // tokens per butterfly round
-  constexpr int NV = TB * GT;                         // values per lane per round
-  constexpr int NR = PS / TB;                         // rounds per page
+  constexpr int U = kUnitTokens;
+  constexpr int TB = (32 / GT) < U ? (32 / GT) : U;  // tokens per butterfly round
+  constexpr int NV = TB * GT;                       // values per lane per round
+  constexpr int NR = U / TB;                        // rounds per unit
   constexpr int CAP = kEntryCapacity;
+  constexpr int ROW = D + 4;  // floats per head of a partial result in global scratch (16-byte rows)
   static_assert(NV <= 32 && (NV & (NV - 1)) == 0);
 
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int scan_totals[kMaxWarps];
+  __shared__ int scan_totals[kMaxWarpsNarrow];
   __shared__ int last_flag;
 
   const int tid = threadIdx.x;
@@ -230,6 +236,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   const int threads = blockDim.x;
   const int stages = p.stages;
   const L layout(warps, stages);
+  const int PS = p.page_size;
+  const int UPP = PS / U;  // units per page: 1 or 2
 
   const int S = p.splits;
   const int task = blockIdx.x / S;
@@ -261,7 +269,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
   float* inv_freq_s = reinterpret_cast<float*>(smem + layout.inv_freq);
   float* rope = reinterpret_cast<float*>(smem + layout.rope);
-  float* probs = reinterpret_cast<float*>(smem + layout.probs) + warp * (PS * DBQ * GT);
+  float* probs = reinterpret_cast<float*>(smem + layout.probs) + warp * (U * DBQ * GT);
   float* alphas = reinterpret_cast<float*>(smem + layout.alphas) + warp * GT;
   const uint32_t ring = smem_addr(smem + layout.ring) + warp * stages * L::kStageBytes;
   const uint32_t my_bars = bars + warp * stages * 8;
@@ -310,38 +318,43 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   const bool holds_value = lane < NV;
   const int lane_db = (DB == 2) ? (lane >> 4) : 0;
 
-  const size_t page_head_stride = static_cast<size_t>(L::kPageBytes);
-  uint32_t iteration = 0;  // pages this warp has consumed: stage = iteration % stages
+  const size_t page_bytes = static_cast<size_t>(PS) * D * EB;
+  uint32_t iteration = 0;  // units this warp has consumed: stage = iteration % stages
   bool failed = false;
 
+  // entries[i] = (physical unit = page * UPP + sub, (logical unit << 5) | tokens in the unit)
   auto issue = [&](int entry_index, int stage) {
-    const int2 e = entries[entry_index];
-    const size_t page_head = static_cast<size_t>(e.x) * p.num_kv_heads + kv_head;
+    const int physical_unit = entries[entry_index].x;
+    const int page = physical_unit / UPP;
+    const int sub = physical_unit - page * UPP;
+    const size_t page_head = static_cast<size_t>(page) * p.num_kv_heads + kv_head;
+    const size_t offset = page_head * page_bytes + static_cast<size_t>(sub) * L::kUnitBytes;
     const uint32_t dst = ring + stage * L::kStageBytes;
     const uint32_t bar = my_bars + stage * 8;
-    mbar_expect_tx(bar, 2 * L::kPageBytes + L::kVScaleBytes);
-    bulk_copy_plain(dst, p.key_pages + page_head * page_head_stride, L::kPageBytes, bar);
-    bulk_copy_plain(dst + L::kPageBytes, p.value_pages + page_head * page_head_stride, L::kPageBytes, bar);
+    mbar_expect_tx(bar, 2 * L::kUnitBytes + L::kVScaleBytes);
+    bulk_copy_plain(dst, p.key_pages + offset, L::kUnitBytes, bar);
+    bulk_copy_plain(dst + L::kUnitBytes, p.value_pages + offset, L::kUnitBytes, bar);
     if constexpr (QUANT) {
-      bulk_copy_plain(dst + 2 * L::kPageBytes, p.value_scales + page_head * (PS * DB), L::kVScaleBytes, bar);
+      bulk_copy_plain(dst + 2 * L::kUnitBytes, p.value_scales + (page_head * PS + sub * U) * DB, L::kVScaleBytes, bar);
     }
   };
 
   float inv_freq_lane[EPL / 2];
   float q_cos[EPL / 2], q_sin[EPL / 2];  // rotation of the query when the keys come rotated
 
-  int total_pages = 0;
+  int total_units = 0;
   for (int round = 0;; ++round) {
     const int local_base = round * CAP;
-    // ---- list this block's pages: flattened page q of the request belongs to split q % S ----
+    // ---- list this block's units: flattened unit q of the request belongs to split q % S ----
     int carry = 0;
     for (int r0 = run_begin; r0 < run_end; r0 += threads) {
       const int r = r0 + tid;
       const bool valid = r < run_end;
-      const int count = valid ? max(p.run_page_counts[r], 0) : 0;
+      const int pages = valid ? max(p.run_page_counts[r], 0) : 0;
       const int base = valid ? p.run_base_pages[r] : 0;
       const int logical_start = valid ? p.run_logical_starts[r] : 0;
       const int last_len = valid ? min(max(p.run_last_page_lens[r], 0), PS) : 0;
+      const int count = pages * UPP;
       int inclusive = count;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -369,16 +382,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
             break;
           }
           if (i >= 0) {
-            const int off = q - first;
-            entries[i] = make_int2(base + off, ((logical_start + off) << 6) | (off == count - 1 ? last_len : PS));
+            const int off = q - first;           // unit within the run
+            const int page_off = off / UPP;
+            const int sub = off - page_off * UPP;
+            const int page_tokens = page_off == pages - 1 ? last_len : PS;
+            const int tokens = min(max(page_tokens - sub * U, 0), U);
+            entries[i] = make_int2((base + page_off) * UPP + sub, (((logical_start + page_off) * UPP + sub) << 5) | tokens);
           }
         }
       }
       carry += chunk_total;
       __syncthreads();
     }
-    total_pages = carry;
-    const int mine = total_pages > split ? (total_pages - split + S - 1) / S : 0;
+    total_units = carry;
+    const int mine = total_units > split ? (total_units - split + S - 1) / S : 0;
     const int in_round = max(0, min(CAP, mine - local_base));
 
     // ---- first copies of the round, then the per-block tables while they fly ----
@@ -392,13 +409,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
     }
     if (round == 0) {
       if constexpr (!ROT) {
-        // rope[(t * 32 + lane) * EPL + 2 i + {0, 1}] = cos, sin of t * theta_pair, pair = lane * EPL/2 + i
-        for (int idx = tid; idx < PS * (D / 2); idx += threads) {
+        // rope[(t * D/2 + pair) * 2 + {0, 1}] = cos, sin of t * theta_pair; lane l owns pairs
+        // l * EPL/2 ..., i.e. floats [t * D + l * EPL, + EPL)
+        for (int idx = tid; idx < U * (D / 2); idx += threads) {
           const int t = idx / (D / 2);
           const int pair = idx - t * (D / 2);
           float sn, cs;
           sincosf(static_cast<float>(t) * inv_freq_s[pair], &sn, &cs);
-          *reinterpret_cast<float2*>(&rope[(t * (D / 2) + pair) * 2]) = make_float2(cs, sn);
+          *reinterpret_cast<float2*>(&rope[idx * 2]) = make_float2(cs, sn);
         }
       }
 #pragma unroll
@@ -413,13 +431,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
       for (int idx = tid; idx < in_round * DB; idx += threads) {
         const int i = idx / DB;
         const int b = idx - i * DB;
-        const size_t page_head = static_cast<size_t>(entries[i].x) * p.num_kv_heads + kv_head;
+        const size_t page_head = static_cast<size_t>(entries[i].x / UPP) * p.num_kv_heads + kv_head;
         kscales[idx] = p.key_scales[page_head * DB + b];
       }
     }
     __syncthreads();
 
-    // ---- this warp's pages ----
+    // ---- this warp's units ----
     for (int i = warp; i < in_round && !failed; i += warps, ++iteration) {
       const int stage = iteration % stages;
       if (!mbar_wait_bounded(my_bars + stage * 8, (iteration / stages) & 1)) {
@@ -430,12 +448,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
         break;
       }
       const int2 entry = entries[i];
-      const int logical_page = entry.y >> 6;
-      const int tokens = entry.y & 63;
+      const int logical_unit = entry.y >> 5;
+      const int tokens = entry.y & 31;
       const uint32_t k_stage = ring + stage * L::kStageBytes;
-      const uint32_t v_stage = k_stage + L::kPageBytes;
+      const uint32_t v_stage = k_stage + L::kUnitBytes;
 
-      // query of this page: rotation by (a - P), key scale, softmax scale
+      // query of this unit: rotation by (a - P), key scale, softmax scale
       float q_rot[GT][EPL];
 #pragma unroll
       for (int pi = 0; pi < EPL / 2; ++pi) {
@@ -444,7 +462,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
           cs = q_cos[pi];
           sn = q_sin[pi];
         } else {
-          const int delta = query_position - logical_page * PS;
+          const int delta = query_position - logical_unit * U;
           sincosf(static_cast<float>(delta) * inv_freq_lane[pi], &sn, &cs);
         }
         float factor = p.scale_log2e;
@@ -473,7 +491,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
             float kk[EPL];
             load_elements<KV, EPL>(k_stage + t * (D * EB) + lane * (EPL * EB), kk);
             if constexpr (!ROT) {
-              const float* cs_sn = &rope[(t * 32 + lane) * EPL];
+              const float* cs_sn = &rope[t * D + lane * EPL];
 #pragma unroll
               for (int pi = 0; pi < EPL / 2; ++pi) {
                 const float2 c = *reinterpret_cast<const float2*>(cs_sn + 2 * pi);
@@ -499,28 +517,28 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
       }
 
       // ---- online softmax for head (lane % GT) ----
-      float page_max = logit[0];
+      float unit_max = logit[0];
 #pragma unroll
       for (int r = 1; r < NR; ++r) {
-        page_max = fmaxf(page_max, logit[r]);
+        unit_max = fmaxf(unit_max, logit[r]);
       }
 #pragma unroll
       for (int o = GT; o < 32; o <<= 1) {
-        page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, o));
+        unit_max = fmaxf(unit_max, __shfl_xor_sync(0xffffffffu, unit_max, o));
       }
-      const float m_new = fmaxf(m_run, page_max);
+      const float m_new = fmaxf(m_run, unit_max);
       const float m_ref = m_new == -INFINITY ? 0.0f : m_new;
-      const float alpha = exp2_or_zero(m_run - m_ref);
+      const float alpha = exp2f(m_run - m_ref);
       float p_sum = 0.0f;
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const float prob = exp2_or_zero(logit[r] - m_ref);
+        const float prob = exp2f(logit[r] - m_ref);
         p_sum += prob;
         if (holds_value && r * TB < tokens) {
           const int t = r * TB + my_token;
           if constexpr (QUANT) {
             const float* vs = reinterpret_cast<const float*>(smem + layout.ring) +
-                              ((warp * stages + stage) * L::kStageBytes + 2 * L::kPageBytes) / 4 + t * DB;
+                              ((warp * stages + stage) * L::kStageBytes + 2 * L::kUnitBytes) / 4 + t * DB;
 #pragma unroll
             for (int b = 0; b < DB; ++b) {
               probs[(t * DBQ + b) * GT + my_head] = prob * vs[b];
@@ -607,6 +625,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   float* merge_m = merge;                     // [warps][GT]
   float* merge_l = merge + warps * GT;        // [warps][GT]
   float* merge_acc = merge + 2 * warps * GT;  // [warps][GT][D]
+  float* split_m = merge + warps * GT * (D + 2);  // [GT][kMaxSplits] maxima, then weights
+  float* split_l = split_m + GT * kMaxSplits;     // [GT][kMaxSplits] denominators
   if (lane < GT) {
     merge_m[warp * GT + lane] = m_run;
     merge_l[warp * GT + lane] = l_run;
@@ -620,7 +640,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   }
   __syncthreads();
 
-  float* my_partial = p.partials + (static_cast<size_t>(task) * S + split) * (GT * (D + 2));
+  float* my_partial = p.partials + (static_cast<size_t>(task) * S + split) * (GT * ROW);
   for (int idx = tid; idx < tile_heads * D; idx += threads) {
     const int h = idx / D;
     const int d = idx - h * D;
@@ -631,7 +651,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
     const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
     float l_all = 0.0f, a_all = 0.0f;
     for (int w = 0; w < warps; ++w) {
-      const float weight = exp2_or_zero(merge_m[w * GT + h] - m_ref);
+      const float weight = exp2f(merge_m[w * GT + h] - m_ref);
       l_all += weight * merge_l[w * GT + h];
       a_all += weight * merge_acc[(w * GT + h) * D + d];
     }
@@ -639,10 +659,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
       const float y = l_all == 0.0f ? 0.0f : a_all / l_all;
       p.output[out_base + idx] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
     } else {
-      my_partial[h * (D + 2) + d] = a_all;
+      my_partial[h * ROW + d] = a_all;
       if (d == 0) {
-        my_partial[h * (D + 2) + D] = m_all;
-        my_partial[h * (D + 2) + D + 1] = l_all;
+        my_partial[h * ROW + D] = m_all;
+        my_partial[h * ROW + D + 1] = l_all;
       }
     }
   }
@@ -658,27 +678,56 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) page_decode_kernel(const __
   if (!last_flag) {
     return;
   }
+  // The last block of the task adds the S partial results in split order. First the maxima and
+  // denominators (one load each, all in flight together), then the weights, then the values as
+  // 16-byte loads with the splits unrolled so that many are in flight.
   __threadfence();
-  const float* task_partials = p.partials + static_cast<size_t>(task) * S * (GT * (D + 2));
-  for (int idx = tid; idx < tile_heads * D; idx += threads) {
-    const int h = idx / D;
-    const int d = idx - h * D;
-    const float* head_partial = task_partials + h * (D + 2);
+  const float* task_partials = p.partials + static_cast<size_t>(task) * S * (GT * ROW);
+  for (int idx = tid; idx < tile_heads * S; idx += threads) {
+    const int h = idx / S;
+    const int s = idx - h * S;
+    const float* src = task_partials + static_cast<size_t>(s) * (GT * ROW) + h * ROW + D;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(src));
+    split_m[h * kMaxSplits + s] = ml.x;
+    split_l[h * kMaxSplits + s] = ml.y;
+  }
+  __syncthreads();
+  if (tid < tile_heads) {
     float m_all = -INFINITY;
     for (int s = 0; s < S; ++s) {
-      m_all = fmaxf(m_all, __ldcg(head_partial + static_cast<size_t>(s) * (GT * (D + 2)) + D));
+      m_all = fmaxf(m_all, split_m[tid * kMaxSplits + s]);
     }
     const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
-    float l_all = 0.0f, a_all = 0.0f;
-#pragma unroll 4
+    float l_all = 0.0f;
     for (int s = 0; s < S; ++s) {
-      const float* src = head_partial + static_cast<size_t>(s) * (GT * (D + 2));
-      const float weight = exp2_or_zero(__ldcg(src + D) - m_ref);
-      l_all += weight * __ldcg(src + D + 1);
-      a_all += weight * __ldcg(src + d);
+      const float weight = exp2f(split_m[tid * kMaxSplits + s] - m_ref);
+      l_all += weight * split_l[tid * kMaxSplits + s];
+      split_m[tid * kMaxSplits + s] = weight;
     }
-    const float y = l_all == 0.0f ? 0.0f : a_all / l_all;
-    p.output[out_base + idx] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
+    split_l[tid * kMaxSplits] = l_all == 0.0f ? 0.0f : 1.0f / l_all;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < tile_heads * (D / 4); idx += threads) {
+    const int h = idx / (D / 4);
+    const int d = (idx - h * (D / 4)) * 4;
+    const float* src = task_partials + h * ROW + d;
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+    for (int s = 0; s < S; ++s) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(s) * (GT * ROW)));
+      const float weight = split_m[h * kMaxSplits + s];
+      sum.x = fmaf(weight, v.x, sum.x);
+      sum.y = fmaf(weight, v.y, sum.y);
+      sum.z = fmaf(weight, v.z, sum.z);
+      sum.w = fmaf(weight, v.w, sum.w);
+    }
+    const float inv = split_l[h * kMaxSplits];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * inv, sum.y * inv);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(sum.z * inv, sum.w * inv);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.output + out_base + static_cast<size_t>(h) * D + d) = packed;
   }
   if (tid == 0) {
     p.tickets[task] = 0;

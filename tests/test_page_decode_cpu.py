@@ -216,7 +216,7 @@ def test_argument_errors_come_before_any_launch() -> None:
         pdc.check(pdc.ERR_INVALID_ARGUMENT)
     assert lib.fk_page_decode_workspace_bytes(0, 8, 2, 128) == 0
     assert lib.fk_page_decode_workspace_bytes(4, 32, 8, 128) >= 64 * 1024
-    assert lib.fk_page_decode_set_launch_config(9, 0) == pdc.ERR_INVALID_ARGUMENT
+    assert lib.fk_page_decode_set_launch_config(13, 0) == pdc.ERR_INVALID_ARGUMENT
     assert lib.fk_page_decode_set_launch_config(0, 0) == pdc.OK
 
 
