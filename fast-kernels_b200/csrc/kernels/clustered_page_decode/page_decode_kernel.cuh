@@ -191,16 +191,31 @@ __device__ __forceinline__ void load_elements(uint32_t addr, float (&x)[EPL]) {
 }
 
 // Sum over lanes of NV values per lane; lane l is left with the total of value (l % NV) in v[0].
-template <int NV>
+// Value index = token * GT + head. A step with lane offset o settles index bit o: a lane keeps the
+// half whose bit equals its own lane bit and hands the other half to its partner. For the token
+// bits (o >= GT) the caller has ALREADY permuted the tokens per lane -- local token tl stands for
+// token tl ^ ((lane / GT) % TB) -- so the half to keep is always the lower one and no selects are
+// needed; the head bits (o < GT) cannot be permuted that way (the queries sit in registers).
+// The permutation makes the row address of a token a per-lane value instead of an immediate (a
+// few integer instructions per token), which pays from head tiles of 4 on: FLIP says whether the
+// caller did it.
+template <int NV, int GT, bool FLIP>
 __device__ __forceinline__ void butterfly_sum(float (&v)[NV], int lane) {
 #pragma unroll
   for (int o = NV / 2; o >= 1; o >>= 1) {
-    const bool upper = (lane & o) != 0;
+    if (FLIP && o >= GT) {
 #pragma unroll
-    for (int i = 0; i < o; ++i) {
-      const float keep = upper ? v[i + o] : v[i];
-      const float give = upper ? v[i] : v[i + o];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+      for (int i = 0; i < o; ++i) {
+        v[i] += __shfl_xor_sync(0xffffffffu, v[i + o], o);
+      }
+    } else {
+      const bool upper = (lane & o) != 0;
+#pragma unroll
+      for (int i = 0; i < o; ++i) {
+        const float keep = upper ? v[i + o] : v[i];
+        const float give = upper ? v[i] : v[i + o];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+      }
     }
   }
 #pragma unroll
@@ -252,18 +267,6 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   const int first_q_head = kv_head * p.group_size + tile_base;
   const size_t out_base = (static_cast<size_t>(request) * p.num_q_heads + first_q_head) * D;
 
-  const int query_position = p.seq_lens[request] - 1;
-  const int run_begin = p.request_run_offsets[request];
-  const int run_end = p.request_run_offsets[request + 1];
-  if (query_position < 0 || run_begin >= run_end) {
-    if (split == 0) {
-      for (int idx = tid; idx < tile_heads * D; idx += threads) {
-        p.output[out_base + idx] = 0;
-      }
-    }
-    return;  // every block of the task takes this branch: nobody waits for a ticket
-  }
-
   const uint32_t bars = smem_addr(smem + layout.bars);
   int2* entries = reinterpret_cast<int2*>(smem + layout.entries);
   float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
@@ -281,6 +284,23 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     inv_freq_s[tid] = p.inv_freq[tid];
   }
   mbar_init_fence();
+  // Programmatic dependent launch (no-ops without the launch attribute): the next kernel of the
+  // stream may be scheduled from here on, and nothing of global memory is touched before the
+  // previous one has completed.
+  fk_w4a16::pdl_launch_dependents();
+  fk_w4a16::pdl_wait_for_prerequisites();
+
+  const int query_position = p.seq_lens[request] - 1;
+  const int run_begin = p.request_run_offsets[request];
+  const int run_end = p.request_run_offsets[request + 1];
+  if (query_position < 0 || run_begin >= run_end) {
+    if (split == 0) {
+      for (int idx = tid; idx < tile_heads * D; idx += threads) {
+        p.output[out_base + idx] = 0;
+      }
+    }
+    return;  // every block of the task takes this branch: nobody waits for a ticket
+  }
 
   // This lane's part of the tile's queries (bf16 -> fp32; heads past the group are zero).
   float q_in[GT][EPL];
@@ -315,6 +335,8 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   float l_run = 0.0f;
   const int my_head = lane % GT;
   const int my_token = (lane % NV) / GT;  // within a butterfly round
+  constexpr bool FLIP = GT >= 4;
+  const int token_flip = FLIP ? (lane / GT) % TB : 0;  // local token tl of a round stands for token tl ^ token_flip
   const bool holds_value = lane < NV;
   const int lane_db = (DB == 2) ? (lane >> 4) : 0;
 
@@ -487,17 +509,23 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
           float vals[NV];
 #pragma unroll
           for (int tl = 0; tl < TB; ++tl) {
-            const int t = r * TB + tl;
+            const int t = r * TB + (tl ^ token_flip);
             float kk[EPL];
             load_elements<KV, EPL>(k_stage + t * (D * EB) + lane * (EPL * EB), kk);
             if constexpr (!ROT) {
-              const float* cs_sn = &rope[t * D + lane * EPL];
+              float cs_sn[EPL];
+              if constexpr (EPL == 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(&rope[t * D + lane * EPL]);
+                cs_sn[0] = c4.x, cs_sn[1] = c4.y, cs_sn[2] = c4.z, cs_sn[3] = c4.w;
+              } else {
+                const float2 c2 = *reinterpret_cast<const float2*>(&rope[t * D + lane * EPL]);
+                cs_sn[0] = c2.x, cs_sn[1] = c2.y;
+              }
 #pragma unroll
               for (int pi = 0; pi < EPL / 2; ++pi) {
-                const float2 c = *reinterpret_cast<const float2*>(cs_sn + 2 * pi);
                 const float ke = kk[2 * pi], ko = kk[2 * pi + 1];
-                kk[2 * pi] = ke * c.x - ko * c.y;
-                kk[2 * pi + 1] = ke * c.y + ko * c.x;
+                kk[2 * pi] = ke * cs_sn[2 * pi] - ko * cs_sn[2 * pi + 1];
+                kk[2 * pi + 1] = ke * cs_sn[2 * pi + 1] + ko * cs_sn[2 * pi];
               }
             }
 #pragma unroll
@@ -510,7 +538,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
               vals[tl * GT + h] = sum;
             }
           }
-          butterfly_sum<NV>(vals, lane);
+          butterfly_sum<NV, GT, FLIP>(vals, lane);
           const int t = r * TB + my_token;
           logit[r] = t < tokens ? vals[0] : -INFINITY;
         }

@@ -6,7 +6,8 @@ non-empty; a bench run validates first, then writes
 ``<root>/<suite.id>/<run_id>/{metadata.json,results.json,results.csv,summary.md,plots/status_counts.svg}``.
 Suites of the ``decode_quant_linear`` family are executed (the reference dispatches on the one suite
 id ``decode_linear_w4a16``; widening to the family lets the added bf16 / edge-shape suites run);
-any other suite yields ``not_implemented`` cases, as the reference's scaffold path does.
+suites of the ``clustered_page_decode`` family likewise; any other suite yields ``not_implemented``
+cases, as the reference's scaffold path does.
 """
 
 from __future__ import annotations
@@ -69,6 +70,10 @@ def _execute(suite: BenchmarkSuite) -> tuple[list[BenchmarkCase], list[str]]:
         from fast_kernels.benchmarking.decode_linear_w4a16 import run_decode_linear_w4a16_suite
 
         return run_decode_linear_w4a16_suite(suite)
+    if suite.family == "clustered_page_decode":
+        from fast_kernels.benchmarking.clustered_page_decode import run_clustered_page_decode_suite
+
+        return run_clustered_page_decode_suite(suite)
     return _scaffold_cases(suite), ["Scaffold run: this suite's family has no runner in this build."]
 
 

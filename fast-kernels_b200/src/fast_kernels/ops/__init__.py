@@ -1,6 +1,19 @@
-"""Python ops of the W4A16 decode path (same public names as the reference's ``fast_kernels.ops``
+"""Python ops of the decode path: the W4A16 linear layer and the paged-KV attention (same public names as the reference's ``fast_kernels.ops``
 for this kernel family, plus the bf16 / explicit-dtype additions)."""
 
+from fast_kernels.ops.clustered_page_decode import (
+    ClusteredPageDecodePlan,
+    PagedKVCache,
+    clustered_page_decode,
+    cuda_clustered_decode_available,
+    estimate_page_decode_metrics,
+    materialize_reference_dense_kv,
+    pack_paged_kv_bf16,
+    plan_clustered_page_decode,
+    quantize_paged_kv_fp8,
+    quantize_paged_kv_int8,
+    reference_clustered_page_decode,
+)
 from fast_kernels.ops.decode_quant_linear import (
     LAYOUT_TO_GROUP_SIZE,
     arc_packet_stride_bytes,
@@ -15,6 +28,17 @@ from fast_kernels.ops.decode_quant_linear import (
 )
 
 __all__ = [
+    "ClusteredPageDecodePlan",
+    "PagedKVCache",
+    "clustered_page_decode",
+    "cuda_clustered_decode_available",
+    "estimate_page_decode_metrics",
+    "materialize_reference_dense_kv",
+    "pack_paged_kv_bf16",
+    "plan_clustered_page_decode",
+    "quantize_paged_kv_fp8",
+    "quantize_paged_kv_int8",
+    "reference_clustered_page_decode",
     "LAYOUT_TO_GROUP_SIZE",
     "arc_packet_stride_bytes",
     "arc_w4a16_forward",

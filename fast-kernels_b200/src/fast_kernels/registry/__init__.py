@@ -1,6 +1,6 @@
 """Kernel and baseline ids a suite may name (``fk verify`` checks suites against these).
 
-The W4A16 ids are the reference's (src/fast_kernels/registry/kernels.py:17-49 and
+The W4A16 and paged-decode ids are the reference's (src/fast_kernels/registry/kernels.py:17-49 and
 baselines.py:16-27); here all four kernel ids run the one sm_100a kernel. ``template/noop_gemm``
 and its two baselines stay registered because the reference's CLI smoke test benches the
 scaffold suite that names them.
@@ -39,6 +39,12 @@ def kernel_registry() -> dict[str, KernelSpec]:
         KernelSpec("decode/w4a16_linear_scalar", "decode_quant_linear", _ONE_KERNEL + "; impl=scalar", "beta", "scalar"),
         KernelSpec("decode/w4a16_linear_tc", "decode_quant_linear", _ONE_KERNEL + "; impl=tc (same kernel)", "beta", "tc"),
         KernelSpec("decode/w4a16_linear_wgmma", "decode_quant_linear", _ONE_KERNEL + "; impl=wgmma (same kernel)", "beta", "wgmma"),
+        KernelSpec("decode/clustered_page_decode_auto", "clustered_page_decode",
+                   "sm_100a paged-KV decode attention (bulk-copy unit ring per warp, split over blocks); force_impl=auto", "beta", "auto"),
+        KernelSpec("decode/clustered_page_decode_direct", "clustered_page_decode",
+                   "the same kernel, one block per (request, kv head, head tile); force_impl=direct", "beta", "direct"),
+        KernelSpec("decode/clustered_page_decode_clustered", "clustered_page_decode",
+                   "the same kernel, pages cut over as many blocks as fill the device; force_impl=clustered", "beta", "clustered"),
         KernelSpec("template/noop_gemm", "gemm", "scaffold entry used by the template suite", "scaffold", None),
     ]
     return {spec.kernel_id: spec for spec in specs}
@@ -50,6 +56,10 @@ def baseline_registry() -> dict[str, BaselineSpec]:
                      "dequantise to a 16-bit weight with the native kernel, then torch.mm"),
         BaselineSpec("vendor/cublaslt_fp16_after_dequant", "vendor", "decode_quant_linear",
                      "dequantise, then a cuBLASLt GEMM with fp32 compute"),
+        BaselineSpec("torch/reference_clustered_page_decode", "torch", "clustered_page_decode",
+                     "dense gather through the page table, rotary embedding, softmax attention in PyTorch"),
+        BaselineSpec("vendor/flashinfer_clustered_page_decode", "vendor", "clustered_page_decode",
+                     "registered as in the reference; reported as skipped (no cache-layout converter here)"),
         BaselineSpec("torch/reference_gemm", "torch", "gemm", "scaffold baseline of the template suite"),
         BaselineSpec("vendor/cublaslt_gemm", "vendor", "gemm", "scaffold baseline of the template suite"),
     ]

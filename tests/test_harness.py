@@ -56,6 +56,25 @@ def test_decode_bench_writes_a_bundle_without_a_gpu(tmp_path: Path) -> None:
     assert first.case_id == "kernel-decode__w4a16_linear-fp16-groupwise_64-llama_qkv_bs1"
 
 
+def test_page_decode_suite_keeps_the_reference_contract_and_benches(tmp_path: Path) -> None:
+    """Ids, shapes and tolerances of the reference's benchmarks/suites/clustered_page_decode.toml; the
+    bench writes one case per subject x layout x shape (skipped without a GPU, never silently run on
+    the CPU)."""
+    suite = load_suite(SUITES / "clustered_page_decode.toml")
+    assert suite.id == "clustered_page_decode" and suite.family == "clustered_page_decode"
+    assert suite.kernels.ids == ["decode/clustered_page_decode_auto", "decode/clustered_page_decode_direct",
+                                 "decode/clustered_page_decode_clustered"]
+    assert suite.baselines.ids == ["torch/reference_clustered_page_decode", "vendor/flashinfer_clustered_page_decode"]
+    assert suite.layouts == ["bf16_kv", "fp8_kv", "int8_kv"] and [s.name for s in suite.shapes] == [
+        "gqa4_short_page16", "gqa4_long_page16", "mqa8_long_page32", "mqa32_long_page32", "gqa2_short_page32_h64"]
+    assert suite.shapes[3].dimensions()["num_kv_heads"] == 1 and suite.shapes[3].dimensions()["max_seq_len"] == 4096
+    assert suite.tolerances.atol == 0.125 and suite.tolerances.rtol == 0.03
+    run_dir = benchmark_suite(SUITES / "clustered_page_decode.toml", tmp_path)
+    bundle = load_result_bundle(run_dir)
+    assert len(bundle.cases) == (3 + 2) * 1 * 3 * 5
+    assert {case.status for case in bundle.cases} <= {"ok", "skipped", "failed"}
+
+
 def test_cli_env_and_template_bench(tmp_path: Path, capsys: pytest.CaptureFixture[str]) -> None:
     assert fk_main(["env", "--json"]) == 0
     payload = json.loads(capsys.readouterr().out)

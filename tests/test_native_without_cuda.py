@@ -21,7 +21,7 @@ REFERENCE_OPS = [
     "pack_arc_w4a16_packets", "compute_arc_w4a16_group_sums", "arc_w4a16_forward",
     "arc_w4a16_forward_split_k", "reduce_arc_w4a16_split_k_partials", "dequant_w4a16_to_fp16",
     "dequant_arc_w4a16_packets_to_fp16", "cublaslt_fp16_with_weight",
-    "cublaslt_fp16_after_packet_dequant", "cublaslt_fp16_after_dequant",
+    "cublaslt_fp16_after_packet_dequant", "cublaslt_fp16_after_dequant", "clustered_page_decode_forward",
 ]
 
 CHILD = r"""
@@ -40,6 +40,12 @@ calls = {
                                          stream_ptr=0),
     "dequant_w4a16_to_fp16": dict(q_ptr=0, alpha_ptr=0, beta_ptr=0, output_ptr=0, n=128, k=128,
                                   group_size=128, stream_ptr=0),
+    "clustered_page_decode_forward": dict(
+        query_ptr=0, key_ptr=0, value_ptr=0, key_scales_ptr=0, value_scales_ptr=0, run_base_pages_ptr=0,
+        run_page_counts_ptr=0, run_logical_starts_ptr=0, run_last_page_lens_ptr=0, request_run_offsets_ptr=0,
+        seq_lens_ptr=0, output_ptr=0, batch=1, num_runs=1, num_q_heads=8, num_kv_heads=2, head_dim=128,
+        page_size=16, group_tile=4, use_clustered_kernel=1, cluster_size=2, kv_format=0, keys_are_rotated=0,
+        softmax_scale=0.1, rope_theta=10000.0, stream_ptr=0),
 }
 for name, kwargs in calls.items():
     try:
