@@ -280,8 +280,8 @@ PYBIND11_MODULE(_native, m) {
     return dql::arc_w4a16_device_status();
   });
 
-  // ---- paged-KV decode attention: the reference's name and keyword arguments, plus one
-  // optional hint at the end ------------------------------------------------------------------
+  // ---- paged-KV decode attention: the reference's name and keyword arguments, plus two
+  // optional ones at the end ------------------------------------------------------------------
   m.def(
       "clustered_page_decode_forward",
       [](ptr_t query_ptr, ptr_t key_ptr, ptr_t value_ptr, ptr_t key_scales_ptr, ptr_t value_scales_ptr,
@@ -289,14 +289,14 @@ PYBIND11_MODULE(_native, m) {
          ptr_t run_last_page_lens_ptr, ptr_t request_run_offsets_ptr, ptr_t seq_lens_ptr, ptr_t output_ptr,
          int batch, int num_runs, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
          int group_tile, int use_clustered_kernel, int cluster_size, int kv_format, int keys_are_rotated,
-         float softmax_scale, float rope_theta, ptr_t stream_ptr, int max_pages_hint) {
+         float softmax_scale, float rope_theta, ptr_t stream_ptr, int max_pages_hint, int early_descriptors) {
         py::gil_scoped_release release;
         fast_kernels::clustered_page_decode::clustered_page_decode_forward_hinted(
             query_ptr, key_ptr, value_ptr, key_scales_ptr, value_scales_ptr, run_base_pages_ptr,
             run_page_counts_ptr, run_logical_starts_ptr, run_last_page_lens_ptr, request_run_offsets_ptr,
             seq_lens_ptr, output_ptr, batch, num_runs, num_q_heads, num_kv_heads, head_dim, page_size,
             group_tile, use_clustered_kernel, cluster_size, kv_format, keys_are_rotated, softmax_scale,
-            rope_theta, max_pages_hint, stream_ptr);
+            rope_theta, max_pages_hint, early_descriptors, stream_ptr);
       },
       py::arg("query_ptr"), py::arg("key_ptr"), py::arg("value_ptr"), py::arg("key_scales_ptr"),
       py::arg("value_scales_ptr"), py::arg("run_base_pages_ptr"), py::arg("run_page_counts_ptr"),
@@ -305,7 +305,7 @@ PYBIND11_MODULE(_native, m) {
       py::arg("num_runs"), py::arg("num_q_heads"), py::arg("num_kv_heads"), py::arg("head_dim"),
       py::arg("page_size"), py::arg("group_tile"), py::arg("use_clustered_kernel"), py::arg("cluster_size"),
       py::arg("kv_format"), py::arg("keys_are_rotated"), py::arg("softmax_scale"), py::arg("rope_theta"),
-      py::arg("stream_ptr"), py::arg("max_pages_hint") = 0);
+      py::arg("stream_ptr"), py::arg("max_pages_hint") = 0, py::arg("early_descriptors") = 0);
   m.def("page_decode_device_status", []() {
     py::gil_scoped_release release;
     return fast_kernels::clustered_page_decode::page_decode_device_status();

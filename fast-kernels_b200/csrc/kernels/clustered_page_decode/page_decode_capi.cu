@@ -120,6 +120,9 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
   if (a.splits < 0 || a.splits > kMaxSplits) {
     return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "splits must be in [0, 64]");
   }
+  if ((a.flags & ~FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS) != 0) {
+    return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "unknown bits in flags");
+  }
   if (a.max_pages_hint < 0) {
     return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "max_pages_hint must be non-negative");
   }
@@ -298,6 +301,7 @@ FK_PAGE_DECODE_API int fk_page_decode_forward(const fk_page_decode_args* args) {
   params.page_size = a.page_size;
   params.splits = plan.splits;
   params.stages = plan.stages;
+  params.early_descriptors = (a.flags & FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS) != 0 ? 1 : 0;
   params.scale_log2e = static_cast<float>(static_cast<double>(a.softmax_scale) * 1.4426950408889634);
   for (int i = 0; i < a.head_dim / 2; ++i) {
     params.inv_freq[i] = static_cast<float>(

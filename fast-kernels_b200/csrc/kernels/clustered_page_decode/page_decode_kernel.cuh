@@ -52,7 +52,7 @@ constexpr int kKvBf16 = 0;
 constexpr int kKvFp8 = 1;
 constexpr int kKvInt8 = 2;
 constexpr int kUnitTokens = 16;       // tokens per unit of work; pages hold one or two units
-constexpr int kEntryCapacity = 1024;  // units of one block that are listed in shared memory at a time
+constexpr int kEntryCapacity = 512;   // units of one block that are listed in shared memory at a time
 constexpr int kMaxWarpsWide = 8;      // head tiles of 8: ~208 registers per thread
 constexpr int kMaxWarpsNarrow = 12;   // head tiles of 1, 2, 4: up to ~160 registers per thread
 constexpr int kMaxPairs = 64;
@@ -86,6 +86,7 @@ struct DecodeParams {
   int page_size;      // 16 or 32
   int splits;
   int stages;
+  int early_descriptors;  // the run arrays and seq_lens are not written by the preceding kernel
   float scale_log2e;  // softmax scale times log2(e): the kernel works with exp2
   float inv_freq[kMaxPairs];  // theta^(-2 i / head_dim), rounded once from double
 };
@@ -101,10 +102,15 @@ struct Layout {
   static constexpr int kDbq = kQuant ? kDimBlocks : 1;  // copies of a probability (one per value scale)
   static constexpr int kUnitBytes = kUnitTokens * D * kElemBytes;
   static constexpr int kVScaleBytes = kQuant ? kUnitTokens * kDimBlocks * 4 : 0;
-  static constexpr int kStageBytes = round_up(2 * kUnitBytes + kVScaleBytes, 128);
+  static constexpr int kStageBytes = 2 * kUnitBytes;  // keys, then values, of one unit
+  static constexpr int kRopeBytes = ROT ? 0 : kUnitTokens * D * 4;  // per token and pair: cos, sin
+  // The key block of a stage and the rotation table are addressed as base ^ (row offset), which
+  // needs them aligned to their own size (16 rows). Both sit at the end of the layout behind one
+  // run-time alignment of the shared-memory address; kAlign bytes of slack pay for it.
+  static constexpr int kAlign = ROT ? kUnitBytes : (kRopeBytes > kUnitBytes ? kRopeBytes : kUnitBytes);
   static constexpr int kEpl = D / 32;
 
-  int bars, entries, kscales, inv_freq, rope, probs, alphas, ring, total;
+  int bars, entries, kscales, inv_freq, vscales, probs, alphas, tail, total;
 
   __host__ __device__ Layout(int warps, int stages) {
     int at = 0;
@@ -116,18 +122,18 @@ struct Layout {
     at += kQuant ? kEntryCapacity * kDimBlocks * 4 : 0;
     inv_freq = at;
     at += kMaxPairs * 4;
-    rope = at;
-    at += ROT ? 0 : kUnitTokens * D * 4;  // per token and pair: cos, sin
+    vscales = at;
+    at += round_up(warps * stages * kVScaleBytes, 128);
     probs = at;
     at += warps * kUnitTokens * kDbq * GT * 4;
     alphas = at;
     at += round_up(warps * GT * 4, 128);
-    ring = at;
+    tail = at;  // aligned at run time: rotation table, then the ring
     const int ring_bytes = warps * stages * kStageBytes;
-    // after the stream: per-warp results [warps][GT][D + 2], then (last block of a task) the
-    // splits' maxima and weights [GT][kMaxSplits] twice
+    // after the stream the ring's memory holds per-warp results [warps][GT][D + 2], then (last
+    // block of a task) the splits' maxima and weights [GT][kMaxSplits] twice
     const int merge_bytes = warps * GT * (D + 2) * 4 + 2 * GT * kMaxSplits * 4;
-    at += ring_bytes > merge_bytes ? ring_bytes : merge_bytes;
+    at += kAlign + kRopeBytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
     total = at;
   }
 };
@@ -271,10 +277,17 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   int2* entries = reinterpret_cast<int2*>(smem + layout.entries);
   float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
   float* inv_freq_s = reinterpret_cast<float*>(smem + layout.inv_freq);
-  float* rope = reinterpret_cast<float*>(smem + layout.rope);
   float* probs = reinterpret_cast<float*>(smem + layout.probs) + warp * (U * DBQ * GT);
   float* alphas = reinterpret_cast<float*>(smem + layout.alphas) + warp * GT;
-  const uint32_t ring = smem_addr(smem + layout.ring) + warp * stages * L::kStageBytes;
+  const float* vscales = reinterpret_cast<const float*>(smem + layout.vscales) + warp * stages * (L::kVScaleBytes / 4);
+  const uint32_t vscales_addr = smem_addr(smem + layout.vscales) + warp * stages * L::kVScaleBytes;
+  // rotation table and ring behind one run-time alignment (see Layout)
+  const uint32_t tail_addr = (smem_addr(smem + layout.tail) + (L::kAlign - 1)) & ~static_cast<uint32_t>(L::kAlign - 1);
+  unsigned char* tail_ptr = smem + layout.tail + (tail_addr - smem_addr(smem + layout.tail));
+  float* rope = reinterpret_cast<float*>(tail_ptr);
+  const uint32_t rope_addr = tail_addr;
+  unsigned char* ring_ptr = tail_ptr + L::kRopeBytes;
+  const uint32_t ring = tail_addr + L::kRopeBytes + warp * stages * L::kStageBytes;
   const uint32_t my_bars = bars + warp * stages * 8;
 
   if (tid < warps * stages) {
@@ -285,15 +298,34 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   }
   mbar_init_fence();
   // Programmatic dependent launch (no-ops without the launch attribute): the next kernel of the
-  // stream may be scheduled from here on, and nothing of global memory is touched before the
-  // previous one has completed.
+  // stream may be scheduled from here on. What follows up to the wait touches no global memory:
+  // the table e^{i t theta} of the keys' token rotation.
   fk_w4a16::pdl_launch_dependents();
-  fk_w4a16::pdl_wait_for_prerequisites();
+  __syncthreads();
+  if constexpr (!ROT) {
+    // rope[(t * D/2 + pair) * 2 + {0, 1}] = cos, sin of t * theta_pair; lane l owns pairs
+    // l * EPL/2 ..., i.e. floats [t * D + l * EPL, + EPL)
+    for (int idx = tid; idx < U * (D / 2); idx += threads) {
+      const int t = idx / (D / 2);
+      const int pair = idx - t * (D / 2);
+      float sn, cs;
+      sincosf(static_cast<float>(t) * inv_freq_s[pair], &sn, &cs);
+      *reinterpret_cast<float2*>(&rope[idx * 2]) = make_float2(cs, sn);
+    }
+  }
+  // Nothing of global memory is read before the previous kernel of the stream has completed --
+  // except, if the caller says that kernel does not write them, the request descriptors.
+  if (!p.early_descriptors) {
+    fk_w4a16::pdl_wait_for_prerequisites();
+  }
 
   const int query_position = p.seq_lens[request] - 1;
   const int run_begin = p.request_run_offsets[request];
   const int run_end = p.request_run_offsets[request + 1];
   if (query_position < 0 || run_begin >= run_end) {
+    if (p.early_descriptors) {
+      fk_w4a16::pdl_wait_for_prerequisites();
+    }
     if (split == 0) {
       for (int idx = tid; idx < tile_heads * D; idx += threads) {
         p.output[out_base + idx] = 0;
@@ -302,25 +334,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     return;  // every block of the task takes this branch: nobody waits for a ticket
   }
 
-  // This lane's part of the tile's queries (bf16 -> fp32; heads past the group are zero).
-  float q_in[GT][EPL];
-#pragma unroll
-  for (int h = 0; h < GT; ++h) {
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      q_in[h][e] = 0.0f;
-    }
-    if (h < tile_heads) {
-      const uint16_t* src = p.query + out_base + static_cast<size_t>(h) * D + lane * EPL;
-#pragma unroll
-      for (int e = 0; e < EPL; e += 2) {
-        const uint32_t w = *reinterpret_cast<const uint32_t*>(src + e);
-        q_in[h][e] = __uint_as_float(w << 16);
-        q_in[h][e + 1] = __uint_as_float(w & 0xffff0000u);
-      }
-    }
-  }
-
+  float q_in[GT][EPL];  // this lane's part of the tile's queries, loaded once the descriptors are read
   float acc[GT][EPL];
 #pragma unroll
   for (int h = 0; h < GT; ++h) {
@@ -357,12 +371,22 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     bulk_copy_plain(dst, p.key_pages + offset, L::kUnitBytes, bar);
     bulk_copy_plain(dst + L::kUnitBytes, p.value_pages + offset, L::kUnitBytes, bar);
     if constexpr (QUANT) {
-      bulk_copy_plain(dst + 2 * L::kUnitBytes, p.value_scales + (page_head * PS + sub * U) * DB, L::kVScaleBytes, bar);
+      bulk_copy_plain(vscales_addr + stage * L::kVScaleBytes, p.value_scales + (page_head * PS + sub * U) * DB,
+                      L::kVScaleBytes, bar);
     }
   };
 
   float inv_freq_lane[EPL / 2];
-  float q_cos[EPL / 2], q_sin[EPL / 2];  // rotation of the query when the keys come rotated
+  // Rotation of the query for the current unit, e^{i (a - P) theta} (for keys that come rotated:
+  // e^{i a theta}, fixed). A warp's units normally follow one another at a fixed distance, so the
+  // next rotation is the current one times a fixed e^{-i 16 step theta}; sincosf is called afresh
+  // whenever the distance differs and every kResync units, which keeps rounding from piling up.
+  constexpr int kResync = 32;
+  float rot_cos[EPL / 2], rot_sin[EPL / 2], step_cos[EPL / 2], step_sin[EPL / 2];
+  int rot_unit = 0, rot_age = kResync;
+  const int unit_step = S * warps;
+  // per-lane parts of the key and table addresses (see the logits loop)
+  const uint32_t flip_row = static_cast<uint32_t>(token_flip);
 
   int total_units = 0;
   for (int round = 0;; ++round) {
@@ -421,6 +445,9 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     const int in_round = max(0, min(CAP, mine - local_base));
 
     // ---- first copies of the round, then the per-block tables while they fly ----
+    if (round == 0 && p.early_descriptors) {
+      fk_w4a16::pdl_wait_for_prerequisites();
+    }
     if (lane == 0 && !failed) {
       for (int k = 0; k < stages; ++k) {
         const int entry_index = warp + k * warps;
@@ -430,22 +457,29 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
       }
     }
     if (round == 0) {
-      if constexpr (!ROT) {
-        // rope[(t * D/2 + pair) * 2 + {0, 1}] = cos, sin of t * theta_pair; lane l owns pairs
-        // l * EPL/2 ..., i.e. floats [t * D + l * EPL, + EPL)
-        for (int idx = tid; idx < U * (D / 2); idx += threads) {
-          const int t = idx / (D / 2);
-          const int pair = idx - t * (D / 2);
-          float sn, cs;
-          sincosf(static_cast<float>(t) * inv_freq_s[pair], &sn, &cs);
-          *reinterpret_cast<float2*>(&rope[idx * 2]) = make_float2(cs, sn);
+#pragma unroll
+      for (int h = 0; h < GT; ++h) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          q_in[h][e] = 0.0f;
+        }
+        if (h < tile_heads) {
+          const uint16_t* src = p.query + out_base + static_cast<size_t>(h) * D + lane * EPL;
+#pragma unroll
+          for (int e = 0; e < EPL; e += 2) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(src + e);
+            q_in[h][e] = __uint_as_float(w << 16);
+            q_in[h][e + 1] = __uint_as_float(w & 0xffff0000u);
+          }
         }
       }
 #pragma unroll
       for (int i = 0; i < EPL / 2; ++i) {
         inv_freq_lane[i] = inv_freq_s[lane * (EPL / 2) + i];
         if constexpr (ROT) {
-          sincosf(static_cast<float>(query_position) * inv_freq_lane[i], &q_sin[i], &q_cos[i]);
+          sincosf(static_cast<float>(query_position) * inv_freq_lane[i], &rot_sin[i], &rot_cos[i]);
+        } else {
+          sincosf(static_cast<float>(-U * unit_step) * inv_freq_lane[i], &step_sin[i], &step_cos[i]);
         }
       }
     }
@@ -476,29 +510,42 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
       const uint32_t v_stage = k_stage + L::kUnitBytes;
 
       // query of this unit: rotation by (a - P), key scale, softmax scale
+      if constexpr (!ROT) {
+        const bool follows = rot_age < kResync && logical_unit == rot_unit + unit_step;
+#pragma unroll
+        for (int pi = 0; pi < EPL / 2; ++pi) {
+          if (follows) {
+            const float c = rot_cos[pi], sn = rot_sin[pi];
+            rot_cos[pi] = c * step_cos[pi] - sn * step_sin[pi];
+            rot_sin[pi] = sn * step_cos[pi] + c * step_sin[pi];
+          } else {
+            const int delta = query_position - logical_unit * U;
+            sincosf(static_cast<float>(delta) * inv_freq_lane[pi], &rot_sin[pi], &rot_cos[pi]);
+          }
+        }
+        rot_age = follows ? rot_age + 1 : 0;
+        rot_unit = logical_unit;
+      }
       float q_rot[GT][EPL];
 #pragma unroll
       for (int pi = 0; pi < EPL / 2; ++pi) {
-        float cs, sn;
-        if constexpr (ROT) {
-          cs = q_cos[pi];
-          sn = q_sin[pi];
-        } else {
-          const int delta = query_position - logical_unit * U;
-          sincosf(static_cast<float>(delta) * inv_freq_lane[pi], &sn, &cs);
-        }
         float factor = p.scale_log2e;
         if constexpr (QUANT) {
           factor *= kscales[i * DB + lane_db];
         }
-        cs *= factor;
-        sn *= factor;
+        const float cs = rot_cos[pi] * factor;
+        const float sn = rot_sin[pi] * factor;
 #pragma unroll
         for (int h = 0; h < GT; ++h) {
           q_rot[h][2 * pi] = q_in[h][2 * pi] * cs - q_in[h][2 * pi + 1] * sn;
           q_rot[h][2 * pi + 1] = q_in[h][2 * pi] * sn + q_in[h][2 * pi + 1] * cs;
         }
       }
+      // Row t of the unit's keys sits at k_stage + t * row bytes, and k_stage is aligned to the 16
+      // rows, so "+" is "^" and the per-lane token permutation (t = tl ^ flip) becomes one XOR of
+      // a per-lane base with a compile-time constant. The same for the rotation table.
+      const uint32_t k_lane = (k_stage + lane * (EPL * EB)) ^ (flip_row * (D * EB));
+      const uint32_t rope_lane = (rope_addr + lane * (EPL * 4)) ^ (flip_row * (D * 4));
 
       // ---- logits: TB tokens x GT heads per butterfly round ----
       float logit[NR];
@@ -509,17 +556,18 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
           float vals[NV];
 #pragma unroll
           for (int tl = 0; tl < TB; ++tl) {
-            const int t = r * TB + (tl ^ token_flip);
             float kk[EPL];
-            load_elements<KV, EPL>(k_stage + t * (D * EB) + lane * (EPL * EB), kk);
+            load_elements<KV, EPL>(k_lane ^ static_cast<uint32_t>((r * TB + tl) * (D * EB)), kk);
             if constexpr (!ROT) {
               float cs_sn[EPL];
+              const uint32_t table = rope_lane ^ static_cast<uint32_t>((r * TB + tl) * (D * 4));
               if constexpr (EPL == 4) {
-                const float4 c4 = *reinterpret_cast<const float4*>(&rope[t * D + lane * EPL]);
-                cs_sn[0] = c4.x, cs_sn[1] = c4.y, cs_sn[2] = c4.z, cs_sn[3] = c4.w;
+                const uint4 c4 = lds128(table);
+                cs_sn[0] = __uint_as_float(c4.x), cs_sn[1] = __uint_as_float(c4.y);
+                cs_sn[2] = __uint_as_float(c4.z), cs_sn[3] = __uint_as_float(c4.w);
               } else {
-                const float2 c2 = *reinterpret_cast<const float2*>(&rope[t * D + lane * EPL]);
-                cs_sn[0] = c2.x, cs_sn[1] = c2.y;
+                const uint2 c2 = lds64(table);
+                cs_sn[0] = __uint_as_float(c2.x), cs_sn[1] = __uint_as_float(c2.y);
               }
 #pragma unroll
               for (int pi = 0; pi < EPL / 2; ++pi) {
@@ -565,8 +613,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
         if (holds_value && r * TB < tokens) {
           const int t = r * TB + my_token;
           if constexpr (QUANT) {
-            const float* vs = reinterpret_cast<const float*>(smem + layout.ring) +
-                              ((warp * stages + stage) * L::kStageBytes + 2 * L::kUnitBytes) / 4 + t * DB;
+            const float* vs = vscales + stage * (L::kVScaleBytes / 4) + t * DB;
 #pragma unroll
             for (int b = 0; b < DB; ++b) {
               probs[(t * DBQ + b) * GT + my_head] = prob * vs[b];
@@ -649,7 +696,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
   }
   __syncthreads();  // every warp is done with its ring: the merge area overlays it
-  float* merge = reinterpret_cast<float*>(smem + layout.ring);
+  float* merge = reinterpret_cast<float*>(ring_ptr);
   float* merge_m = merge;                     // [warps][GT]
   float* merge_l = merge + warps * GT;        // [warps][GT]
   float* merge_acc = merge + 2 * warps * GT;  // [warps][GT][D]

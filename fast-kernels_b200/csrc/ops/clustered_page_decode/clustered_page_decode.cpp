@@ -84,7 +84,7 @@ void clustered_page_decode_forward_hinted(
     int batch, int num_runs, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
     int group_tile, int use_clustered_kernel, int cluster_size, int kv_format,
     int keys_are_rotated, float softmax_scale, float rope_theta, int max_pages_hint,
-    std::uintptr_t stream_ptr) {
+    int early_descriptors, std::uintptr_t stream_ptr) {
   // the argument rules of the reference's launcher that have no counterpart in the C ABI
   // (clustered_page_decode.cu:1110-1115 there)
   if (cluster_size < 1 || cluster_size > 8) {
@@ -120,6 +120,7 @@ void clustered_page_decode_forward_hinted(
   args.softmax_scale = softmax_scale;
   args.rope_theta = rope_theta;
   args.stream = as<void>(stream_ptr);
+  args.flags = early_descriptors != 0 ? FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS : 0;
   if (args.splits != 1 && batch > 0 && num_q_heads > 0 && num_kv_heads > 0 && (head_dim == 64 || head_dim == 128)) {
     args.workspace_bytes = fk_page_decode_workspace_bytes(batch, num_q_heads, num_kv_heads, head_dim);
     args.workspace = workspace_for(args.workspace_bytes, reinterpret_cast<cudaStream_t>(stream_ptr));
@@ -141,7 +142,7 @@ void clustered_page_decode_forward(
                                        run_last_page_lens_ptr, request_run_offsets_ptr, seq_lens_ptr, output_ptr,
                                        batch, num_runs, num_q_heads, num_kv_heads, head_dim, page_size, group_tile,
                                        use_clustered_kernel, cluster_size, kv_format, keys_are_rotated,
-                                       softmax_scale, rope_theta, /*max_pages_hint=*/0, stream_ptr);
+                                       softmax_scale, rope_theta, /*max_pages_hint=*/0, /*early_descriptors=*/0, stream_ptr);
 }
 
 int page_decode_device_status() {

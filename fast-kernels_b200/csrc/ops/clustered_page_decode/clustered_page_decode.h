@@ -34,7 +34,9 @@ void clustered_page_decode_forward(
     int keys_are_rotated, float softmax_scale, float rope_theta, std::uintptr_t stream_ptr);
 
 // Additions of this build: the same call with the longest request's page count as a hint (it
-// keeps short requests from being cut into empty pieces), and the device status word.
+// keeps short requests from being cut into empty pieces) and with the caller's word that the
+// kernel before this one in the stream does not write the descriptor arrays (they may then be
+// read while that kernel drains); and the device status word.
 void clustered_page_decode_forward_hinted(
     std::uintptr_t query_ptr, std::uintptr_t key_ptr, std::uintptr_t value_ptr,
     std::uintptr_t key_scales_ptr, std::uintptr_t value_scales_ptr,
@@ -44,7 +46,7 @@ void clustered_page_decode_forward_hinted(
     int batch, int num_runs, int num_q_heads, int num_kv_heads, int head_dim, int page_size,
     int group_tile, int use_clustered_kernel, int cluster_size, int kv_format,
     int keys_are_rotated, float softmax_scale, float rope_theta, int max_pages_hint,
-    std::uintptr_t stream_ptr);
+    int early_descriptors, std::uintptr_t stream_ptr);
 int page_decode_device_status();
 
 }  // namespace fast_kernels::clustered_page_decode

@@ -16,7 +16,7 @@ void clustered_page_decode_forward(ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, 
   unavailable();
 }
 void clustered_page_decode_forward_hinted(ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, int, int, int, int,
-                                          int, int, int, int, int, int, int, float, float, int, ptr) {
+                                          int, int, int, int, int, int, int, float, float, int, int, ptr) {
   unavailable();
 }
 int page_decode_device_status() { unavailable(); }

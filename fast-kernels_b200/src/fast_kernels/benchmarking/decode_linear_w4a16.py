@@ -64,6 +64,18 @@ def _explicit_reference(torch: Any, act: Any, q_u8: Any, alpha: Any, beta: Any, 
     return (act.float() @ weight.t()).to(act.dtype)
 
 
+_CAPTURE_STREAMS: dict[int, Any] = {}
+
+
+def _capture_stream(torch: Any) -> Any:
+    """One capturing stream per device for the whole run: the ops keep a scratch buffer per
+    (device, stream), so a fresh stream per measurement would leave one buffer behind each time."""
+    device = torch.cuda.current_device()
+    if device not in _CAPTURE_STREAMS:
+        _CAPTURE_STREAMS[device] = torch.cuda.Stream()
+    return _CAPTURE_STREAMS[device]
+
+
 def _time_device(torch: Any, calls: list[Callable[[], Any]], iters: int) -> list[float]:
     """Device time per call in microseconds, one sample per replay of a CUDA graph that holds one
     launch per entry of ``calls`` (distinct weight copies), so that host launch overhead is not in
@@ -73,8 +85,13 @@ def _time_device(torch: Any, calls: list[Callable[[], Any]], iters: int) -> list
     torch.cuda.synchronize()
     try:
         graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
+        side = _capture_stream(torch)
         side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            # the ops keep their scratch per (device, stream) and allocate it on a stream's first
+            # call, which must not happen under capture: make that call on the capturing stream
+            calls[0]()
+        side.synchronize()
         with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
             for fn in calls:
                 fn()

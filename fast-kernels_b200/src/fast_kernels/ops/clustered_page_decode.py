@@ -587,6 +587,7 @@ def clustered_page_decode(
         max(2, plan.cluster_size) if not direct else 1,
         _layout_id(cache.kv_layout), int(cache.keys_are_rotated), float(scale), float(rope_theta),
         int(torch.cuda.current_stream(device=query.device).cuda_stream), max_pages_hint=plan.max_pages,
+        early_descriptors=1,  # the descriptors were uploaded from the host when the plan was made
     )
     return output
 

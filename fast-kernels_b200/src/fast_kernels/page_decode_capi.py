@@ -20,6 +20,7 @@ ERR_CUDA = -2
 KV_BF16 = 0
 KV_FP8_E4M3 = 1
 KV_INT8 = 2
+FLAG_EARLY_DESCRIPTORS = 1
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfk_page_decode.so"
 
@@ -60,6 +61,7 @@ class PageDecodeArgs(ctypes.Structure):
         ("softmax_scale", ctypes.c_float),
         ("rope_theta", ctypes.c_float),
         ("stream", _c_void_p),
+        ("flags", _c_int),
     ]
 
 

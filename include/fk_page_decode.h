@@ -54,6 +54,14 @@ extern "C" {
 #define FK_PAGE_DECODE_KV_FP8_E4M3 1
 #define FK_PAGE_DECODE_KV_INT8 2
 
+/* The kernel is launched with programmatic stream serialisation: it may be scheduled while the
+ * kernel before it in the stream is still draining, and waits for that kernel's completion before
+ * it touches global memory. With this flag the caller states that the preceding kernel does not
+ * write the request descriptors (the run arrays, request_run_offsets, seq_lens) -- the usual case,
+ * they come from the host -- and the kernel reads and sorts them before it waits. Queries, pages,
+ * scales and outputs are never touched early. */
+#define FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS 1
+
 typedef struct fk_page_decode_args {
   const void* query;
   const void* key_pages;
@@ -94,6 +102,8 @@ typedef struct fk_page_decode_args {
   float softmax_scale;
   float rope_theta;
   void* stream;
+  /* FK_PAGE_DECODE_FLAG_* bits, 0 = none. */
+  int32_t flags;
 } fk_page_decode_args;
 
 FK_PAGE_DECODE_API const char* fk_page_decode_last_error(void);

@@ -59,7 +59,8 @@ class DeviceCase:
         self.rope_theta = float(rope_theta)
         self.workspace = None
 
-    def args(self, pdc: Any, output: Any, *, splits: int = 0, group_tile: int = 0, max_pages_hint: int = 0) -> Any:
+    def args(self, pdc: Any, output: Any, *, splits: int = 0, group_tile: int = 0, max_pages_hint: int = 0,
+             flags: int = 0) -> Any:
         torch = self.torch
         lib = pdc.load_library()
         if self.workspace is None:
@@ -91,6 +92,7 @@ class DeviceCase:
         a.keys_are_rotated = int(self.keys_are_rotated)
         a.splits = splits
         a.max_pages_hint = max_pages_hint
+        a.flags = flags
         a.softmax_scale = self.softmax_scale
         a.rope_theta = self.rope_theta
         a.stream = int(torch.cuda.current_stream().cuda_stream)

@@ -284,6 +284,24 @@ def test_call_recorded_into_a_cuda_graph_replays() -> None:
     _status_ok()
 
 
+def test_early_descriptor_reads_give_the_same_bits_in_a_busy_stream() -> None:
+    """With FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS the kernel sorts the request's runs before it waits
+    for the kernel ahead of it in the stream; queries, pages and outputs are still read after the
+    wait. Here the kernel ahead WRITES the query (a copy from a staging buffer) and the call before
+    that used the same workspace, several times in a row: every result must equal the plain one."""
+    query, cache, plan = _random_problem(batch=4, q_heads=16, kv_heads=4, head_dim=128, page_size=16,
+                                         lens=[900, 640, 17, 1024], layout="bf16_kv", rotated=False, seed=5)
+    dev = _device_case(query, cache, plan)
+    plain = dev.forward(pdc)
+    staged = dev.query.clone()
+    for _ in range(6):
+        dev.query.zero_()
+        dev.query.copy_(staged)  # a kernel that writes the query, right ahead of the decode
+        out = dev.forward(pdc, flags=pdc.FLAG_EARLY_DESCRIPTORS)
+        assert torch.equal(out.view(torch.int16), plain.view(torch.int16))
+    _status_ok()
+
+
 def test_group_tile_and_launch_overrides_keep_the_result() -> None:
     query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
                                          lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)

@@ -208,7 +208,7 @@ def test_argument_errors_come_before_any_launch() -> None:
         (dict(num_q_heads=7), "divisible by num_kv_heads"), (dict(group_tile=3), "group_tile must be one of"),
         (dict(kv_format=5), "unsupported kv_format"), (dict(kv_format=2), "need key_scales and value_scales"),
         (dict(splits=65), "splits must be in"), (dict(query=4100), "16-byte aligned"), (dict(output=0), "must not be NULL"),
-        (dict(rope_theta=0.0), "rope_theta positive"),
+        (dict(rope_theta=0.0), "rope_theta positive"), (dict(flags=6), "unknown bits in flags"),
     ]:
         code, text = call(**changes)
         assert code == pdc.ERR_INVALID_ARGUMENT and message in text, (changes, text)
