@@ -121,6 +121,7 @@ def build_python_module_without_cuda(out_dir: Path) -> Path:
             CSRC / "bindings" / "python_module.cpp",
             CSRC / "ops" / "decode_quant_linear" / "arc_w4a16_nocuda.cpp",
             CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode_nocuda.cpp",
+            CSRC / "ops" / "prefix_union_decode" / "prefix_union_decode.cpp",
         ]
     )
     return target
@@ -134,6 +135,7 @@ def build_python_module(force: bool = False) -> Path:
         CSRC / "bindings" / "python_module.cpp",
         CSRC / "ops" / "decode_quant_linear" / "arc_w4a16.cpp",
         CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode.cpp",
+        CSRC / "ops" / "prefix_union_decode" / "prefix_union_decode.cpp",
     ]
     deps = sources + [CSRC / "ops" / "decode_quant_linear" / "arc_w4a16.h", REPO / "include" / "fk_w4a16.h",
                       CSRC / "ops" / "clustered_page_decode" / "clustered_page_decode.h",

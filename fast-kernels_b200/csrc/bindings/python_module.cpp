@@ -13,6 +13,7 @@
 
 #include "ops/clustered_page_decode/clustered_page_decode.h"
 #include "ops/decode_quant_linear/arc_w4a16.h"
+#include "ops/prefix_union_decode/prefix_union_decode.h"
 
 #ifndef FK_COMPILED_WITH_CUDA
 #define FK_COMPILED_WITH_CUDA 1
@@ -306,6 +307,26 @@ PYBIND11_MODULE(_native, m) {
       py::arg("page_size"), py::arg("group_tile"), py::arg("use_clustered_kernel"), py::arg("cluster_size"),
       py::arg("kv_format"), py::arg("keys_are_rotated"), py::arg("softmax_scale"), py::arg("rope_theta"),
       py::arg("stream_ptr"), py::arg("max_pages_hint") = 0, py::arg("early_descriptors") = 0);
+  m.def(
+      "prefix_union_decode_forward",
+      [](ptr_t query_ptr, ptr_t key_ptr, ptr_t value_ptr, ptr_t key_scales_ptr, ptr_t value_scales_ptr,
+         ptr_t tasks_ptr, ptr_t shared_pages_ptr, ptr_t tail_pages_ptr, ptr_t consumers_ptr,
+         ptr_t scheduler_counter_ptr, ptr_t output_ptr, int num_tasks, int num_pages, int num_q_heads,
+         int num_kv_heads, int head_dim, int page_size, int cluster_size, int kv_format, int keys_are_rotated,
+         float softmax_scale, float rope_theta, ptr_t stream_ptr) {
+        py::gil_scoped_release release;
+        fast_kernels::prefix_union_decode::prefix_union_decode_forward(
+            query_ptr, key_ptr, value_ptr, key_scales_ptr, value_scales_ptr, tasks_ptr, shared_pages_ptr,
+            tail_pages_ptr, consumers_ptr, scheduler_counter_ptr, output_ptr, num_tasks, num_pages, num_q_heads,
+            num_kv_heads, head_dim, page_size, cluster_size, kv_format, keys_are_rotated, softmax_scale, rope_theta,
+            stream_ptr);
+      },
+      py::arg("query_ptr"), py::arg("key_ptr"), py::arg("value_ptr"), py::arg("key_scales_ptr"),
+      py::arg("value_scales_ptr"), py::arg("tasks_ptr"), py::arg("shared_pages_ptr"), py::arg("tail_pages_ptr"),
+      py::arg("consumers_ptr"), py::arg("scheduler_counter_ptr"), py::arg("output_ptr"), py::arg("num_tasks"),
+      py::arg("num_pages"), py::arg("num_q_heads"), py::arg("num_kv_heads"), py::arg("head_dim"),
+      py::arg("page_size"), py::arg("cluster_size"), py::arg("kv_format"), py::arg("keys_are_rotated"),
+      py::arg("softmax_scale"), py::arg("rope_theta"), py::arg("stream_ptr"));
   m.def("page_decode_device_status", []() {
     py::gil_scoped_release release;
     return fast_kernels::clustered_page_decode::page_decode_device_status();

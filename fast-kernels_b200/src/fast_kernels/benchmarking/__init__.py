@@ -70,7 +70,7 @@ def _execute(suite: BenchmarkSuite) -> tuple[list[BenchmarkCase], list[str]]:
         from fast_kernels.benchmarking.decode_linear_w4a16 import run_decode_linear_w4a16_suite
 
         return run_decode_linear_w4a16_suite(suite)
-    if suite.family == "clustered_page_decode":
+    if suite.family in ("clustered_page_decode", "prefix_union_decode"):
         from fast_kernels.benchmarking.clustered_page_decode import run_clustered_page_decode_suite
 
         return run_clustered_page_decode_suite(suite)

@@ -1,4 +1,5 @@
-"""Runner for suites of the ``clustered_page_decode`` family (what ``fk bench`` executes for them).
+"""Runner for suites of the ``clustered_page_decode`` and ``prefix_union_decode`` families (what
+``fk bench`` executes for them).
 
 Same flow as the reference's runner for this family
 (src/fast_kernels/benchmarking/clustered_page_decode.py there): per layout x shape it draws seeded
@@ -10,6 +11,13 @@ is the PyTorch statement of the op; ``vendor/flashinfer_clustered_page_decode`` 
 skipped (that library's paged decode takes another cache layout and applies no rotary embedding,
 and nothing here converts for it). Latencies are CUDA-event device times over CUDA-graph replays
 that cycle through enough copies of the pages to exceed L2. Without a GPU every case is skipped.
+
+``prefix_union_decode`` suites (the reference's runner: src/fast_kernels/benchmarking/prefix_union_decode.py
+there) use the same flow with the shared-prefix recipe: groups of ``prefix_group_size`` requests
+repeat their leader's first ``shared_prefix_pages`` pages, identical pages are stored once, keys
+are rotated ahead of time. ``decode/prefix_union_decode_{auto,fallback}`` are the op with that
+``force_impl``; ``decode/prefix_union_decode_union`` is skipped with the reference's own reason (its
+union kernel needs compute capability 12).
 """
 
 from __future__ import annotations
@@ -27,6 +35,9 @@ FORCE_IMPL = {
     "decode/clustered_page_decode_auto": "auto",
     "decode/clustered_page_decode_direct": "direct",
     "decode/clustered_page_decode_clustered": "clustered",
+    "decode/prefix_union_decode_auto": "auto",
+    "decode/prefix_union_decode_union": "union",
+    "decode/prefix_union_decode_fallback": "fallback",
 }
 
 
@@ -52,6 +63,8 @@ def run_clustered_page_decode_suite(suite: BenchmarkSuite) -> tuple[list[Benchma
     from fast_kernels.benchmarking.decode_linear_w4a16 import _time_device
 
     ops = importlib.import_module("fast_kernels.ops.clustered_page_decode")
+    union = importlib.import_module("fast_kernels.ops.prefix_union_decode")
+    shared_prefixes = suite.family == "prefix_union_decode"
     try:
         import torch
     except ImportError:
@@ -89,15 +102,29 @@ def run_clustered_page_decode_suite(suite: BenchmarkSuite) -> tuple[list[Benchma
                         emit(kind, subject, dtype_name, layout, shape, status="skipped", reason=f"{exc}")
                     continue
                 batch = int(shape.batch)
-                torch.manual_seed(batch + q_heads + kv_heads + dim + max_len + page)
+                shared_pages, group = int(extra.get("shared_prefix_pages", 0)), int(extra.get("prefix_group_size", 1))
+                torch.manual_seed(batch + q_heads + kv_heads + dim + max_len + page + shared_pages + group * shared_prefixes)
                 query = torch.randn((batch, q_heads, dim), device=device).to(torch.bfloat16)
                 keys = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
                 values = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
-                lens = torch.randint(max(page, max_len - page + 1), max_len + 1, (batch,), dtype=torch.int32)
-                cache = builders[layout](keys, values, lens, page_size=page, fragment_pages=True, seed=1)
-                plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens,
-                                                      num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim,
-                                                      page_size=page, kv_layout=layout)
+                if shared_prefixes:
+                    shared_tokens = shared_pages * page
+                    lens = torch.randint(max(page, shared_tokens + 1), max_len + 1, (batch,), dtype=torch.int32)
+                    for start in range(0, batch, max(1, group)):
+                        keys[start + 1 : start + group, :, :shared_tokens] = keys[start, :, :shared_tokens]
+                        values[start + 1 : start + group, :, :shared_tokens] = values[start, :, :shared_tokens]
+                    cache = builders[layout](keys, values, lens, page_size=page, fragment_pages=True, seed=3,
+                                             key_rope_theta=10000.0, deduplicate_identical_pages=True)
+                    union_plan = union.plan_prefix_union_decode(
+                        page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads,
+                        num_kv_heads=kv_heads, head_dim=dim, page_size=page, kv_layout=layout, keys_are_rotated=True)
+                    plan = union_plan.fallback_plan
+                else:
+                    lens = torch.randint(max(page, max_len - page + 1), max_len + 1, (batch,), dtype=torch.int32)
+                    cache = builders[layout](keys, values, lens, page_size=page, fragment_pages=True, seed=1)
+                    plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens,
+                                                          num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim,
+                                                          page_size=page, kv_layout=layout)
                 expected = ops.reference_clustered_page_decode(query, cache)
                 tokens = int(lens.sum())
                 element = 2 if layout == "bf16_kv" else 1
@@ -131,8 +158,17 @@ def run_clustered_page_decode_suite(suite: BenchmarkSuite) -> tuple[list[Benchma
                                 emit(kind, subject, dtype_name, layout, shape, status="skipped",
                                      reason='force_impl="direct" only supports group_size <= 8')
                                 continue
-                            calls = [(lambda c=c: ops.clustered_page_decode(query, c, plan=plan, output=out,
-                                                                            force_impl=impl)) for c in caches]
+                            if impl == "union":
+                                emit(kind, subject, dtype_name, layout, shape, status="skipped",
+                                     reason="prefix_union_decode requires a Blackwell-class GPU for union mode "
+                                            "(compute capability 12, the reference's rule)")
+                                continue
+                            if shared_prefixes:
+                                calls = [(lambda c=c: union.prefix_union_decode(query, c, plan=union_plan, output=out,
+                                                                                force_impl=impl)) for c in caches]
+                            else:
+                                calls = [(lambda c=c: ops.clustered_page_decode(query, c, plan=plan, output=out,
+                                                                                force_impl=impl)) for c in caches]
                         else:
                             calls = [lambda: ops.reference_clustered_page_decode(query, cache, output=out)]
                         out.fill_(float("nan"))
@@ -155,7 +191,9 @@ def run_clustered_page_decode_suite(suite: BenchmarkSuite) -> tuple[list[Benchma
                         "throughput": batch * 1e6 / dev_med, "decode_tokens_per_second": batch * 1e6 / dev_med,
                         "metrics": {"hbm_gbs": gbs, "hbm_frac_of_measured_peak": gbs / peak,
                                     "algorithmic_bytes": float(bytes_moved), "max_abs_err": max_err,
-                                    "context_tokens": float(tokens), **ops.estimate_page_decode_metrics(cache, plan)},
+                                    "context_tokens": float(tokens),
+                                    **(union.estimate_prefix_union_decode_metrics(cache, union_plan) if shared_prefixes
+                                       else ops.estimate_page_decode_metrics(cache, plan))},
                     }))
                 for kind, subject, fields in pending:
                     if kind == "kernel":

@@ -45,6 +45,12 @@ def kernel_registry() -> dict[str, KernelSpec]:
                    "the same kernel, one block per (request, kv head, head tile); force_impl=direct", "beta", "direct"),
         KernelSpec("decode/clustered_page_decode_clustered", "clustered_page_decode",
                    "the same kernel, pages cut over as many blocks as fill the device; force_impl=clustered", "beta", "clustered"),
+        KernelSpec("decode/prefix_union_decode_auto", "prefix_union_decode",
+                   "shared-prefix paged decode; below compute capability 12 the plan's fallback (the paged-KV decode kernel)", "beta", "auto"),
+        KernelSpec("decode/prefix_union_decode_union", "prefix_union_decode",
+                   "registered as in the reference; its union kernel needs compute capability 12, reported as skipped", "scaffold", "union"),
+        KernelSpec("decode/prefix_union_decode_fallback", "prefix_union_decode",
+                   "shared-prefix paged decode through the paged-KV decode kernel", "beta", "fallback"),
         KernelSpec("template/noop_gemm", "gemm", "scaffold entry used by the template suite", "scaffold", None),
     ]
     return {spec.kernel_id: spec for spec in specs}
@@ -60,6 +66,8 @@ def baseline_registry() -> dict[str, BaselineSpec]:
                      "dense gather through the page table, rotary embedding, softmax attention in PyTorch"),
         BaselineSpec("vendor/flashinfer_clustered_page_decode", "vendor", "clustered_page_decode",
                      "registered as in the reference; reported as skipped (no cache-layout converter here)"),
+        BaselineSpec("torch/reference_prefix_union_decode", "torch", "prefix_union_decode",
+                     "the PyTorch statement of the paged decode (sharing pages does not change the mathematics)"),
         BaselineSpec("torch/reference_gemm", "torch", "gemm", "scaffold baseline of the template suite"),
         BaselineSpec("vendor/cublaslt_gemm", "vendor", "gemm", "scaffold baseline of the template suite"),
     ]

@@ -13,6 +13,9 @@ not.
 
     python tests/golden/make_page_decode_golden.py --reference <path of the reference checkout>
 
+Also writes tests/golden/prefix_union_*.npz: page tables with shared prefixes and the four
+descriptor tables the reference's `plan_prefix_union_decode` makes of them.
+
 Cases: the shapes of the reference's GPU tests scaled to CPU-friendly sizes, each layout, keys
 rotated ahead of time or not, both page sizes and head dims, fragmented and contiguous page
 tables, de-duplicated pages.
@@ -44,6 +47,18 @@ CASES = [
     ("int8_d128_p32_g32_rot", "int8_kv", 2, 32, 1, 128, 160, 32, 10000.0, True, False),
     ("bf16_d128_p16_g2_contig", "bf16_kv", 3, 4, 2, 128, 100, 16, None, False, False),
     ("int8_d64_p32_g2_dedup", "int8_kv", 3, 4, 2, 64, 96, 32, None, True, True),
+]
+
+
+# Shared-prefix cases for the planner of prefix_union_decode (the reference's
+# tests/gpu/test_prefix_union_decode.py:48-98 recipe: the requests of a group repeat their leader's
+# first pages, pages are de-duplicated and fragmented with seed 3, keys rotated ahead of time):
+# name, batch, q_heads, kv_heads, head_dim, max_seq_len, page_size, shared_prefix_pages, prefix_group_size, layout
+PREFIX_CASES = [
+    ("gqa4_prefix4", 8, 8, 2, 64, 160, 16, 4, 4, "bf16_kv"),
+    ("mqa8_prefix3_odd_groups", 7, 8, 1, 64, 200, 32, 3, 3, "int8_kv"),
+    ("gqa2_prefix2_pairs", 6, 4, 2, 64, 96, 16, 2, 2, "fp8_kv"),
+    ("no_sharing", 3, 4, 2, 64, 80, 16, 0, 1, "bf16_kv"),
 ]
 
 
@@ -126,6 +141,44 @@ def main() -> int:
         })
         print(name, "pages", cache.total_pages, "runs", plan.num_runs)
     (HERE / "page_decode_manifest.json").write_text(json.dumps(manifest, indent=1) + "\n")
+
+    import importlib  # noqa: PLC0415
+
+    union = importlib.import_module("fast_kernels.ops.prefix_union_decode")
+    prefix_manifest = []
+    for name, batch, q_heads, kv_heads, head_dim, max_seq, page, shared_pages, group, layout in PREFIX_CASES:
+        torch.manual_seed(batch + q_heads + kv_heads + head_dim + max_seq + page + shared_pages + group)
+        shared_tokens = shared_pages * page
+        keys = torch.randn((batch, kv_heads, max_seq, head_dim)).to(torch.bfloat16)
+        values = torch.randn((batch, kv_heads, max_seq, head_dim)).to(torch.bfloat16)
+        seq_lens = torch.randint(low=max(page, shared_tokens + 1), high=max_seq + 1, size=(batch,), dtype=torch.int32)
+        for start in range(0, batch, group):
+            for follower in range(start + 1, min(batch, start + group)):
+                keys[follower, :, :shared_tokens] = keys[start, :, :shared_tokens]
+                values[follower, :, :shared_tokens] = values[start, :, :shared_tokens]
+        build = {"bf16_kv": ops.pack_paged_kv_bf16, "int8_kv": ops.quantize_paged_kv_int8,
+                 "fp8_kv": ops.quantize_paged_kv_fp8}[layout]
+        cache = build(keys, values, seq_lens, page_size=page, fragment_pages=True, seed=3, key_rope_theta=10000.0,
+                      deduplicate_identical_pages=True)
+        plan = union.plan_prefix_union_decode(
+            page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads, num_kv_heads=kv_heads,
+            head_dim=head_dim, page_size=page, kv_layout=layout, keys_are_rotated=True, use_cache=False)
+        np.savez_compressed(
+            HERE / f"prefix_union_{name}.npz", page_table=cache.page_table.numpy().copy(),
+            seq_lens=seq_lens.numpy().copy(), tasks=plan.tasks_cpu.numpy().copy(),
+            shared_pages=plan.shared_pages_cpu.numpy().copy(), tail_pages=plan.tail_pages_cpu.numpy().copy(),
+            consumers=plan.consumers_cpu.numpy().copy(),
+            fallback_run_base_pages=plan.fallback_plan.run_base_pages_cpu.numpy().copy())
+        prefix_manifest.append({
+            "name": name, "batch": batch, "num_q_heads": q_heads, "num_kv_heads": kv_heads, "head_dim": head_dim,
+            "max_seq_len": max_seq, "page_size": page, "shared_prefix_pages": shared_pages,
+            "prefix_group_size": group, "layout": layout, "total_pages": cache.total_pages,
+            "launch_mode": plan.launch_mode, "cluster_size": plan.cluster_size,
+            "estimated_saved_hbm_bytes": plan.estimated_saved_hbm_bytes, "num_tasks": plan.num_tasks,
+            "metrics": union.estimate_prefix_union_decode_metrics(cache, plan),
+        })
+        print(name, "tasks", plan.num_tasks, "saved", plan.estimated_saved_hbm_bytes, "pages", cache.total_pages)
+    (HERE / "prefix_union_manifest.json").write_text(json.dumps(prefix_manifest, indent=1) + "\n")
     return 0
 
 

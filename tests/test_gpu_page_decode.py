@@ -334,6 +334,48 @@ def test_workspace_that_is_too_small_is_refused() -> None:
     _status_ok()
 
 
+# ---- shared prefixes: the reference's prefix_union_decode op ------------------------------------------
+@pytest.mark.parametrize("layout", ["bf16_kv", "fp8_kv", "int8_kv"])
+def test_prefix_union_op_on_requests_that_share_pages(layout) -> None:
+    """The recipe of the reference's tests (tests/gpu/test_prefix_union_decode.py:48-98 there): groups
+    of four requests repeat their leader's first pages, identical pages are stored once, keys are
+    rotated ahead of time. On a device below compute capability 12 the reference computes the op
+    through its fallback plan and refuses force_impl="union"; so does this build."""
+    union = importlib.import_module("fast_kernels.ops.prefix_union_decode")
+    batch, q_heads, kv_heads, dim, max_len, page, shared_pages, group = 8, 32, 8, 128, 512, 16, 4, 4
+    torch.manual_seed(batch + q_heads + kv_heads + dim + max_len + page + shared_pages + group)
+    query = torch.randn((batch, q_heads, dim), device="cuda").to(torch.bfloat16)
+    keys = torch.randn((batch, kv_heads, max_len, dim), device="cuda").to(torch.bfloat16)
+    values = torch.randn((batch, kv_heads, max_len, dim), device="cuda").to(torch.bfloat16)
+    lens = torch.randint(shared_pages * page + 1, max_len + 1, (batch,), dtype=torch.int32)
+    for start in range(0, batch, group):
+        keys[start + 1 : start + group, :, : shared_pages * page] = keys[start, :, : shared_pages * page]
+        values[start + 1 : start + group, :, : shared_pages * page] = values[start, :, : shared_pages * page]
+    build = {"bf16_kv": ops.pack_paged_kv_bf16, "int8_kv": ops.quantize_paged_kv_int8,
+             "fp8_kv": ops.quantize_paged_kv_fp8}[layout]
+    cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=3, key_rope_theta=10000.0,
+                  deduplicate_identical_pages=True)
+    assert cache.total_pages < int(((lens + page - 1) // page).sum())  # shared pages are stored once
+    plan = union.plan_prefix_union_decode(page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads,
+                                          num_kv_heads=kv_heads, head_dim=dim, page_size=page, kv_layout=layout,
+                                          keys_are_rotated=True)
+    assert plan.launch_mode == "fallback" and plan.estimated_saved_hbm_bytes > 0
+    assert int(plan.tasks_cpu[:, 1].max()) == shared_pages
+    actual = union.prefix_union_decode(query, cache, plan=plan)
+    expected = union.reference_prefix_union_decode(query, cache)
+    torch.testing.assert_close(actual, expected, atol=1.25e-1, rtol=3e-2)
+    cpu_cache = _cache_to(cache, "cpu")
+    want = _device_case(query.cpu(), cpu_cache, plan.fallback_plan).oracle(oracle)
+    _assert_close_to_oracle(actual, want, layout)
+    assert torch.equal(union.prefix_union_decode(query, cache, force_impl="fallback").view(torch.int16),
+                       actual.view(torch.int16))
+    with pytest.raises(RuntimeError, match="Blackwell-class GPU for union mode"):
+        union.prefix_union_decode(query, cache, plan=plan, force_impl="union")
+    with pytest.raises(ValueError, match="force_impl must be one of"):
+        union.prefix_union_decode(query, cache, plan=plan, force_impl="clustered")
+    _status_ok()
+
+
 # ---- beside the reference's own CUDA kernels ----------------------------------------------------------
 @pytest.mark.skipif(not refgpu.available(), reason="oracle/_ref/libfk_reference_page_decode.so is not built")
 @pytest.mark.parametrize(("layout", "clustered", "cluster_size", "rotated", "shape"), [

@@ -75,6 +75,18 @@ def test_page_decode_suite_keeps_the_reference_contract_and_benches(tmp_path: Pa
     assert {case.status for case in bundle.cases} <= {"ok", "skipped", "failed"}
 
 
+def test_prefix_union_suite_keeps_the_reference_contract(tmp_path: Path) -> None:
+    suite = load_suite(SUITES / "prefix_union_decode.toml")
+    assert suite.family == "prefix_union_decode" and suite.kernels.ids == [
+        "decode/prefix_union_decode_auto", "decode/prefix_union_decode_union", "decode/prefix_union_decode_fallback"]
+    assert suite.baselines.ids == ["torch/reference_prefix_union_decode"]
+    assert [s.name for s in suite.shapes] == ["gqa4_prefix4_page16", "gqa4_prefix8_page16", "mqa8_prefix8_page32",
+                                              "gqa2_prefix4_page32_h64"]
+    assert suite.shapes[1].dimensions()["shared_prefix_pages"] == 8
+    bundle = load_result_bundle(benchmark_suite(SUITES / "prefix_union_decode.toml", tmp_path))
+    assert len(bundle.cases) == (3 + 1) * 1 * 3 * 4 and {case.status for case in bundle.cases} <= {"ok", "skipped", "failed"}
+
+
 def test_cli_env_and_template_bench(tmp_path: Path, capsys: pytest.CaptureFixture[str]) -> None:
     assert fk_main(["env", "--json"]) == 0
     payload = json.loads(capsys.readouterr().out)

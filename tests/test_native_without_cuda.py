@@ -21,7 +21,7 @@ REFERENCE_OPS = [
     "pack_arc_w4a16_packets", "compute_arc_w4a16_group_sums", "arc_w4a16_forward",
     "arc_w4a16_forward_split_k", "reduce_arc_w4a16_split_k_partials", "dequant_w4a16_to_fp16",
     "dequant_arc_w4a16_packets_to_fp16", "cublaslt_fp16_with_weight",
-    "cublaslt_fp16_after_packet_dequant", "cublaslt_fp16_after_dequant", "clustered_page_decode_forward",
+    "cublaslt_fp16_after_packet_dequant", "cublaslt_fp16_after_dequant", "clustered_page_decode_forward", "prefix_union_decode_forward",
 ]
 
 CHILD = r"""
