@@ -4,10 +4,12 @@ workload to put under a profiler
 (``ncu -k regex:page_decode ... python run_page_decode.py 16 32 8 128 16 4096 bf16_kv 3``).
 
     run_page_decode.py BATCH Q_HEADS KV_HEADS HEAD_DIM PAGE_SIZE MAX_LEN bf16_kv|fp8_kv|int8_kv LAUNCHES [WARPS STAGES [SPLITS]]
+                       [--shared-prefix TOKENS]
 
 Sequence lengths are drawn within one page of MAX_LEN, the page table is fragmented by a seeded
 permutation. The optional numbers override the launch plan (fk_page_decode_set_launch_config and
-the `splits` argument). Prints the launch plan, the time per launch (CUDA events around the whole
+the `splits` argument). With --shared-prefix every request repeats the first request's first TOKENS
+tokens and identical pages are stored once (a prompt prefix shared through the page table). Prints the launch plan, the time per launch (CUDA events around the whole
 burst, so launch overhead is in it) and the device status word.
 """
 
@@ -26,6 +28,11 @@ from fast_kernels import page_decode_capi as pdc  # noqa: E402
 
 
 def main() -> int:
+    shared_tokens = 0
+    if "--shared-prefix" in sys.argv:
+        at = sys.argv.index("--shared-prefix")
+        shared_tokens = int(sys.argv[at + 1])
+        del sys.argv[at : at + 2]
     if len(sys.argv) < 9:
         print(__doc__)
         return 2
@@ -44,7 +51,11 @@ def main() -> int:
     values = torch.randn((batch, kv_heads, max_len, dim), device="cuda").to(torch.bfloat16)
     build = {"bf16_kv": ops.pack_paged_kv_bf16, "fp8_kv": ops.quantize_paged_kv_fp8,
              "int8_kv": ops.quantize_paged_kv_int8}[layout]
-    cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1)
+    if shared_tokens > 0:
+        keys[1:, :, :shared_tokens] = keys[0, :, :shared_tokens]
+        values[1:, :, :shared_tokens] = values[0, :, :shared_tokens]
+    cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1,
+                  deduplicate_identical_pages=shared_tokens > 0)
     del keys, values
     plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads,
                                           num_kv_heads=kv_heads, head_dim=dim, page_size=page, kv_layout=layout,
@@ -75,7 +86,7 @@ def main() -> int:
     stop.record()
     torch.cuda.synchronize()
     tokens = int(lens.sum())
-    print("plan", pdc.describe_plan(a))
+    print("plan", pdc.describe_plan(a), "physical pages", cache.total_pages)
     print(f"context tokens {tokens}, {start.elapsed_time(stop) * 1e3 / max(1, launches):.1f} us per launch, "
           f"device status {pdc.device_status()}, max |y| {float(out.float().abs().max()):.4f}")
     return 0

@@ -14,9 +14,7 @@ Which kernel runs: the reference's union kernel refuses devices below compute ca
 ``launch_mode = "fallback"`` on them (:322-324), so on a B200 (10.0) the reference ALWAYS computes
 this op with ``clustered_page_decode`` on the plan's ``fallback_plan``, and ``force_impl="union"``
 raises. This module does exactly that, over this build's paged-KV decode kernel; no separate union
-kernel is built. What the union kernel is for -- fetching a shared page from HBM once -- the
-fallback gets from the 126 MB L2 here: the blocks of the requests that share a prefix stream the
-same physical pages at about the same time.
+kernel is built.
 """
 
 from __future__ import annotations
