@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -32,6 +33,7 @@ constexpr int kMaxDevices = 64;
 constexpr size_t kTicketBytes = 64 * 1024;      // fixed header: one counter per task
 constexpr int kMaxTicketTasks = kTicketBytes / 4;
 constexpr int kWorkspaceBlocks = 1024;          // partial results the documented size has room for
+constexpr int kMaxClusterMerge = 4;              // blocks of one task that merge inside a cluster
 constexpr int kSharedBudget = 220 * 1024;       // of the 227 KB a block may use
 
 struct DeviceInfo {
@@ -73,10 +75,20 @@ int device_info(DeviceInfo* out) {
   return FK_PAGE_DECODE_OK;
 }
 
+// FK_PAGE_DECODE_CLUSTER_MERGE=0 sends every split call through global scratch (for comparisons).
+bool cluster_merge_enabled() {
+  static const bool enabled = [] {
+    const char* text = std::getenv("FK_PAGE_DECODE_CLUSTER_MERGE");
+    return text == nullptr || text[0] != '0';
+  }();
+  return enabled;
+}
+
 std::atomic<int> g_warps_override{0};
 std::atomic<int> g_stages_override{0};
 
 struct Plan {
+  bool cluster_merge = false;
   Variant variant;
   int head_tiles = 0;
   int tasks = 0;
@@ -153,7 +165,15 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
   const int group = a.num_q_heads / a.num_kv_heads;
   const int wanted = a.group_tile == 0 ? 8 : a.group_tile;
   Plan out;
-  out.variant = Variant{a.head_dim, a.kv_format, a.keys_are_rotated != 0, smallest_tile_for(std::min(wanted, group))};
+  int tile = smallest_tile_for(std::min(wanted, group));
+  if (tile == 8 && static_cast<long long>(a.batch) * a.num_kv_heads * ((group + 7) / 8) * 2 <= info.sm_count) {
+    // Few tasks: the call is bound by latency, not by traffic, and a tile of 4 heads runs 12 warps
+    // per block where a tile of 8 has registers for 8 (measured on 2 requests x 4 kv heads x 4096
+    // tokens, 8 heads per kv head: 15.5 us against 16.7). The tile is a tiling choice only: results
+    // agree to fp32 rounding.
+    tile = 4;
+  }
+  out.variant = Variant{a.head_dim, a.kv_format, a.keys_are_rotated != 0, tile};
   const int gt = out.variant.group_tile;
   out.head_tiles = (group + gt - 1) / gt;
   const long long tasks = static_cast<long long>(a.batch) * a.num_kv_heads * out.head_tiles;
@@ -186,7 +206,20 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
     // tokens, 155 us uncut, 173 us cut in 4).
     splits = out.tasks <= info.sm_count ? info.sm_count / out.tasks : 1;
     splits = std::max(1, std::min({splits, most, kMaxSplits}));
+    // 2 or 4 blocks per task can be one thread-block cluster and merge through shared memory (no
+    // scratch, no ticket; 4 requests x 8 kv heads x 2048 tokens: 16.1 us against 16.9); worth it
+    // when that power of two is not much below the count that fills the device. Clusters of 8
+    // blocks of this size do not pack: 16 of them ran in two waves (26.7 us against 15.5 with 9
+    // blocks per task through the workspace).
+    int pow2 = 1;
+    while (pow2 * 2 <= std::min(splits, kMaxClusterMerge)) {
+      pow2 *= 2;
+    }
+    if (cluster_merge_enabled() && pow2 >= 2 && pow2 * 4 >= splits * 3) {
+      splits = pow2;
+    }
   }
+  out.cluster_merge = cluster_merge_enabled() && (splits == 2 || splits == 4);
   if (out.tasks > kMaxTicketTasks) {
     if (a.splits > 1) {
       return fail(FK_PAGE_DECODE_ERR_INVALID_ARGUMENT, "splits > 1 supports at most 16384 tasks");
@@ -195,7 +228,7 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
   }
   out.splits = splits;
   out.workspace_need =
-      splits == 1 ? 0 : kTicketBytes + static_cast<size_t>(out.tasks) * splits * partial_floats(gt, a.head_dim) * 4;
+      (splits == 1 || out.cluster_merge) ? 0 : kTicketBytes + static_cast<size_t>(out.tasks) * splits * partial_floats(gt, a.head_dim) * 4;
   if (out.workspace_need > 0 && check_workspace) {
     if (a.workspace == nullptr || a.workspace_bytes < out.workspace_need) {
       char text[160];
@@ -301,6 +334,7 @@ FK_PAGE_DECODE_API int fk_page_decode_forward(const fk_page_decode_args* args) {
   params.page_size = a.page_size;
   params.splits = plan.splits;
   params.stages = plan.stages;
+  params.cluster_merge = plan.cluster_merge ? 1 : 0;
   params.early_descriptors = (a.flags & FK_PAGE_DECODE_FLAG_EARLY_DESCRIPTORS) != 0 ? 1 : 0;
   params.scale_log2e = static_cast<float>(static_cast<double>(a.softmax_scale) * 1.4426950408889634);
   for (int i = 0; i < a.head_dim / 2; ++i) {
@@ -344,8 +378,9 @@ FK_PAGE_DECODE_API int fk_page_decode_describe_plan(const fk_page_decode_args* a
   if (const int code = make_plan(*args, &plan, false); code != FK_PAGE_DECODE_OK) {
     return code;
   }
-  std::snprintf(text, capacity, "kernel=page_decode blocks=%lld tasks=%d splits=%d group_tile=%d warps=%d stages=%d shared=%d",
-                static_cast<long long>(plan.tasks) * plan.splits, plan.tasks, plan.splits, plan.variant.group_tile,
+  std::snprintf(text, capacity, "kernel=page_decode blocks=%lld tasks=%d splits=%d merge=%s group_tile=%d warps=%d stages=%d shared=%d",
+                static_cast<long long>(plan.tasks) * plan.splits, plan.tasks, plan.splits,
+                plan.splits == 1 ? "none" : plan.cluster_merge ? "cluster" : "global", plan.variant.group_tile,
                 plan.warps, plan.stages, plan.shared_bytes);
   return FK_PAGE_DECODE_OK;
 }

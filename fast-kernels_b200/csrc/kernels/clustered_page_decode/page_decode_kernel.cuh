@@ -87,6 +87,7 @@ struct DecodeParams {
   int splits;
   int stages;
   int early_descriptors;  // the run arrays and seq_lens are not written by the preceding kernel
+  int cluster_merge;      // the S blocks of a task are one thread-block cluster: merge through shared memory
   float scale_log2e;  // softmax scale times log2(e): the kernel works with exp2
   float inv_freq[kMaxPairs];  // theta^(-2 i / head_dim), rounded once from double
 };
@@ -130,9 +131,10 @@ struct Layout {
     at += round_up(warps * GT * 4, 128);
     tail = at;  // aligned at run time: rotation table, then the ring
     const int ring_bytes = warps * stages * kStageBytes;
-    // after the stream the ring's memory holds per-warp results [warps][GT][D + 2], then (last
-    // block of a task) the splits' maxima and weights [GT][kMaxSplits] twice
-    const int merge_bytes = warps * GT * (D + 2) * 4 + 2 * GT * kMaxSplits * 4;
+    // after the stream the ring's memory holds per-warp results [warps][GT][D + 2], then (merging
+    // block of a task) the splits' maxima and weights [GT][kMaxSplits] twice, then the block's own
+    // result [GT][D + 4] for the merge inside a cluster
+    const int merge_bytes = round_up(warps * GT * (D + 2), 4) * 4 + 2 * GT * kMaxSplits * 4 + GT * (D + 4) * 4;
     at += kAlign + kRopeBytes + (ring_bytes > merge_bytes ? ring_bytes : merge_bytes);
     total = at;
   }
@@ -143,6 +145,31 @@ __device__ __forceinline__ void bulk_copy_plain(uint32_t dst, const void* src, u
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// Thread-block cluster: barrier, address of a peer block's shared memory, loads from it.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
 }
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
@@ -290,11 +317,11 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   const uint32_t ring = tail_addr + L::kRopeBytes + warp * stages * L::kStageBytes;
   const uint32_t my_bars = bars + warp * stages * 8;
 
-  if (tid < warps * stages) {
-    mbar_init(bars + tid * 8, 1);
+  for (int i = tid; i < warps * stages; i += threads) {
+    mbar_init(bars + i * 8, 1);
   }
-  if (tid < D / 2) {
-    inv_freq_s[tid] = p.inv_freq[tid];
+  for (int i = tid; i < D / 2; i += threads) {  // a block may have fewer threads than pairs
+    inv_freq_s[i] = p.inv_freq[i];
   }
   mbar_init_fence();
   // Programmatic dependent launch (no-ops without the launch attribute): the next kernel of the
@@ -700,8 +727,9 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   float* merge_m = merge;                     // [warps][GT]
   float* merge_l = merge + warps * GT;        // [warps][GT]
   float* merge_acc = merge + 2 * warps * GT;  // [warps][GT][D]
-  float* split_m = merge + warps * GT * (D + 2);  // [GT][kMaxSplits] maxima, then weights
+  float* split_m = merge + round_up(warps * GT * (D + 2), 4);  // [GT][kMaxSplits] maxima, then weights
   float* split_l = split_m + GT * kMaxSplits;     // [GT][kMaxSplits] denominators
+  float* block_result = split_l + GT * kMaxSplits;  // [GT][ROW]: this block's result, read by the cluster's rank 0
   if (lane < GT) {
     merge_m[warp * GT + lane] = m_run;
     merge_l[warp * GT + lane] = l_run;
@@ -734,14 +762,70 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
       const float y = l_all == 0.0f ? 0.0f : a_all / l_all;
       p.output[out_base + idx] = __bfloat16_as_ushort(__float2bfloat16_rn(y));
     } else {
-      my_partial[h * ROW + d] = a_all;
+      float* dst = p.cluster_merge ? block_result : my_partial;
+      dst[h * ROW + d] = a_all;
       if (d == 0) {
-        my_partial[h * ROW + D] = m_all;
-        my_partial[h * ROW + D + 1] = l_all;
+        dst[h * ROW + D] = m_all;
+        dst[h * ROW + D + 1] = l_all;
       }
     }
   }
   if (S == 1) {
+    return;
+  }
+  if (p.cluster_merge) {
+    // The S blocks of the task are one cluster (rank = split). Everybody's result sits in its own
+    // shared memory; rank 0 reads them in rank order -- same arithmetic as the path through
+    // global memory below, no scratch, no ticket -- and nobody leaves before it is done.
+    cluster_sync_all();
+    if (cluster_rank() == 0) {
+      const uint32_t result_addr = smem_addr(block_result);
+      for (int idx = tid; idx < tile_heads * S; idx += threads) {
+        const int h = idx / S;
+        const int s = idx - h * S;
+        const float2 ml = ld_cluster_f2(cluster_map(result_addr + (h * ROW + D) * 4, s));
+        split_m[h * kMaxSplits + s] = ml.x;
+        split_l[h * kMaxSplits + s] = ml.y;
+      }
+      __syncthreads();
+      if (tid < tile_heads) {
+        float m_all = -INFINITY;
+        for (int s = 0; s < S; ++s) {
+          m_all = fmaxf(m_all, split_m[tid * kMaxSplits + s]);
+        }
+        const float m_ref = m_all == -INFINITY ? 0.0f : m_all;
+        float l_all = 0.0f;
+        for (int s = 0; s < S; ++s) {
+          const float weight = exp2f(split_m[tid * kMaxSplits + s] - m_ref);
+          l_all += weight * split_l[tid * kMaxSplits + s];
+          split_m[tid * kMaxSplits + s] = weight;
+        }
+        split_l[tid * kMaxSplits] = l_all == 0.0f ? 0.0f : 1.0f / l_all;
+      }
+      __syncthreads();
+      for (int idx = tid; idx < tile_heads * (D / 4); idx += threads) {
+        const int h = idx / (D / 4);
+        const int d = (idx - h * (D / 4)) * 4;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+        for (int s = 0; s < S; ++s) {
+          const float4 v = ld_cluster_f4(cluster_map(result_addr + (h * ROW + d) * 4, s));
+          const float weight = split_m[h * kMaxSplits + s];
+          sum.x = fmaf(weight, v.x, sum.x);
+          sum.y = fmaf(weight, v.y, sum.y);
+          sum.z = fmaf(weight, v.z, sum.z);
+          sum.w = fmaf(weight, v.w, sum.w);
+        }
+        const float inv = split_l[h * kMaxSplits];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * inv, sum.y * inv);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(sum.z * inv, sum.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.output + out_base + static_cast<size_t>(h) * D + d) = packed;
+      }
+    }
+    cluster_sync_all();
     return;
   }
   __threadfence();

@@ -88,13 +88,17 @@ typedef struct fk_page_decode_args {
   int32_t head_dim;
   int32_t page_size;
   /* Query heads of one kv head that one thread block carries together (1, 2, 4 or 8; 0 = the
-   * smallest of those that covers the group, capped at 8). The reference's `group_tile`. */
+   * smallest of those that covers the group, capped at 8). The reference's `group_tile`. An upper
+   * bound: with few tasks the launcher may carry 4 where 8 were asked for (more warps per block);
+   * results agree to fp32 rounding. */
   int32_t group_tile;
   int32_t kv_format;
   int32_t keys_are_rotated;
   /* How many thread blocks share the pages of one (request, kv head, head tile): 0 = as many as
    * fill the device, 1 = one block and no scratch, n = exactly n (at most 64). The blocks'
-   * partial results are merged in block order by the block that finishes last. */
+   * partial results are merged in block order: for 2 or 4 blocks inside a thread-block cluster
+   * through shared memory (no scratch), otherwise through the workspace by the block that
+   * finishes last. */
   int32_t splits;
   /* Upper bound of the pages of one request if the caller knows it (it bounds `splits` so that
    * short requests are not cut into empty pieces), 0 = unknown. */

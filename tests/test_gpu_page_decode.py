@@ -40,7 +40,7 @@ def _status_ok() -> None:
 
 
 # ---- fixtures: the kernel on the reference's inputs --------------------------------------------------
-@pytest.mark.parametrize("splits", [1, 0, 3])
+@pytest.mark.parametrize("splits", [1, 0, 3, 8])
 @pytest.mark.parametrize("meta", CASES, ids=IDS)
 def test_kernel_on_the_reference_fixtures(meta, splits) -> None:
     case = load_case(meta["name"])
@@ -97,7 +97,7 @@ def test_every_instantiation_against_the_oracle(group, head_dim, page_size, layo
                                          seed=group * 1000 + head_dim + page_size)
     dev = _device_case(query, cache, plan)
     want = dev.oracle(oracle)
-    for splits in (1, 2):
+    for splits in (1, 2, 3):  # one block; a cluster of two; three blocks through the workspace
         _assert_close_to_oracle(dev.forward(pdc, splits=splits), want, f"splits={splits}")
     _status_ok()
 
@@ -258,8 +258,15 @@ def test_results_do_not_depend_on_timing_and_the_workspace_stays_clean() -> None
     assert not header.any().item() and not dev.workspace[: 64 * 1024].any().item()  # tickets are zero again
     info = pdc.describe_plan(dev.args(pdc, first))
     assert int(info["splits"]) > 1 and int(info["blocks"]) == int(info["tasks"]) * int(info["splits"])
+    assert info["merge"] == "cluster"  # 32 tasks x 4 blocks
+    through_workspace = dev.forward(pdc, splits=5)
+    for _ in range(3):
+        assert torch.equal(dev.forward(pdc, splits=5).view(torch.int16), through_workspace.view(torch.int16))
+    torch.cuda.synchronize()
+    assert not dev.workspace[: 64 * 1024].any().item()
     one = dev.forward(pdc, splits=1)
-    assert (one.float() - first.float()).abs().max().item() <= 2e-2  # another order of the same sums
+    for other in (first, through_workspace):
+        assert (one.float() - other.float()).abs().max().item() <= 2e-2  # another order of the same sums
     _status_ok()
 
 
@@ -324,13 +331,15 @@ def test_workspace_that_is_too_small_is_refused() -> None:
                                          lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
     dev = _device_case(query, cache, plan)
     out = dev.forward(pdc)
-    args = dev.args(pdc, out, splits=4)
+    args = dev.args(pdc, out, splits=3)  # 3 blocks per task merge through the workspace (2 or 4: a cluster)
     args.workspace_bytes = 64 * 1024
     assert pdc.load_library().fk_page_decode_forward(ctypes.byref(args)) == pdc.ERR_INVALID_ARGUMENT
     assert "workspace too small" in pdc.load_library().fk_page_decode_last_error().decode()
-    args.splits, args.workspace, args.workspace_bytes = 1, 0, 0  # one block per task needs none
-    pdc.check(pdc.load_library().fk_page_decode_forward(ctypes.byref(args)))
-    _assert_close_to_oracle(out, dev.oracle(oracle))
+    for splits in (1, 4):  # one block per task needs no scratch, nor does a cluster of 4
+        args.splits, args.workspace, args.workspace_bytes = splits, 0, 0
+        out.fill_(float("nan"))
+        pdc.check(pdc.load_library().fk_page_decode_forward(ctypes.byref(args)))
+        _assert_close_to_oracle(out, dev.oracle(oracle), f"splits={splits}")
     _status_ok()
 
 
