@@ -126,7 +126,7 @@ struct Layout {
     vscales = at;
     at += round_up(warps * stages * kVScaleBytes, 128);
     probs = at;
-    at += warps * kUnitTokens * kDbq * GT * 4;
+    at += warps * kUnitTokens * kDbq * GT * 8;  // each probability twice: a ready-made pair (p, p)
     alphas = at;
     at += round_up(warps * GT * 4, 128);
     tail = at;  // aligned at run time: rotation table, then the ring
@@ -181,6 +181,29 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
   return v;
+}
+
+// Packed fp32 pairs: sm_100 multiplies and accumulates two fp32 lanes with one instruction
+// (fma.rn.f32x2 / mul.rn.f32x2 on 64-bit registers), each lane an ordinary IEEE fma. The inner
+// products below keep accumulators, queries, keys and values as such pairs.
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 // EPL elements of one row of a page, starting at this lane's first dimension, as floats
@@ -304,7 +327,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   int2* entries = reinterpret_cast<int2*>(smem + layout.entries);
   float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
   float* inv_freq_s = reinterpret_cast<float*>(smem + layout.inv_freq);
-  float* probs = reinterpret_cast<float*>(smem + layout.probs) + warp * (U * DBQ * GT);
+  float2* probs = reinterpret_cast<float2*>(smem + layout.probs) + warp * (U * DBQ * GT);
   float* alphas = reinterpret_cast<float*>(smem + layout.alphas) + warp * GT;
   const float* vscales = reinterpret_cast<const float*>(smem + layout.vscales) + warp * stages * (L::kVScaleBytes / 4);
   const uint32_t vscales_addr = smem_addr(smem + layout.vscales) + warp * stages * L::kVScaleBytes;
@@ -362,12 +385,12 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   }
 
   float q_in[GT][EPL];  // this lane's part of the tile's queries, loaded once the descriptors are read
-  float acc[GT][EPL];
+  f32x2 acc[GT][EPL / 2];  // weighted values, pairs of neighbouring dimensions
 #pragma unroll
   for (int h = 0; h < GT; ++h) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      acc[h][e] = 0.0f;
+    for (int e = 0; e < EPL / 2; ++e) {
+      acc[h][e] = pack2(0.0f, 0.0f);
     }
   }
   // Softmax state of head (lane % GT): the running maximum is the same on all lanes of a head,
@@ -553,7 +576,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
         rot_age = follows ? rot_age + 1 : 0;
         rot_unit = logical_unit;
       }
-      float q_rot[GT][EPL];
+      f32x2 q_rot[GT][EPL / 2];
 #pragma unroll
       for (int pi = 0; pi < EPL / 2; ++pi) {
         float factor = p.scale_log2e;
@@ -564,8 +587,8 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
         const float sn = rot_sin[pi] * factor;
 #pragma unroll
         for (int h = 0; h < GT; ++h) {
-          q_rot[h][2 * pi] = q_in[h][2 * pi] * cs - q_in[h][2 * pi + 1] * sn;
-          q_rot[h][2 * pi + 1] = q_in[h][2 * pi] * sn + q_in[h][2 * pi + 1] * cs;
+          q_rot[h][pi] = pack2(q_in[h][2 * pi] * cs - q_in[h][2 * pi + 1] * sn,
+                               q_in[h][2 * pi] * sn + q_in[h][2 * pi + 1] * cs);
         }
       }
       // Row t of the unit's keys sits at k_stage + t * row bytes, and k_stage is aligned to the 16
@@ -603,14 +626,21 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
                 kk[2 * pi + 1] = ke * cs_sn[2 * pi + 1] + ko * cs_sn[2 * pi];
               }
             }
+            f32x2 kk2[EPL / 2];
+#pragma unroll
+            for (int pi = 0; pi < EPL / 2; ++pi) {
+              kk2[pi] = pack2(kk[2 * pi], kk[2 * pi + 1]);
+            }
 #pragma unroll
             for (int h = 0; h < GT; ++h) {
-              float sum = q_rot[h][0] * kk[0];
+              f32x2 sum = mul2(q_rot[h][0], kk2[0]);
 #pragma unroll
-              for (int e = 1; e < EPL; ++e) {
-                sum = fmaf(q_rot[h][e], kk[e], sum);
+              for (int pi = 1; pi < EPL / 2; ++pi) {
+                sum = fma2(q_rot[h][pi], kk2[pi], sum);
               }
-              vals[tl * GT + h] = sum;
+              float lo, hi;
+              unpack2(sum, lo, hi);
+              vals[tl * GT + h] = lo + hi;
             }
           }
           butterfly_sum<NV, GT, FLIP>(vals, lane);
@@ -643,10 +673,10 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
             const float* vs = vscales + stage * (L::kVScaleBytes / 4) + t * DB;
 #pragma unroll
             for (int b = 0; b < DB; ++b) {
-              probs[(t * DBQ + b) * GT + my_head] = prob * vs[b];
+              probs[(t * DBQ + b) * GT + my_head] = make_float2(prob * vs[b], prob * vs[b]);
             }
           } else {
-            probs[t * GT + my_head] = prob;
+            probs[t * GT + my_head] = make_float2(prob, prob);
           }
         }
       }
@@ -661,37 +691,39 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
 #pragma unroll
       for (int h = 0; h < GT; ++h) {
         const float a = alphas[h];
+        const f32x2 a2 = pack2(a, a);
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          acc[h][e] *= a;
+        for (int e = 0; e < EPL / 2; ++e) {
+          acc[h][e] = mul2(acc[h][e], a2);
         }
       }
-      const float* prob_row = probs + lane_db * (QUANT ? GT : 0);
+      const uint32_t prob_row = smem_addr(probs) + lane_db * (QUANT ? GT * 8 : 0);
 #pragma unroll 4
       for (int t = 0; t < tokens; ++t) {
         float vv[EPL];
         load_elements<KV, EPL>(v_stage + t * (D * EB) + lane * (EPL * EB), vv);
-        float pr[GT];
-        if constexpr (GT >= 4) {
+        f32x2 vv2[EPL / 2];
 #pragma unroll
-          for (int h = 0; h < GT; h += 4) {
-            const float4 q4 = *reinterpret_cast<const float4*>(prob_row + t * (DBQ * GT) + h);
-            pr[h] = q4.x;
-            pr[h + 1] = q4.y;
-            pr[h + 2] = q4.z;
-            pr[h + 3] = q4.w;
+        for (int e = 0; e < EPL / 2; ++e) {
+          vv2[e] = pack2(vv[2 * e], vv[2 * e + 1]);
+        }
+        f32x2 pr[GT];  // (p, p) of every head, as stored
+        if constexpr (GT >= 2) {
+#pragma unroll
+          for (int h = 0; h < GT; h += 2) {
+            const uint4 two = lds128(prob_row + (t * (DBQ * GT) + h) * 8);
+            pr[h] = static_cast<f32x2>(two.x) | (static_cast<f32x2>(two.y) << 32);
+            pr[h + 1] = static_cast<f32x2>(two.z) | (static_cast<f32x2>(two.w) << 32);
           }
         } else {
-#pragma unroll
-          for (int h = 0; h < GT; ++h) {
-            pr[h] = prob_row[t * (DBQ * GT) + h];
-          }
+          const uint2 one = lds64(prob_row + t * (DBQ * GT) * 8);
+          pr[0] = static_cast<f32x2>(one.x) | (static_cast<f32x2>(one.y) << 32);
         }
 #pragma unroll
         for (int h = 0; h < GT; ++h) {
 #pragma unroll
-          for (int e = 0; e < EPL; ++e) {
-            acc[h][e] = fmaf(pr[h], vv[e], acc[h][e]);
+          for (int e = 0; e < EPL / 2; ++e) {
+            acc[h][e] = fma2(pr[h], vv2[e], acc[h][e]);
           }
         }
       }
@@ -737,8 +769,10 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
 #pragma unroll
   for (int h = 0; h < GT; ++h) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) {
-      merge_acc[(warp * GT + h) * D + lane * EPL + e] = acc[h][e];
+    for (int e = 0; e < EPL / 2; ++e) {
+      float lo, hi;
+      unpack2(acc[h][e], lo, hi);
+      *reinterpret_cast<float2*>(&merge_acc[(warp * GT + h) * D + lane * EPL + 2 * e]) = make_float2(lo, hi);
     }
   }
   __syncthreads();
