@@ -793,12 +793,16 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
         keys = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
         values = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
         tokens = int(lens.sum())
-        for layout in ("bf16_kv", "fp8_kv", "int8_kv"):
+        for label in ("bf16_kv", "bf16_kv_rotated", "fp8_kv", "int8_kv"):
+            # "bf16_kv_rotated": keys stored with their rotary embedding applied, as serving engines
+            # keep them; the kernel then rotates the query only (and runs on the tensor cores)
+            layout, rotated = label.replace("_rotated", ""), label.endswith("_rotated")
             if layout != "bf16_kv" and batch >= 32:
-                continue  # the large batch once, in bf16: its 8-bit forms are in the tests
+                continue  # the large batch in bf16 only: its 8-bit forms are in the tests
             build = {"bf16_kv": ops.pack_paged_kv_bf16, "fp8_kv": ops.quantize_paged_kv_fp8,
                      "int8_kv": ops.quantize_paged_kv_int8}[layout]
-            cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1)
+            cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1,
+                          key_rope_theta=10000.0 if rotated else None)
             plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens,
                                                   num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim,
                                                   page_size=page, kv_layout=layout, use_cache=False)
@@ -825,6 +829,7 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
                 a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
                 a.batch, a.num_runs, a.num_q_heads, a.num_kv_heads = batch, plan.num_runs, q_heads, kv_heads
                 a.head_dim, a.page_size, a.kv_format = dim, page, ops.KV_FORMAT_IDS[layout]
+                a.keys_are_rotated = int(rotated)
                 a.max_pages_hint, a.softmax_scale, a.rope_theta = plan.max_pages, 1.0 / dim**0.5, 10000.0
                 a.stream = stream()
                 a.flags = pdc.FLAG_EARLY_DESCRIPTORS  # the descriptors are uploaded once, nothing on the device writes them
@@ -849,12 +854,13 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
                 plan.run_base_pages_cpu.numpy()[first], plan.run_page_counts_cpu.numpy()[first],
                 plan.run_logical_starts_cpu.numpy()[first], plan.run_last_page_lens_cpu.numpy()[first],
                 np.asarray([0, first.stop - first.start]), lens.numpy()[:1], kv_format=ops.KV_FORMAT_IDS[layout],
-                keys_are_rotated=False, softmax_scale=1.0 / dim**0.5, rope_theta=10000.0)
+                keys_are_rotated=rotated, softmax_scale=1.0 / dim**0.5, rope_theta=10000.0)
             pdc.check(lib.fk_page_decode_forward(ctypes.byref(arguments(0))))
             torch.cuda.synchronize(device)
             worst, scaled = pd_oracle.max_abs_and_scaled_error(out[:1].float().cpu().numpy().astype(np.float64), want,
                                                                2e-3, 8e-3)
-            row = {"shape": name, "layout": layout, "batch": batch, "tokens": tokens, "us_per_call": us,
+            row = {"shape": name, "layout": label, "kernel": info["kernel"], "batch": batch, "tokens": tokens,
+                   "us_per_call": us,
                    "algorithmic_bytes": algorithmic, "gbs": algorithmic / us / 1e3,
                    "frac": algorithmic / us / 1e3 / peak_gbs, "blocks": int(info["blocks"]),
                    "splits": int(info["splits"]), "warps": int(info["warps"]), "max_abs_err": worst,
@@ -862,6 +868,7 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
             if scaled > 1.0:
                 row["failed"] = "result is off the fp64 oracle"
             if refgpu.available() and layout == "bf16_kv" and batch < 32:
+                rotated_flag = int(rotated)
                 group = q_heads // kv_heads
                 modes = [("reference_cluster_us", 1, max(1, plan.cluster_size))]
                 if group <= 8:
@@ -873,7 +880,7 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
                                        runs=descriptors, seq_lens=descriptors["seq_lens"], output=out, batch=batch,
                                        num_q_heads=q_heads, num_kv_heads=kv_heads, head_dim=dim, page_size=page,
                                        group_tile=plan.group_tile, use_clustered_kernel=clustered,
-                                       cluster_size=cluster_size, kv_format=0, keys_are_rotated=False,
+                                       cluster_size=cluster_size, kv_format=0, keys_are_rotated=bool(rotated_flag),
                                        softmax_scale=1.0 / dim**0.5, rope_theta=10000.0, stream=stream())
 
                     row[key] = _time_rotation(torch, device, theirs, list(range(min(8, len(key_copies)))), reps=2)

@@ -4,12 +4,14 @@ workload to put under a profiler
 (``ncu -k regex:page_decode ... python run_page_decode.py 16 32 8 128 16 4096 bf16_kv 3``).
 
     run_page_decode.py BATCH Q_HEADS KV_HEADS HEAD_DIM PAGE_SIZE MAX_LEN bf16_kv|fp8_kv|int8_kv LAUNCHES [WARPS STAGES [SPLITS]]
-                       [--shared-prefix TOKENS]
+                       [--shared-prefix TOKENS] [--rotated-keys]
 
 Sequence lengths are drawn within one page of MAX_LEN, the page table is fragmented by a seeded
 permutation. The optional numbers override the launch plan (fk_page_decode_set_launch_config and
 the `splits` argument). With --shared-prefix every request repeats the first request's first TOKENS
-tokens and identical pages are stored once (a prompt prefix shared through the page table). Prints the launch plan, the time per launch (CUDA events around the whole
+tokens and identical pages are stored once (a prompt prefix shared through the page table). With
+--rotated-keys the pages hold keys with their rotary embedding applied (bf16 pages then take the
+tensor-core form of the kernel). Prints the launch plan, the time per launch (CUDA events around the whole
 burst, so launch overhead is in it) and the device status word.
 """
 
@@ -28,6 +30,9 @@ from fast_kernels import page_decode_capi as pdc  # noqa: E402
 
 
 def main() -> int:
+    rotated = "--rotated-keys" in sys.argv
+    if rotated:
+        sys.argv.remove("--rotated-keys")
     shared_tokens = 0
     if "--shared-prefix" in sys.argv:
         at = sys.argv.index("--shared-prefix")
@@ -55,7 +60,7 @@ def main() -> int:
         keys[1:, :, :shared_tokens] = keys[0, :, :shared_tokens]
         values[1:, :, :shared_tokens] = values[0, :, :shared_tokens]
     cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1,
-                  deduplicate_identical_pages=shared_tokens > 0)
+                  deduplicate_identical_pages=shared_tokens > 0, key_rope_theta=10000.0 if rotated else None)
     del keys, values
     plan = ops.plan_clustered_page_decode(page_table=cache.page_table, seq_lens=cache.seq_lens, num_q_heads=q_heads,
                                           num_kv_heads=kv_heads, head_dim=dim, page_size=page, kv_layout=layout,
@@ -75,6 +80,7 @@ def main() -> int:
     a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     a.batch, a.num_runs, a.num_q_heads, a.num_kv_heads, a.head_dim, a.page_size = batch, plan.num_runs, q_heads, kv_heads, dim, page
     a.kv_format, a.splits, a.max_pages_hint = ops.KV_FORMAT_IDS[layout], splits, plan.max_pages
+    a.keys_are_rotated = int(rotated)
     a.softmax_scale, a.rope_theta = dim**-0.5, 10000.0
     a.stream = int(torch.cuda.current_stream().cuda_stream)
     pdc.check(lib.fk_page_decode_forward(ctypes.byref(a)))

@@ -36,6 +36,7 @@
 #include <cuda_fp8.h>
 
 #include "../decode_quant_linear/w4a16_common.cuh"
+#include "page_decode_mma.cuh"
 
 namespace fk_page_decode {
 
@@ -95,7 +96,7 @@ struct DecodeParams {
 __host__ __device__ constexpr int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Shared-memory layout, the same arithmetic on host (size) and device (offsets).
-template <int D, int KV, bool ROT, int GT>
+template <int D, int KV, bool ROT, int GT, bool MMA = false>
 struct Layout {
   static constexpr int kElemBytes = KV == kKvBf16 ? 2 : 1;
   static constexpr bool kQuant = KV != kKvBf16;
@@ -103,7 +104,9 @@ struct Layout {
   static constexpr int kDbq = kQuant ? kDimBlocks : 1;  // copies of a probability (one per value scale)
   static constexpr int kUnitBytes = kUnitTokens * D * kElemBytes;
   static constexpr int kVScaleBytes = kQuant ? kUnitTokens * kDimBlocks * 4 : 0;
-  static constexpr int kStageBytes = 2 * kUnitBytes;  // keys, then values, of one unit
+  // The tensor-core variant keeps pairs of rows with a skew between them (see page_decode_mma.cuh).
+  static constexpr int kUnitSmem = MMA ? MmaWarp<D>::kUnitSmem : kUnitBytes;
+  static constexpr int kStageBytes = 2 * kUnitSmem;  // keys, then values, of one unit
   static constexpr int kRopeBytes = ROT ? 0 : kUnitTokens * D * 4;  // per token and pair: cos, sin
   // The key block of a stage and the rotation table are addressed as base ^ (row offset), which
   // needs them aligned to their own size (16 rows). Both sit at the end of the layout behind one
@@ -280,9 +283,11 @@ __device__ __forceinline__ void butterfly_sum(float (&v)[NV], int lane) {
   }
 }
 
-template <int D, int KV, bool ROT, int GT>
-__global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(const __grid_constant__ DecodeParams p) {
-  using L = Layout<D, KV, ROT, GT>;
+template <int D, int KV, bool ROT, int GT, bool MMA = false>
+__global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 32, 1)
+    page_decode_kernel(const __grid_constant__ DecodeParams p) {
+  static_assert(!MMA || (KV == kKvBf16 && ROT && GT == 8), "the tensor-core variant: bf16 pages, rotated keys, tiles of 8");
+  using L = Layout<D, KV, ROT, GT, MMA>;
   constexpr int EPL = L::kEpl;
   constexpr int EB = L::kElemBytes;
   constexpr bool QUANT = L::kQuant;
@@ -417,14 +422,30 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     const size_t offset = page_head * page_bytes + static_cast<size_t>(sub) * L::kUnitBytes;
     const uint32_t dst = ring + stage * L::kStageBytes;
     const uint32_t bar = my_bars + stage * 8;
-    mbar_expect_tx(bar, 2 * L::kUnitBytes + L::kVScaleBytes);
-    bulk_copy_plain(dst, p.key_pages + offset, L::kUnitBytes, bar);
-    bulk_copy_plain(dst + L::kUnitBytes, p.value_pages + offset, L::kUnitBytes, bar);
-    if constexpr (QUANT) {
-      bulk_copy_plain(vscales_addr + stage * L::kVScaleBytes, p.value_scales + (page_head * PS + sub * U) * DB,
-                      L::kVScaleBytes, bar);
+    if constexpr (MMA) {
+      // called by the whole warp: lane 0 announces the bytes, then lanes 0-7 fetch one pair of key
+      // rows each and lanes 8-15 one pair of value rows each into the skewed pairs of the stage
+      if (lane == 0) {
+        mbar_expect_tx(bar, 2 * L::kUnitBytes);
+      }
+      __syncwarp();
+      if (lane < 16) {
+        const int pair = lane & 7;
+        const uint8_t* base = lane < 8 ? p.key_pages : p.value_pages;
+        bulk_copy_plain(dst + (lane < 8 ? 0 : L::kUnitSmem) + pair * MmaWarp<D>::kPairBytes,
+                        base + offset + pair * (2 * D * EB), 2 * D * EB, bar);
+      }
+    } else {
+      mbar_expect_tx(bar, 2 * L::kUnitBytes + L::kVScaleBytes);
+      bulk_copy_plain(dst, p.key_pages + offset, L::kUnitBytes, bar);
+      bulk_copy_plain(dst + L::kUnitBytes, p.value_pages + offset, L::kUnitBytes, bar);
+      if constexpr (QUANT) {
+        bulk_copy_plain(vscales_addr + stage * L::kVScaleBytes, p.value_scales + (page_head * PS + sub * U) * DB,
+                        L::kVScaleBytes, bar);
+      }
     }
   };
+  MmaWarp<D> tensor;  // state of the tensor-core variant (unused otherwise)
 
   float inv_freq_lane[EPL / 2];
   // Rotation of the query for the current unit, e^{i (a - P) theta} (for keys that come rotated:
@@ -498,7 +519,7 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
     if (round == 0 && p.early_descriptors) {
       fk_w4a16::pdl_wait_for_prerequisites();
     }
-    if (lane == 0 && !failed) {
+    if ((MMA || lane == 0) && !failed) {
       for (int k = 0; k < stages; ++k) {
         const int entry_index = warp + k * warps;
         if (entry_index < in_round) {
@@ -506,7 +527,12 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
         }
       }
     }
-    if (round == 0) {
+    if (round == 0 && MMA) {
+      const int head = lane >> 2;
+      tensor.prepare(head < tile_heads ? p.query + out_base + static_cast<size_t>(head) * D : nullptr, lane,
+                     query_position, inv_freq_s, p.scale_log2e, reinterpret_cast<float*>(probs));
+    }
+    if (round == 0 && !MMA) {
 #pragma unroll
       for (int h = 0; h < GT; ++h) {
 #pragma unroll
@@ -557,7 +583,21 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
       const int logical_unit = entry.y >> 5;
       const int tokens = entry.y & 31;
       const uint32_t k_stage = ring + stage * L::kStageBytes;
-      const uint32_t v_stage = k_stage + L::kUnitBytes;
+      const uint32_t v_stage = k_stage + L::kUnitSmem;
+      if constexpr (MMA) {
+        if (tokens < U) {
+          // value rows past the unit's end may hold anything; a zero weight times a NaN is a NaN
+          for (int idx = lane; idx < (U - tokens) * (D / 8); idx += 32) {
+            const int row = tokens + idx / (D / 8);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(MmaWarp<D>::row_address(v_stage, row) +
+                                                                      (idx % (D / 8)) * 16),
+                         "r"(0u)
+                         : "memory");
+          }
+          __syncwarp();
+        }
+        tensor.unit(k_stage, v_stage, tokens, lane);
+      } else {
 
       // query of this unit: rotation by (a - P), key scale, softmax scale
       if constexpr (!ROT) {
@@ -728,10 +768,18 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
         }
       }
 
+      }  // !MMA
+
       // ---- hand the buffer back ----
       __syncwarp();
       const int refill = i + stages * warps;
-      if (lane == 0 && refill < in_round) {
+      if constexpr (MMA) {
+        if (refill < in_round) {
+          proxy_fence_async();  // every lane has read the stage through the generic proxy
+          __syncwarp();
+          issue(refill, stage);
+        }
+      } else if (lane == 0 && refill < in_round) {
         proxy_fence_async();
         issue(refill, stage);
       }
@@ -750,9 +798,14 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   }
 
   // ---- this warp's result -> shared memory, block result, then the splits ----
+  if constexpr (MMA) {
+    tensor.l_run += __shfl_xor_sync(0xffffffffu, tensor.l_run, 1);
+    tensor.l_run += __shfl_xor_sync(0xffffffffu, tensor.l_run, 2);
+  } else {
 #pragma unroll
-  for (int o = GT; o < 32; o <<= 1) {
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+    for (int o = GT; o < 32; o <<= 1) {
+      l_run += __shfl_xor_sync(0xffffffffu, l_run, o);
+    }
   }
   __syncthreads();  // every warp is done with its ring: the merge area overlays it
   float* merge = reinterpret_cast<float*>(ring_ptr);
@@ -762,17 +815,30 @@ __global__ void __launch_bounds__(max_warps_for(GT) * 32, 1) page_decode_kernel(
   float* split_m = merge + round_up(warps * GT * (D + 2), 4);  // [GT][kMaxSplits] maxima, then weights
   float* split_l = split_m + GT * kMaxSplits;     // [GT][kMaxSplits] denominators
   float* block_result = split_l + GT * kMaxSplits;  // [GT][ROW]: this block's result, read by the cluster's rank 0
-  if (lane < GT) {
-    merge_m[warp * GT + lane] = m_run;
-    merge_l[warp * GT + lane] = l_run;
-  }
+  if constexpr (MMA) {
+    const int head = lane >> 2, c = lane & 3;  // rows past the tile carry zero queries: written, never read
+    if (c == 0) {
+      merge_m[warp * GT + head] = tensor.m_run;
+      merge_l[warp * GT + head] = tensor.l_run;
+    }
 #pragma unroll
-  for (int h = 0; h < GT; ++h) {
+    for (int t = 0; t < D / 8; ++t) {  // head part (c0, c1) + remainder part (c2, c3) of the probabilities
+      *reinterpret_cast<float2*>(&merge_acc[(warp * GT + head) * D + t * 8 + 2 * c]) =
+          make_float2(tensor.o[t][0] + tensor.o[t][2], tensor.o[t][1] + tensor.o[t][3]);
+    }
+  } else {
+    if (lane < GT) {
+      merge_m[warp * GT + lane] = m_run;
+      merge_l[warp * GT + lane] = l_run;
+    }
 #pragma unroll
-    for (int e = 0; e < EPL / 2; ++e) {
-      float lo, hi;
-      unpack2(acc[h][e], lo, hi);
-      *reinterpret_cast<float2*>(&merge_acc[(warp * GT + h) * D + lane * EPL + 2 * e]) = make_float2(lo, hi);
+    for (int h = 0; h < GT; ++h) {
+#pragma unroll
+      for (int e = 0; e < EPL / 2; ++e) {
+        float lo, hi;
+        unpack2(acc[h][e], lo, hi);
+        *reinterpret_cast<float2*>(&merge_acc[(warp * GT + h) * D + lane * EPL + 2 * e]) = make_float2(lo, hi);
+      }
     }
   }
   __syncthreads();

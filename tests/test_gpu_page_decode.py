@@ -309,6 +309,51 @@ def test_early_descriptor_reads_give_the_same_bits_in_a_busy_stream() -> None:
     _status_ok()
 
 
+@pytest.mark.parametrize(("layout", "rotated"), [("bf16_kv", True), ("bf16_kv", False), ("fp8_kv", True)])
+def test_whatever_lies_past_a_page_s_last_token_does_not_matter(layout, rotated) -> None:
+    """Page tails past the last token are nobody's data: fill them with NaN bit patterns (bf16
+    0x7fc0, e4m3 0x7f) in keys and values. Logits of those tokens are masked, and neither path may
+    let a zero weight meet a NaN value (the tensor-core path zeroes such value rows in shared
+    memory first; the fp32 path never reads them)."""
+    query, cache, plan = _random_problem(batch=3, q_heads=8, kv_heads=2, head_dim=128, page_size=32,
+                                         lens=[45, 7, 100], layout=layout, rotated=rotated, seed=13)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    info = pdc.describe_plan(dev.args(pdc, torch.empty_like(dev.query)))
+    assert info["kernel"] == ("page_decode_mma" if layout == "bf16_kv" and rotated else "page_decode")
+    poison = torch.tensor(0x7FC0, dtype=torch.int16) if layout == "bf16_kv" else torch.tensor(0x7F, dtype=torch.uint8)
+    table, lens = cache.page_table.numpy(), cache.seq_lens.numpy()
+    for request in range(3):
+        last_slot = (int(lens[request]) - 1) // 32
+        live = int(lens[request]) - last_slot * 32
+        page = int(table[request, last_slot])
+        for pages in (dev.key_pages, dev.value_pages):
+            raw = pages.view(torch.int16) if layout == "bf16_kv" else pages
+            raw[page, :, live:, :] = poison.to(raw.device)
+    for splits in (1, 3):
+        _assert_close_to_oracle(dev.forward(pdc, splits=splits), want, f"{layout} splits={splits}")
+    _status_ok()
+
+
+def test_tensor_core_variant_on_the_suite_shapes_with_rotated_keys() -> None:
+    """bf16 pages whose keys carry their rotation take the mma.sync form of the kernel: same bound
+    against the fp64 oracle as the fp32 form (query and probabilities enter as bf16 head +
+    remainder, nothing else is rounded)."""
+    for batch, page, max_len, q_heads, kv_heads, dim in ((4, 16, 2048, 32, 8, 128), (2, 32, 4096, 32, 1, 128),
+                                                          (8, 32, 512, 16, 8, 64), (3, 16, 300, 24, 2, 128)):
+        generator = torch.Generator().manual_seed(batch + max_len)
+        lens = torch.randint(max_len // 2, max_len + 1, (batch,), generator=generator).tolist()
+        query, cache, plan = _random_problem(batch=batch, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim,
+                                             page_size=page, lens=lens, layout="bf16_kv", rotated=True, seed=23)
+        dev = _device_case(query, cache, plan)
+        out = dev.forward(pdc, max_pages_hint=plan.max_pages)
+        info = pdc.describe_plan(dev.args(pdc, out, max_pages_hint=plan.max_pages))
+        assert info["kernel"] == "page_decode_mma" and info["group_tile"] == "8"
+        _assert_close_to_oracle(out, dev.oracle(oracle), f"{batch}x{kv_heads}x{max_len}")
+        assert torch.equal(dev.forward(pdc, max_pages_hint=plan.max_pages).view(torch.int16), out.view(torch.int16))
+    _status_ok()
+
+
 def test_group_tile_and_launch_overrides_keep_the_result() -> None:
     query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
                                          lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
