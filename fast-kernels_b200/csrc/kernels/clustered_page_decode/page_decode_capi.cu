@@ -199,10 +199,10 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
 
   // ring: as many warps as fit with `stages` buffers each
   out.stages = g_stages_override.load() > 0 ? g_stages_override.load() : 2;
-  // The tensor-core variant: 12 warps keep HBM busy when every SM has a block of its own; with
-  // fewer tasks than SMs the call is bound by latency and 8 warps (less to set up and to merge)
-  // are quicker (4 x 8 x 256 tokens: 7.0 against 7.6 us; 2 x 4 x 4096: 12.6 against 14.8).
-  const int most_warps = out.variant.tensor_cores ? (out.tasks >= info.sm_count ? kMaxWarpsNarrow : 8)
+  // The tensor-core variant: 12 warps keep HBM busy when most SMs have a task of their own (long
+  // work per block); with few tasks the call is bound by latency and 8 warps (less to set up and
+  // to merge) are quicker (4 x 8 x 256 tokens: 7.0 against 7.6 us; 2 x 4 x 4096: 12.6 against 14.8).
+  const int most_warps = out.variant.tensor_cores ? (out.tasks * 2 > info.sm_count ? kMaxWarpsNarrow : 8)
                                                   : max_warps_for(gt);
   int warps = g_warps_override.load() > 0 ? std::min(g_warps_override.load(), most_warps) : most_warps;
   while (warps > 1 && variant_shared_bytes(out.variant, warps, out.stages) > kSharedBudget) {
