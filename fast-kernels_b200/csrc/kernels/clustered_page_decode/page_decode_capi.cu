@@ -93,6 +93,9 @@ bool tensor_cores_enabled() {
   return enabled;
 }
 
+// Shared memory of a block such that two of them fit one SM (228 KB, 1 KB of it taken per block).
+constexpr int kSharedPerResidentPair = 113 * 1024;
+
 std::atomic<int> g_warps_override{0};
 std::atomic<int> g_stages_override{0};
 
@@ -183,9 +186,10 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
     tile = 4;
   }
   out.variant = Variant{a.head_dim, a.kv_format, a.keys_are_rotated != 0, tile};
-  if (tensor_cores_enabled() && a.kv_format == FK_PAGE_DECODE_KV_BF16 && a.keys_are_rotated != 0) {
-    // bf16 keys that carry their rotation are exact tensor-core operands: logits and weighted
-    // values as mma.sync, always with the full tile of 8 heads (the MMA has the rows anyway)
+  if (tensor_cores_enabled() && a.keys_are_rotated != 0) {
+    // keys that carry their rotation are exact tensor-core operands (8-bit elements convert to
+    // bf16 exactly): logits and weighted values as mma.sync, always with the full tile of 8 heads
+    // (the MMA has the rows anyway)
     out.variant.tensor_cores = true;
     out.variant.group_tile = 8;
   }
@@ -202,8 +206,14 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
   // The tensor-core variant: 12 warps keep HBM busy when most SMs have a task of their own (long
   // work per block); with few tasks the call is bound by latency and 8 warps (less to set up and
   // to merge) are quicker (4 x 8 x 256 tokens: 7.0 against 7.6 us; 2 x 4 x 4096: 12.6 against 14.8).
-  const int most_warps = out.variant.tensor_cores ? (out.tasks * 2 > info.sm_count ? kMaxWarpsNarrow : 8)
-                                                  : max_warps_for(gt);
+  int most_warps = out.variant.tensor_cores ? (out.tasks * 2 > info.sm_count ? kMaxWarpsNarrow : 8) : max_warps_for(gt);
+  if (out.variant.tensor_cores && a.kv_format != FK_PAGE_DECODE_KV_BF16 && out.tasks > info.sm_count &&
+      out.tasks <= 2 * info.sm_count && variant_shared_bytes(out.variant, 6, out.stages) <= kSharedPerResidentPair) {
+    // Between one and two tasks per SM, blocks of 12 warps run in two waves and the second leaves
+    // SMs idle; blocks of 6 warps of 8-bit pages fit two to an SM and all start at once (32
+    // requests x 8 kv heads x 4096 tokens, int8: 92.7 us against 99.5)
+    most_warps = 6;
+  }
   int warps = g_warps_override.load() > 0 ? std::min(g_warps_override.load(), most_warps) : most_warps;
   while (warps > 1 && variant_shared_bytes(out.variant, warps, out.stages) > kSharedBudget) {
     --warps;
@@ -275,7 +285,10 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
 
 int variant_shared_bytes(const Variant& v, int warps, int stages) {
   if (v.tensor_cores) {
-    return v.head_dim == 64 ? shared_bytes_mma_d64_bf16(warps, stages) : shared_bytes_mma_d128_bf16(warps, stages);
+#define FK_PD_SHARED_MMA(NAME) shared_bytes_mma_##NAME(warps, stages)
+    FK_PD_DISPATCH(FK_PD_SHARED_MMA)
+#undef FK_PD_SHARED_MMA
+    return -1;
   }
 #define FK_PD_SHARED(NAME) shared_bytes_##NAME(v.keys_are_rotated, v.group_tile, warps, stages)
   FK_PD_DISPATCH(FK_PD_SHARED)
@@ -286,8 +299,10 @@ int variant_shared_bytes(const Variant& v, int warps, int stages) {
 cudaError_t launch_variant(const Variant& v, const DecodeParams& params, int blocks, int warps, int stages,
                            cudaStream_t stream) {
   if (v.tensor_cores) {
-    return v.head_dim == 64 ? launch_mma_d64_bf16(params, blocks, warps, stages, stream)
-                            : launch_mma_d128_bf16(params, blocks, warps, stages, stream);
+#define FK_PD_LAUNCH_MMA(NAME) launch_mma_##NAME(params, blocks, warps, stages, stream)
+    FK_PD_DISPATCH(FK_PD_LAUNCH_MMA)
+#undef FK_PD_LAUNCH_MMA
+    return cudaErrorInvalidValue;
   }
 #define FK_PD_LAUNCH(NAME) launch_##NAME(v.keys_are_rotated, v.group_tile, params, blocks, warps, stages, stream)
   FK_PD_DISPATCH(FK_PD_LAUNCH)

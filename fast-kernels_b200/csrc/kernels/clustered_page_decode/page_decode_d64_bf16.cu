@@ -2,5 +2,4 @@
 #define FK_PD_D 64
 #define FK_PD_KV kKvBf16
 #define FK_PD_NAME d64_bf16
-#define FK_PD_WITH_MMA 1
 #include "page_decode_shape.inc"

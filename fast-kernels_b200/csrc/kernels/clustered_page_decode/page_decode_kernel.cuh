@@ -105,7 +105,10 @@ struct Layout {
   static constexpr int kUnitBytes = kUnitTokens * D * kElemBytes;
   static constexpr int kVScaleBytes = kQuant ? kUnitTokens * kDimBlocks * 4 : 0;
   // The tensor-core variant keeps pairs of rows with a skew between them (see page_decode_mma.cuh).
-  static constexpr int kUnitSmem = MMA ? MmaWarp<D>::kUnitSmem : kUnitBytes;
+  static constexpr bool kPairStage = MMA && !kQuant;  // bf16 pages land in the tensor-core layout directly
+  static constexpr int kUnitSmem = kPairStage ? MmaWarp<D, false>::kUnitSmem : kUnitBytes;
+  // 8-bit pages on tensor cores: the unit is converted to bf16 rows (keys, values) per warp
+  static constexpr int kConvertedBytes = (MMA && kQuant) ? 2 * MmaWarp<D, false>::kUnitSmem : 0;
   static constexpr int kStageBytes = 2 * kUnitSmem;  // keys, then values, of one unit
   static constexpr int kRopeBytes = ROT ? 0 : kUnitTokens * D * 4;  // per token and pair: cos, sin
   // The key block of a stage and the rotation table are addressed as base ^ (row offset), which
@@ -114,7 +117,7 @@ struct Layout {
   static constexpr int kAlign = ROT ? kUnitBytes : (kRopeBytes > kUnitBytes ? kRopeBytes : kUnitBytes);
   static constexpr int kEpl = D / 32;
 
-  int bars, entries, kscales, inv_freq, vscales, probs, alphas, tail, total;
+  int bars, entries, kscales, inv_freq, vscales, probs, alphas, converted, tail, total;
 
   __host__ __device__ Layout(int warps, int stages) {
     int at = 0;
@@ -129,9 +132,12 @@ struct Layout {
     vscales = at;
     at += round_up(warps * stages * kVScaleBytes, 128);
     probs = at;
-    at += warps * kUnitTokens * kDbq * GT * 8;  // each probability twice: a ready-made pair (p, p)
+    // each probability twice: a ready-made pair (p, p); the tensor-core form only needs D floats of scratch
+    at += warps * (MMA ? D * 4 : kUnitTokens * kDbq * GT * 8);
     alphas = at;
     at += round_up(warps * GT * 4, 128);
+    converted = at;
+    at += warps * kConvertedBytes;
     tail = at;  // aligned at run time: rotation table, then the ring
     const int ring_bytes = warps * stages * kStageBytes;
     // after the stream the ring's memory holds per-warp results [warps][GT][D + 2], then (merging
@@ -249,6 +255,41 @@ __device__ __forceinline__ void load_elements(uint32_t addr, float (&x)[EPL]) {
   }
 }
 
+// Four 8-bit elements of a page (one word) as two f16 pairs, exactly. SHIFTED (e4m3 only): by bit
+// operations alone, which yields the values times 2^-8 -- sign | magnitude bits << 7 reads, as f16,
+// as the same mantissa under an exponent 8 lower, subnormals included.
+// The conversion instruction (two bytes per cvt) and the bit operations (six per four bytes) run on
+// different pipes; keys through the one and values through the other was the quickest mix (32
+// requests x 8 kv heads x 4096 tokens: 107.8 us; both by cvt 111.9, both by bit operations 109.0).
+constexpr bool kFp8ShiftKeys = false;
+constexpr bool kFp8ShiftValues = true;
+template <int KV, bool SHIFTED = false>
+__device__ __forceinline__ void bytes_to_half2(uint32_t w, uint32_t& first, uint32_t& second) {
+  if constexpr (KV == kKvFp8 && SHIFTED) {
+    const uint32_t upper = ((w >> 1) & 0x3f3f3f3fu) | (w & 0x80808080u);  // per byte: sign, magnitude >> 1
+    const uint32_t lower = (w << 7) & 0x80808080u;                        // per byte: lowest magnitude bit, on top
+    first = __byte_perm(upper, lower, 0x1504u);
+    second = __byte_perm(upper, lower, 0x3726u);
+  } else if constexpr (KV == kKvInt8) {
+    // byte + 128 dropped into the mantissa of 1024 (0x64xx = 1024 + x + 128), then minus 1152
+    const uint32_t u = w ^ 0x80808080u;
+    const __half2 offset = __half2half2(__ushort_as_half(0x6480));
+    const uint32_t lo = __byte_perm(u, 0x64646464u, 0x4140u), hi = __byte_perm(u, 0x64646464u, 0x4342u);
+    const __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&lo), offset);
+    const __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&hi), offset);
+    first = *reinterpret_cast<const uint32_t*>(&a);
+    second = *reinterpret_cast<const uint32_t*>(&b);
+  } else {
+    const __half2_raw a = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xffffu), __NV_E4M3);
+    const __half2_raw b = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
+    first = static_cast<uint32_t>(a.x) | (static_cast<uint32_t>(a.y) << 16);
+    second = static_cast<uint32_t>(b.x) | (static_cast<uint32_t>(b.y) << 16);
+  }
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // Sum over lanes of NV values per lane; lane l is left with the total of value (l % NV) in v[0].
 // Value index = token * GT + head. A step with lane offset o settles index bit o: a lane keeps the
 // half whose bit equals its own lane bit and hands the other half to its partner. For the token
@@ -286,8 +327,9 @@ __device__ __forceinline__ void butterfly_sum(float (&v)[NV], int lane) {
 template <int D, int KV, bool ROT, int GT, bool MMA = false>
 __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 32, 1)
     page_decode_kernel(const __grid_constant__ DecodeParams p) {
-  static_assert(!MMA || (KV == kKvBf16 && ROT && GT == 8), "the tensor-core variant: bf16 pages, rotated keys, tiles of 8");
+  static_assert(!MMA || (ROT && GT == 8), "the tensor-core variant: rotated keys, tiles of 8");
   using L = Layout<D, KV, ROT, GT, MMA>;
+  constexpr bool PAIRS = L::kPairStage;  // the stage itself holds skewed row pairs (bf16 pages on tensor cores)
   constexpr int EPL = L::kEpl;
   constexpr int EB = L::kElemBytes;
   constexpr bool QUANT = L::kQuant;
@@ -332,7 +374,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
   int2* entries = reinterpret_cast<int2*>(smem + layout.entries);
   float* kscales = reinterpret_cast<float*>(smem + layout.kscales);
   float* inv_freq_s = reinterpret_cast<float*>(smem + layout.inv_freq);
-  float2* probs = reinterpret_cast<float2*>(smem + layout.probs) + warp * (U * DBQ * GT);
+  float2* probs = reinterpret_cast<float2*>(smem + layout.probs) + warp * (MMA ? D / 2 : U * DBQ * GT);
   float* alphas = reinterpret_cast<float*>(smem + layout.alphas) + warp * GT;
   const float* vscales = reinterpret_cast<const float*>(smem + layout.vscales) + warp * stages * (L::kVScaleBytes / 4);
   const uint32_t vscales_addr = smem_addr(smem + layout.vscales) + warp * stages * L::kVScaleBytes;
@@ -422,7 +464,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
     const size_t offset = page_head * page_bytes + static_cast<size_t>(sub) * L::kUnitBytes;
     const uint32_t dst = ring + stage * L::kStageBytes;
     const uint32_t bar = my_bars + stage * 8;
-    if constexpr (MMA) {
+    if constexpr (PAIRS) {
       // called by the whole warp: lane 0 announces the bytes, then lanes 0-7 fetch one pair of key
       // rows each and lanes 8-15 one pair of value rows each into the skewed pairs of the stage
       if (lane == 0) {
@@ -432,7 +474,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       if (lane < 16) {
         const int pair = lane & 7;
         const uint8_t* base = lane < 8 ? p.key_pages : p.value_pages;
-        bulk_copy_plain(dst + (lane < 8 ? 0 : L::kUnitSmem) + pair * MmaWarp<D>::kPairBytes,
+        bulk_copy_plain(dst + (lane < 8 ? 0 : L::kUnitSmem) + pair * MmaWarp<D, false>::kPairBytes,
                         base + offset + pair * (2 * D * EB), 2 * D * EB, bar);
       }
     } else {
@@ -445,7 +487,10 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       }
     }
   };
-  MmaWarp<D> tensor;  // state of the tensor-core variant (unused otherwise)
+  using Tensor = MmaWarp<D, L::kQuant>;  // 8-bit pages: f16 operands
+  constexpr bool kShiftKeys = KV == kKvFp8 && kFp8ShiftKeys;
+  constexpr bool kShiftValues = KV == kKvFp8 && kFp8ShiftValues;
+  Tensor tensor;  // state of the tensor-core variant (unused otherwise)
 
   float inv_freq_lane[EPL / 2];
   // Rotation of the query for the current unit, e^{i (a - P) theta} (for keys that come rotated:
@@ -519,7 +564,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
     if (round == 0 && p.early_descriptors) {
       fk_w4a16::pdl_wait_for_prerequisites();
     }
-    if ((MMA || lane == 0) && !failed) {
+    if ((PAIRS || lane == 0) && !failed) {
       for (int k = 0; k < stages; ++k) {
         const int entry_index = warp + k * warps;
         if (entry_index < in_round) {
@@ -530,7 +575,8 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
     if (round == 0 && MMA) {
       const int head = lane >> 2;
       tensor.prepare(head < tile_heads ? p.query + out_base + static_cast<size_t>(head) * D : nullptr, lane,
-                     query_position, inv_freq_s, p.scale_log2e, reinterpret_cast<float*>(probs));
+                     query_position, inv_freq_s, p.scale_log2e, reinterpret_cast<float*>(probs),
+                     kShiftKeys ? 256.0f : 1.0f, kShiftValues ? 256.0f : 1.0f);
     }
     if (round == 0 && !MMA) {
 #pragma unroll
@@ -584,19 +630,59 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       const int tokens = entry.y & 31;
       const uint32_t k_stage = ring + stage * L::kStageBytes;
       const uint32_t v_stage = k_stage + L::kUnitSmem;
-      if constexpr (MMA) {
+      if constexpr (MMA && QUANT) {
+        // 8-bit unit -> f16 rows in the tensor-core layout (exact: int8 and e4m3 values are f16
+        // values); scales stay out of it. A lane takes 8 elements of a row: one 8-byte load, one
+        // 16-byte store, both free of bank conflicts.
+        const uint32_t k_rows = smem_addr(smem + layout.converted) + warp * L::kConvertedBytes;
+        const uint32_t v_rows = k_rows + Tensor::kUnitSmem;
+        constexpr int kLanesPerRow = D / 8;
+        constexpr int kRowsPerStep = 32 / kLanesPerRow;
+        const uint32_t to = Tensor::row_address(0, lane / kLanesPerRow) + (lane % kLanesPerRow) * 16;
+#pragma unroll
+        for (int step = 0; step < U / kRowsPerStep; ++step) {
+          const uint2 kb = lds64(k_stage + step * 256 + lane * 8);
+          const uint2 vb = lds64(v_stage + step * 256 + lane * 8);
+          uint32_t kh[4], vh[4];
+          bytes_to_half2<KV, kShiftKeys>(kb.x, kh[0], kh[1]);
+          bytes_to_half2<KV, kShiftKeys>(kb.y, kh[2], kh[3]);
+          bytes_to_half2<KV, kShiftValues>(vb.x, vh[0], vh[1]);
+          bytes_to_half2<KV, kShiftValues>(vb.y, vh[2], vh[3]);
+          const uint32_t at = to + step * (kRowsPerStep / 2) * Tensor::kPairBytes;
+          sts128(k_rows + at, make_uint4(kh[0], kh[1], kh[2], kh[3]));
+          sts128(v_rows + at, make_uint4(vh[0], vh[1], vh[2], vh[3]));
+        }
+        if (tokens < U) {
+          // value rows past the unit's end may hold anything; a zero weight times a NaN is a NaN
+          __syncwarp();
+          for (int idx = lane; idx < (U - tokens) * (D / 8); idx += 32) {
+            const int row = tokens + idx / (D / 8);
+            sts128(Tensor::row_address(v_rows, row) + (idx % (D / 8)) * 16, make_uint4(0u, 0u, 0u, 0u));
+          }
+        }
+        float value_scales[DB][4];
+        Tensor::template lane_value_scales<DB>(vscales + stage * (L::kVScaleBytes / 4), tokens, lane, value_scales);
+        __syncwarp();
+        // the stage is read out: its next unit can fly while this one is worked on
+        if (lane == 0 && i + stages * warps < in_round) {
+          proxy_fence_async();
+          issue(i + stages * warps, stage);
+        }
+        tensor.template unit<DB>(k_rows, v_rows, tokens, lane, &kscales[i * DB], value_scales);
+      } else if constexpr (MMA) {
         if (tokens < U) {
           // value rows past the unit's end may hold anything; a zero weight times a NaN is a NaN
           for (int idx = lane; idx < (U - tokens) * (D / 8); idx += 32) {
             const int row = tokens + idx / (D / 8);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(MmaWarp<D>::row_address(v_stage, row) +
+            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(Tensor::row_address(v_stage, row) +
                                                                       (idx % (D / 8)) * 16),
                          "r"(0u)
                          : "memory");
           }
           __syncwarp();
         }
-        tensor.unit(k_stage, v_stage, tokens, lane);
+        const float no_scales[1][4] = {{1.0f, 1.0f, 1.0f, 1.0f}};
+        tensor.template unit<0>(k_stage, v_stage, tokens, lane, nullptr, no_scales);
       } else {
 
       // query of this unit: rotation by (a - P), key scale, softmax scale
@@ -773,13 +859,13 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       // ---- hand the buffer back ----
       __syncwarp();
       const int refill = i + stages * warps;
-      if constexpr (MMA) {
+      if constexpr (PAIRS) {
         if (refill < in_round) {
           proxy_fence_async();  // every lane has read the stage through the generic proxy
           __syncwarp();
           issue(refill, stage);
         }
-      } else if (lane == 0 && refill < in_round) {
+      } else if (!(MMA && QUANT) && lane == 0 && refill < in_round) {
         proxy_fence_async();
         issue(refill, stage);
       }
@@ -799,6 +885,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
 
   // ---- this warp's result -> shared memory, block result, then the splits ----
   if constexpr (MMA) {
+    tensor.finish();
     tensor.l_run += __shfl_xor_sync(0xffffffffu, tensor.l_run, 1);
     tensor.l_run += __shfl_xor_sync(0xffffffffu, tensor.l_run, 2);
   } else {

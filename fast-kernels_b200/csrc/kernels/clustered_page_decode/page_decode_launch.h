@@ -14,7 +14,7 @@ struct Variant {
   int kv_format;
   bool keys_are_rotated;
   int group_tile;
-  bool tensor_cores = false;  // the mma.sync form: bf16 pages, rotated keys, tiles of 8 only
+  bool tensor_cores = false;  // the mma.sync form: rotated keys, tiles of 8 only
 };
 
 // Dynamic shared memory of a launch, or -1 for an unknown variant.
@@ -33,9 +33,15 @@ FK_PAGE_DECODE_DECLARE_SHAPE(d128_bf16)
 FK_PAGE_DECODE_DECLARE_SHAPE(d128_fp8)
 FK_PAGE_DECODE_DECLARE_SHAPE(d128_int8)
 #undef FK_PAGE_DECODE_DECLARE_SHAPE
-int shared_bytes_mma_d64_bf16(int warps, int stages);
-int shared_bytes_mma_d128_bf16(int warps, int stages);
-cudaError_t launch_mma_d64_bf16(const DecodeParams& params, int blocks, int warps, int stages, cudaStream_t stream);
-cudaError_t launch_mma_d128_bf16(const DecodeParams& params, int blocks, int warps, int stages, cudaStream_t stream);
+#define FK_PAGE_DECODE_DECLARE_MMA(NAME)                            \
+  int shared_bytes_mma_##NAME(int warps, int stages);               \
+  cudaError_t launch_mma_##NAME(const DecodeParams& params, int blocks, int warps, int stages, cudaStream_t stream);
+FK_PAGE_DECODE_DECLARE_MMA(d64_bf16)
+FK_PAGE_DECODE_DECLARE_MMA(d64_fp8)
+FK_PAGE_DECODE_DECLARE_MMA(d64_int8)
+FK_PAGE_DECODE_DECLARE_MMA(d128_bf16)
+FK_PAGE_DECODE_DECLARE_MMA(d128_fp8)
+FK_PAGE_DECODE_DECLARE_MMA(d128_int8)
+#undef FK_PAGE_DECODE_DECLARE_MMA
 
 }  // namespace fk_page_decode

@@ -309,18 +309,19 @@ def test_early_descriptor_reads_give_the_same_bits_in_a_busy_stream() -> None:
     _status_ok()
 
 
-@pytest.mark.parametrize(("layout", "rotated"), [("bf16_kv", True), ("bf16_kv", False), ("fp8_kv", True)])
+@pytest.mark.parametrize(("layout", "rotated"),
+                         [("bf16_kv", True), ("bf16_kv", False), ("fp8_kv", True), ("fp8_kv", False)])
 def test_whatever_lies_past_a_page_s_last_token_does_not_matter(layout, rotated) -> None:
     """Page tails past the last token are nobody's data: fill them with NaN bit patterns (bf16
     0x7fc0, e4m3 0x7f) in keys and values. Logits of those tokens are masked, and neither path may
     let a zero weight meet a NaN value (the tensor-core path zeroes such value rows in shared
-    memory first; the fp32 path never reads them)."""
+    memory first -- for 8-bit pages while it converts them; the fp32 path never reads them)."""
     query, cache, plan = _random_problem(batch=3, q_heads=8, kv_heads=2, head_dim=128, page_size=32,
                                          lens=[45, 7, 100], layout=layout, rotated=rotated, seed=13)
     dev = _device_case(query, cache, plan)
     want = dev.oracle(oracle)
     info = pdc.describe_plan(dev.args(pdc, torch.empty_like(dev.query)))
-    assert info["kernel"] == ("page_decode_mma" if layout == "bf16_kv" and rotated else "page_decode")
+    assert info["kernel"] == ("page_decode_mma" if rotated else "page_decode")
     poison = torch.tensor(0x7FC0, dtype=torch.int16) if layout == "bf16_kv" else torch.tensor(0x7F, dtype=torch.uint8)
     table, lens = cache.page_table.numpy(), cache.seq_lens.numpy()
     for request in range(3):
@@ -335,22 +336,83 @@ def test_whatever_lies_past_a_page_s_last_token_does_not_matter(layout, rotated)
     _status_ok()
 
 
-def test_tensor_core_variant_on_the_suite_shapes_with_rotated_keys() -> None:
-    """bf16 pages whose keys carry their rotation take the mma.sync form of the kernel: same bound
+@pytest.mark.parametrize("layout", ["bf16_kv", "fp8_kv", "int8_kv"])
+def test_tensor_core_variant_on_the_suite_shapes_with_rotated_keys(layout) -> None:
+    """Pages whose keys carry their rotation take the mma.sync form of the kernel: same bound
     against the fp64 oracle as the fp32 form (query and probabilities enter as bf16 head +
-    remainder, nothing else is rounded)."""
+    remainder, nothing else is rounded; e4m3 and int8 elements are bf16 values exactly, their
+    scales stay in fp32)."""
     for batch, page, max_len, q_heads, kv_heads, dim in ((4, 16, 2048, 32, 8, 128), (2, 32, 4096, 32, 1, 128),
                                                           (8, 32, 512, 16, 8, 64), (3, 16, 300, 24, 2, 128)):
         generator = torch.Generator().manual_seed(batch + max_len)
         lens = torch.randint(max_len // 2, max_len + 1, (batch,), generator=generator).tolist()
         query, cache, plan = _random_problem(batch=batch, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim,
-                                             page_size=page, lens=lens, layout="bf16_kv", rotated=True, seed=23)
+                                             page_size=page, lens=lens, layout=layout, rotated=True, seed=23)
         dev = _device_case(query, cache, plan)
         out = dev.forward(pdc, max_pages_hint=plan.max_pages)
         info = pdc.describe_plan(dev.args(pdc, out, max_pages_hint=plan.max_pages))
         assert info["kernel"] == "page_decode_mma" and info["group_tile"] == "8"
         _assert_close_to_oracle(out, dev.oracle(oracle), f"{batch}x{kv_heads}x{max_len}")
         assert torch.equal(dev.forward(pdc, max_pages_hint=plan.max_pages).view(torch.int16), out.view(torch.int16))
+    _status_ok()
+
+
+@pytest.mark.parametrize("layout", ["fp8_kv", "int8_kv"])
+def test_tensor_core_variant_with_scales_and_elements_at_the_ends_of_their_ranges(layout) -> None:
+    """8-bit pages enter the tensor cores as f16, with powers of two taken out of the query and out
+    of the value scales (a running exponent). Here the value scales of neighbouring tokens differ by
+    up to 2^30 and grow along the sequence, the query is large, and the e4m3 pages hold subnormals
+    (bytes 0x01-0x07), which the f16 operands must carry exactly: an operand flushed to zero, or a
+    weight that left the f16 range, shows as an error relative to the output's own magnitude."""
+    for seed, query_gain in ((3, 64.0), (4, 2.0**-12)):
+        query, cache, plan = _random_problem(batch=3, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
+                                             lens=[700, 33, 512], layout=layout, rotated=True, seed=seed)
+        generator = torch.Generator().manual_seed(100 + seed)
+        query = (query.float() * query_gain).to(torch.bfloat16)
+        # per-token value scales: 2^(-20 .. +10), drifting upwards with the slot inside the page
+        shape = cache.value_scales.shape  # [pages, kv_heads, page_size, blocks]
+        exponent = torch.randint(-20, 0, shape, generator=generator).float()
+        exponent += torch.arange(shape[2]).float().view(1, 1, -1, 1) * (10.0 / shape[2])
+        cache.value_scales.copy_(torch.exp2(exponent))
+        # logits are degree-0 in (query gain x key scale): keep them in a softmax's working range
+        cache.key_scales.mul_(1.0 / query_gain)
+        if layout == "fp8_kv":
+            tiny = torch.randint(1, 8, cache.value_pages.shape, generator=generator, dtype=torch.uint8)
+            sign = torch.randint(0, 2, cache.value_pages.shape, generator=generator, dtype=torch.uint8) << 7
+            every_other_page = (torch.arange(cache.value_pages.shape[0]) % 2 == 0).view(-1, 1, 1, 1)
+            raw = cache.value_pages.view(torch.uint8)
+            raw.copy_(torch.where(every_other_page, tiny | sign, raw))
+        dev = _device_case(query, cache, plan)
+        want = dev.oracle(oracle)
+        info = pdc.describe_plan(dev.args(pdc, torch.empty_like(dev.query)))
+        assert info["kernel"] == "page_decode_mma"
+        for splits in (1, 0):
+            got = dev.forward(pdc, splits=splits).float().cpu().numpy().astype(np.float64)
+            assert np.isfinite(got).all()
+            for request in range(3):
+                size = np.abs(want[request]).max()
+                assert size > 0.0
+                assert np.abs(got[request] - want[request]).max() <= 1.0e-2 * size, (layout, seed, splits, request)
+    _status_ok()
+
+
+def test_e4m3_subnormal_values_alone_survive_the_tensor_core_path() -> None:
+    """Every value element an e4m3 subnormal (|x| <= 7 * 2^-9), value scales 1: the output is of that
+    size and must match the oracle to bf16 rounding -- not zero, as it would be if the f16 operands
+    of the MMA lost their subnormals."""
+    query, cache, plan = _random_problem(batch=2, q_heads=8, kv_heads=2, head_dim=64, page_size=32,
+                                         lens=[200, 96], layout="fp8_kv", rotated=True, seed=9)
+    generator = torch.Generator().manual_seed(9)
+    tiny = torch.randint(1, 8, cache.value_pages.shape, generator=generator, dtype=torch.uint8)
+    sign = torch.randint(0, 2, cache.value_pages.shape, generator=generator, dtype=torch.uint8) << 7
+    cache.value_pages.view(torch.uint8).copy_(tiny | sign)
+    cache.value_scales.fill_(1.0)
+    dev = _device_case(query, cache, plan)
+    want = dev.oracle(oracle)
+    got = dev.forward(pdc).float().cpu().numpy().astype(np.float64)
+    size = np.abs(want).max()
+    assert 2.0**-12 < size < 2.0**-6
+    assert np.abs(got - want).max() <= 1.0e-2 * size
     _status_ok()
 
 
