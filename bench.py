@@ -793,12 +793,12 @@ def _page_decode_leg(torch, device, peak_gbs: float) -> dict:
         keys = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
         values = torch.randn((batch, kv_heads, max_len, dim), device=device).to(torch.bfloat16)
         tokens = int(lens.sum())
-        for label in ("bf16_kv", "bf16_kv_rotated", "fp8_kv", "int8_kv"):
-            # "bf16_kv_rotated": keys stored with their rotary embedding applied, as serving engines
-            # keep them; the kernel then rotates the query only (and runs on the tensor cores)
+        for label in ("bf16_kv", "bf16_kv_rotated", "fp8_kv", "fp8_kv_rotated", "int8_kv", "int8_kv_rotated"):
+            # "*_rotated": keys stored with their rotary embedding applied, as serving engines keep
+            # them; the kernel then rotates the query only (and runs on the tensor cores)
             layout, rotated = label.replace("_rotated", ""), label.endswith("_rotated")
-            if layout != "bf16_kv" and batch >= 32:
-                continue  # the large batch in bf16 only: its 8-bit forms are in the tests
+            if layout != "bf16_kv" and not rotated and batch >= 32:
+                continue  # the large batch: 8-bit pages in the form serving engines store only
             build = {"bf16_kv": ops.pack_paged_kv_bf16, "fp8_kv": ops.quantize_paged_kv_fp8,
                      "int8_kv": ops.quantize_paged_kv_int8}[layout]
             cache = build(keys, values, lens, page_size=page, fragment_pages=True, seed=1,

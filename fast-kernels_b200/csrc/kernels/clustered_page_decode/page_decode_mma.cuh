@@ -89,6 +89,13 @@ __device__ __forceinline__ void split_pair(float first, float second, uint32_t& 
   }
 }
 
+// 2^x for x <= 0 in one instruction (2 ulp; results below the normal range become 0).
+__device__ __forceinline__ float exp2_quick(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Exponent fields (bits of a float, mantissa cleared) the power-of-two scalings stay within, so
 // that 2^e and 2^-e are both normal numbers.
 constexpr int kMinExponentBits = 27 << 23;   // 2^-100
@@ -256,12 +263,12 @@ struct MmaWarp {
     unit_max = fmaxf(unit_max, __shfl_xor_sync(0xffffffffu, unit_max, 2));
     const float m_new = fmaxf(m_run, unit_max);
     const float m_ref = m_new == -INFINITY ? 0.0f : m_new;
-    const float alpha = exp2f(m_run - m_ref);
+    const float alpha = exp2_quick(m_run - m_ref);
     float prob[4];
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      prob[j] = exp2f(logit[j] - m_ref);
+      prob[j] = exp2_quick(logit[j] - m_ref);
       sum += prob[j];
     }
     l_run = l_run * alpha + sum;
@@ -304,13 +311,18 @@ struct MmaWarp {
     // addresses token 2 (i % 8) + ((i / 8) % 2) of dim tile (i / 16): matrices 0, 1 = even, odd
     // tokens of tile t; 2, 3 = of tile t + 1
     const uint32_t v_lane = v_rows + (lane & 7) * kPairBytes + ((lane >> 3) & 1) * kRowBytes + (lane >> 4) * 16;
+    // once the running maximum (and exponent) has settled, most units leave the sum as it is
+    if (__any_sync(0xffffffffu, carry != 1.0f)) {
+#pragma unroll
+      for (int t = 0; t < kTiles; ++t) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[t][j] *= carry;
+        }
+      }
+    }
 #pragma unroll
     for (int t = 0; t < kTiles; t += 2) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        o[t][j] *= carry;
-        o[t + 1][j] *= carry;
-      }
       uint32_t b[4];
       ldmatrix_x4_trans(v_lane + t * 16, b);
       mma_16816<HALF>(o[t], pa[t / (kTiles / NB)], b[0], b[1]);
