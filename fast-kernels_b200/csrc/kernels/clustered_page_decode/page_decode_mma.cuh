@@ -98,8 +98,8 @@ __device__ __forceinline__ float exp2_quick(float x) {
 
 // Exponent fields (bits of a float, mantissa cleared) the power-of-two scalings stay within, so
 // that 2^e and 2^-e are both normal numbers.
-constexpr int kMinExponentBits = 27 << 23;   // 2^-100
-constexpr int kMaxExponentBits = 227 << 23;  // 2^100
+constexpr int kMinExponentBits = 7 << 23;    // 2^-120
+constexpr int kMaxExponentBits = 237 << 23;  // 2^110 (times the fixed 2^8 of shifted e4m3 operands: still finite)
 __device__ __forceinline__ int exponent_bits(float magnitude) {
   return min(max(__float_as_int(magnitude) & 0x7f800000, kMinExponentBits), kMaxExponentBits);
 }
