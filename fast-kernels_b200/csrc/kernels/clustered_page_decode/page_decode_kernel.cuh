@@ -356,6 +356,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
   const L layout(warps, stages);
   const int PS = p.page_size;
   const int UPP = PS / U;  // units per page: 1 or 2
+  const int upp_shift = UPP - 1;  // log2(UPP)
 
   const int S = p.splits;
   const int task = blockIdx.x / S;
@@ -451,17 +452,17 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
   const bool holds_value = lane < NV;
   const int lane_db = (DB == 2) ? (lane >> 4) : 0;
 
-  const size_t page_bytes = static_cast<size_t>(PS) * D * EB;
   uint32_t iteration = 0;  // units this warp has consumed: stage = iteration % stages
   bool failed = false;
 
   // entries[i] = (physical unit = page * UPP + sub, (logical unit << 5) | tokens in the unit)
   auto issue = [&](int entry_index, int stage) {
     const int physical_unit = entries[entry_index].x;
-    const int page = physical_unit / UPP;
-    const int sub = physical_unit - page * UPP;
-    const size_t page_head = static_cast<size_t>(page) * p.num_kv_heads + kv_head;
-    const size_t offset = page_head * page_bytes + static_cast<size_t>(sub) * L::kUnitBytes;
+    const int page = physical_unit >> upp_shift;
+    const int sub = physical_unit & (UPP - 1);
+    // this kv head's unit among all units of the pool (a page of one kv head is UPP units in a row)
+    const size_t pool_unit = ((static_cast<size_t>(page) * p.num_kv_heads + kv_head) << upp_shift) + sub;
+    const size_t offset = pool_unit * L::kUnitBytes;
     const uint32_t dst = ring + stage * L::kStageBytes;
     const uint32_t bar = my_bars + stage * 8;
     if constexpr (PAIRS) {
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       bulk_copy_plain(dst, p.key_pages + offset, L::kUnitBytes, bar);
       bulk_copy_plain(dst + L::kUnitBytes, p.value_pages + offset, L::kUnitBytes, bar);
       if constexpr (QUANT) {
-        bulk_copy_plain(vscales_addr + stage * L::kVScaleBytes, p.value_scales + (page_head * PS + sub * U) * DB,
+        bulk_copy_plain(vscales_addr + stage * L::kVScaleBytes, p.value_scales + pool_unit * (U * DB),
                         L::kVScaleBytes, bar);
       }
     }
@@ -545,8 +546,8 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
           }
           if (i >= 0) {
             const int off = q - first;           // unit within the run
-            const int page_off = off / UPP;
-            const int sub = off - page_off * UPP;
+            const int page_off = off >> upp_shift;
+            const int sub = off & (UPP - 1);
             const int page_tokens = page_off == pages - 1 ? last_len : PS;
             const int tokens = min(max(page_tokens - sub * U, 0), U);
             entries[i] = make_int2((base + page_off) * UPP + sub, (((logical_start + page_off) * UPP + sub) << 5) | tokens);
@@ -609,7 +610,7 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
       for (int idx = tid; idx < in_round * DB; idx += threads) {
         const int i = idx / DB;
         const int b = idx - i * DB;
-        const size_t page_head = static_cast<size_t>(entries[i].x / UPP) * p.num_kv_heads + kv_head;
+        const size_t page_head = static_cast<size_t>(entries[i].x >> upp_shift) * p.num_kv_heads + kv_head;
         kscales[idx] = p.key_scales[page_head * DB + b];
       }
     }
@@ -661,14 +662,24 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
           }
         }
         float value_scales[DB][4];
-        Tensor::template lane_value_scales<DB>(vscales + stage * (L::kVScaleBytes / 4), tokens, lane, value_scales);
+        if (tokens == U) {
+          Tensor::template lane_value_scales<DB, true>(vscales + stage * (L::kVScaleBytes / 4), tokens, lane,
+                                                       value_scales);
+        } else {
+          Tensor::template lane_value_scales<DB, false>(vscales + stage * (L::kVScaleBytes / 4), tokens, lane,
+                                                        value_scales);
+        }
         __syncwarp();
         // the stage is read out: its next unit can fly while this one is worked on
         if (lane == 0 && i + stages * warps < in_round) {
           proxy_fence_async();
           issue(i + stages * warps, stage);
         }
-        tensor.template unit<DB>(k_rows, v_rows, tokens, lane, &kscales[i * DB], value_scales);
+        if (tokens == U) {
+          tensor.template unit<DB, true>(k_rows, v_rows, tokens, lane, &kscales[i * DB], value_scales);
+        } else {
+          tensor.template unit<DB, false>(k_rows, v_rows, tokens, lane, &kscales[i * DB], value_scales);
+        }
       } else if constexpr (MMA) {
         if (tokens < U) {
           // value rows past the unit's end may hold anything; a zero weight times a NaN is a NaN
@@ -682,7 +693,11 @@ __global__ void __launch_bounds__((MMA ? kMaxWarpsNarrow : max_warps_for(GT)) * 
           __syncwarp();
         }
         const float no_scales[1][4] = {{1.0f, 1.0f, 1.0f, 1.0f}};
-        tensor.template unit<0>(k_stage, v_stage, tokens, lane, nullptr, no_scales);
+        if (tokens == U) {
+          tensor.template unit<0, true>(k_stage, v_stage, tokens, lane, nullptr, no_scales);
+        } else {
+          tensor.template unit<0, false>(k_stage, v_stage, tokens, lane, nullptr, no_scales);
+        }
       } else {
 
       // query of this unit: rotation by (a - P), key scale, softmax scale

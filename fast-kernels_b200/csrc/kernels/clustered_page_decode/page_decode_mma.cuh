@@ -197,22 +197,35 @@ struct MmaWarp {
   // the values of block b carry the value scales `scales` (lane_value_scales). BLOCKS = 0: no scales.
   // This lane's value scales of a unit, in the order unit() takes them: [block][j], j = the lane's
   // four tokens {2c, 2c + 1} of the even tile and of the odd tile; 0 for a token past the end.
-  template <int NB>
+  template <int NB, bool FULL>
   static __device__ __forceinline__ void lane_value_scales(const float* value_scales, int tokens, int lane,
                                                            float (&scales)[NB][4]) {
+    // the lane's tokens are 4c .. 4c + 3 (j = 0, 2, 1, 3): NB * 4 neighbouring floats, 16-byte aligned
     const int c = lane & 3;
+    float raw[4][NB];  // [token - 4c][block]
+    const float4* src = reinterpret_cast<const float4*>(value_scales + 4 * c * NB);
+#pragma unroll
+    for (int v = 0; v < NB; ++v) {
+      const float4 x = src[v];
+      const float four[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        raw[(v * 4 + e) / NB][(v * 4 + e) % NB] = four[e];
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int token = 2 * (2 * c + (j & 1)) + (j >> 1);
+      const int offset = 2 * (j & 1) + (j >> 1);  // token - 4c
 #pragma unroll
       for (int b = 0; b < NB; ++b) {
         // (a token past the end has probability 0; its scale may be anything, finite or not)
-        scales[b][j] = token < tokens ? value_scales[token * NB + b] : 0.0f;
+        scales[b][j] = (FULL || 4 * c + offset < tokens) ? raw[offset][b] : 0.0f;
       }
     }
   }
 
-  template <int BLOCKS>
+  // FULL: the caller knows that all 16 tokens are real (no masks).
+  template <int BLOCKS, bool FULL>
   __device__ __forceinline__ void unit(uint32_t k_rows, uint32_t v_rows, int tokens, int lane, const float* key_scale,
                                        const float (&scales)[BLOCKS > 0 ? BLOCKS : 1][4]) {
     constexpr int NB = BLOCKS > 0 ? BLOCKS : 1;
@@ -255,7 +268,7 @@ struct MmaWarp {
         if constexpr (HALF) {
           value *= q_power;
         }
-        logit[nt * 2 + j] = token < tokens ? value : -INFINITY;
+        logit[nt * 2 + j] = (FULL || token < tokens) ? value : -INFINITY;
       }
     }
     float unit_max = fmaxf(fmaxf(logit[0], logit[1]), fmaxf(logit[2], logit[3]));
