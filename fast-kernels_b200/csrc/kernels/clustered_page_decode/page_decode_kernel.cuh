@@ -258,10 +258,11 @@ __device__ __forceinline__ void load_elements(uint32_t addr, float (&x)[EPL]) {
 // Four 8-bit elements of a page (one word) as two f16 pairs, exactly. SHIFTED (e4m3 only): by bit
 // operations alone, which yields the values times 2^-8 -- sign | magnitude bits << 7 reads, as f16,
 // as the same mantissa under an exponent 8 lower, subnormals included.
-// The conversion instruction (two bytes per cvt) and the bit operations (six per four bytes) run on
-// different pipes; keys through the one and values through the other was the quickest mix (32
-// requests x 8 kv heads x 4096 tokens: 107.8 us; both by cvt 111.9, both by bit operations 109.0).
-constexpr bool kFp8ShiftKeys = false;
+// The conversion instruction (two bytes per cvt) and the bit operations (seven per four bytes) run
+// on different pipes, but bit operations for both keys and values are the quickest (32 requests x
+// 8 kv heads x 4096 tokens: 93.9 us; keys only 95.4, values only 96.8; before the rest of the
+// per-unit work was trimmed the mix with keys by cvt had been ahead, 107.8 against 109.0).
+constexpr bool kFp8ShiftKeys = true;
 constexpr bool kFp8ShiftValues = true;
 template <int KV, bool SHIFTED = false>
 __device__ __forceinline__ void bytes_to_half2(uint32_t w, uint32_t& first, uint32_t& second) {

@@ -382,6 +382,12 @@ def test_tensor_core_variant_with_scales_and_elements_at_the_ends_of_their_range
             every_other_page = (torch.arange(cache.value_pages.shape[0]) % 2 == 0).view(-1, 1, 1, 1)
             raw = cache.value_pages.view(torch.uint8)
             raw.copy_(torch.where(every_other_page, tiny | sign, raw))
+            # and keys: subnormals in half of the dimensions of every third page (their logits
+            # then come from the other half, which keeps them apart from one another)
+            third = (torch.arange(cache.key_pages.shape[0]) % 3 == 0).view(-1, 1, 1, 1)
+            odd_dims = (torch.arange(cache.key_pages.shape[3]) % 2 == 1).view(1, 1, 1, -1)
+            raw = cache.key_pages.view(torch.uint8)
+            raw.copy_(torch.where(third & odd_dims, tiny | sign, raw))
         dev = _device_case(query, cache, plan)
         want = dev.oracle(oracle)
         info = pdc.describe_plan(dev.args(pdc, torch.empty_like(dev.query)))
