@@ -206,15 +206,21 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
   // The tensor-core variant: 12 warps keep HBM busy when most SMs have a task of their own (long
   // work per block); with few tasks the call is bound by latency and 8 warps (less to set up and
   // to merge) are quicker (4 x 8 x 256 tokens: 7.0 against 7.6 us; 2 x 4 x 4096: 12.6 against 14.8).
-  int most_warps = out.variant.tensor_cores ? (out.tasks * 2 > info.sm_count ? kMaxWarpsNarrow : 8) : max_warps_for(gt);
-  if (out.variant.tensor_cores && a.kv_format != FK_PAGE_DECODE_KV_BF16 && out.tasks > info.sm_count &&
-      out.tasks <= 2 * info.sm_count && variant_shared_bytes(out.variant, 6, out.stages) <= kSharedPerResidentPair) {
-    // Between one and two tasks per SM, blocks of 12 warps run in two waves and the second leaves
-    // SMs idle; blocks of 6 warps of 8-bit pages fit two to an SM and all start at once (32
-    // requests x 8 kv heads x 4096 tokens, int8: 92.7 us against 99.5)
-    most_warps = 6;
+  const int warp_limit = out.variant.tensor_cores ? kMaxWarpsNarrow : max_warps_for(gt);
+  int chosen_warps = out.variant.tensor_cores ? (out.tasks * 2 > info.sm_count ? kMaxWarpsNarrow : 8) : warp_limit;
+  const long long waves_whole = (tasks + info.sm_count - 1) / info.sm_count;
+  const long long waves_halved = (tasks + 2 * info.sm_count - 1) / (2 * info.sm_count);
+  if (out.variant.tensor_cores && out.tasks > info.sm_count && 10 * waves_halved <= 6 * waves_whole &&
+      variant_shared_bytes(out.variant, 6, out.stages) <= kSharedPerResidentPair) {
+    // With more tasks than SMs, blocks of 12 warps run in waves and the last one leaves SMs idle;
+    // blocks of 6 warps fit two to an SM, take twice as long each and start twice as many at
+    // once, and one block's prologue and merge overlap the other's streaming. They win unless
+    // they add more than a fifth to the wave count (bf16, requests x 8 kv heads x tokens, us with
+    // 6 / 12 warps: 24 x 4096 73 / 89, 32 x 4096 87 / 93, 40 x 4096 155 / 136, 64 x 2048 92 / 111,
+    // 75 x 2048 131 / 134, 100 x 1024 83 / 106; int8 pages alike).
+    chosen_warps = 6;
   }
-  int warps = g_warps_override.load() > 0 ? std::min(g_warps_override.load(), most_warps) : most_warps;
+  int warps = g_warps_override.load() > 0 ? std::min(g_warps_override.load(), warp_limit) : chosen_warps;
   while (warps > 1 && variant_shared_bytes(out.variant, warps, out.stages) > kSharedBudget) {
     --warps;
   }

@@ -422,6 +422,36 @@ def test_e4m3_subnormal_values_alone_survive_the_tensor_core_path() -> None:
     _status_ok()
 
 
+@pytest.mark.parametrize("layout", ["bf16_kv", "int8_kv"])
+def test_tensor_core_variant_block_size_follows_the_wave_count(layout) -> None:
+    """With more tasks than SMs the tensor-core form uses blocks of 6 warps (two to an SM) unless
+    that adds more than a fifth to the number of waves; otherwise 12 warps, or 8 when fewer than
+    half of the SMs have a task. Every such plan must give the oracle's result."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    kv_heads = 8
+    for batch in (sms // (4 * kv_heads), sms // kv_heads, sms // kv_heads + 6, 2 * sms // kv_heads + 3,
+                  3 * sms // kv_heads + 1):
+        batch = max(batch, 1)
+        tasks = batch * kv_heads
+        generator = torch.Generator().manual_seed(tasks)
+        lens = torch.randint(20, 70, (batch,), generator=generator).tolist()
+        query, cache, plan = _random_problem(batch=batch, q_heads=32, kv_heads=kv_heads, head_dim=128,
+                                             page_size=16, lens=lens, layout=layout, rotated=True, seed=tasks)
+        dev = _device_case(query, cache, plan)
+        out = dev.forward(pdc)
+        info = pdc.describe_plan(dev.args(pdc, out))
+        whole, halved = -(-tasks // sms), -(-tasks // (2 * sms))
+        if tasks * 2 <= sms:
+            expected = 8
+        elif tasks > sms and 10 * halved <= 6 * whole:
+            expected = 6
+        else:
+            expected = 12
+        assert info["kernel"] == "page_decode_mma" and int(info["warps"]) == expected, (tasks, info)
+        _assert_close_to_oracle(out, dev.oracle(oracle), f"{layout} tasks={tasks}")
+    _status_ok()
+
+
 def test_group_tile_and_launch_overrides_keep_the_result() -> None:
     query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
                                          lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
