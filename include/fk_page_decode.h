@@ -24,7 +24,11 @@
  *
  * A request with seq_lens <= 0 or without runs gets zeros. head_dim is 64 or 128, page_size 16 or
  * 32, num_q_heads a multiple of num_kv_heads. With keys_are_rotated != 0 the keys in the pages
- * already carry their rotary embedding and only the query is rotated.
+ * already carry their rotary embedding and only the query is rotated; such calls run on the tensor
+ * cores (mma.sync with the query and the probabilities as exact 16-bit head + remainder pairs, 8-bit
+ * pages converted to f16 rows on the fly), all others on fp32 FMAs. Both forms accumulate in fp32
+ * and keep every scale in fp32; results agree with an fp64 evaluation of the same bytes to
+ * 2e-3 + 8e-3 |y| (the bound of the parity tests) and are bit-reproducible run to run.
  *
  * All pointers are device pointers. Calls are asynchronous on `stream`. Plain C: no C++ or
  * framework types cross this boundary.
