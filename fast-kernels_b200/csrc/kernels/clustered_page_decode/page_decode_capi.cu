@@ -262,6 +262,19 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
     splits = 1;
   }
   out.splits = splits;
+  if (out.variant.tensor_cores && g_warps_override.load() <= 0 && out.warps == 8 && a.max_pages_hint > 0) {
+    // Few tasks but long ones: 8 warps are the quicker choice only while a warp sees a handful of
+    // units (prologue and merge weigh more than the streaming). From 8 units per warp of a
+    // 12-warp block on, 12 warps win on 8-bit pages, whose conversion keeps the schedulers busy
+    // (4 requests x 8 kv heads x 16384 tokens, int8: 53.4 us against 61.0; bf16 pages, bound by
+    // HBM at that size, do not care: 53.6 against 54.4).
+    const long long units = static_cast<long long>(a.max_pages_hint) * (a.page_size / kUnitTokens);
+    if (units / splits >= 8LL * kMaxWarpsNarrow &&
+        variant_shared_bytes(out.variant, kMaxWarpsNarrow, out.stages) <= kSharedBudget) {
+      out.warps = kMaxWarpsNarrow;
+      out.shared_bytes = variant_shared_bytes(out.variant, out.warps, out.stages);
+    }
+  }
   out.workspace_need =
       (splits == 1 || out.cluster_merge) ? 0 : kTicketBytes + static_cast<size_t>(out.tasks) * splits * partial_floats(gt, a.head_dim) * 4;
   if (out.workspace_need > 0 && check_workspace) {

@@ -449,6 +449,15 @@ def test_tensor_core_variant_block_size_follows_the_wave_count(layout) -> None:
             expected = 12
         assert info["kernel"] == "page_decode_mma" and int(info["warps"]) == expected, (tasks, info)
         _assert_close_to_oracle(out, dev.oracle(oracle), f"{layout} tasks={tasks}")
+    # few tasks: 8 warps while a block's share is short, 12 once a warp of 12 would see 8 units or more
+    # (the plan only; `dev` is the last problem above, the hint stands for the length of the requests)
+    query, cache, plan = _random_problem(batch=1, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
+                                         lens=[40], layout=layout, rotated=True, seed=1)
+    dev = _device_case(query, cache, plan)
+    out = torch.empty_like(dev.query)
+    for hint, expected in ((64, 8), (1024, 8), (16384, 12)):
+        info = pdc.describe_plan(dev.args(pdc, out, max_pages_hint=hint))
+        assert int(info["warps"]) == expected, (hint, info)
     _status_ok()
 
 
