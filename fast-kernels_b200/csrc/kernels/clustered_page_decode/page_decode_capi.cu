@@ -253,6 +253,20 @@ int make_plan(const fk_page_decode_args& a, Plan* plan, bool check_workspace = t
     if (cluster_merge_enabled() && pow2 >= 2 && pow2 * 4 >= splits * 3) {
       splits = pow2;
     }
+    // 8-bit pages on the tensor cores are bound by their instruction stream, so SMs without a task
+    // are what costs: with more than half but at most two thirds of the SMs taken, three 6-warp
+    // blocks per task (two resident per SM, merge through the workspace) bring every SM in. 10
+    // and 12 requests x 8 kv heads x 4096 tokens, int8: 39.6 and 40.4 us against 48.2 and 49.1
+    // (bf16 pages, bound by HBM: 40.4 and 44.1 against 40.6 and 42.3, left as they are).
+    const int resident_splits = 2 * info.sm_count / std::max(1, out.tasks);
+    if (out.variant.tensor_cores && a.kv_format != FK_PAGE_DECODE_KV_BF16 && g_warps_override.load() <= 0 &&
+        splits == 1 && out.tasks <= info.sm_count && resident_splits >= 3 && a.max_pages_hint > 0 &&
+        units / resident_splits >= 8LL * 6 && out.tasks <= kMaxTicketTasks && a.workspace != nullptr &&
+        variant_shared_bytes(out.variant, 6, out.stages) <= kSharedPerResidentPair) {
+      splits = resident_splits;
+      out.warps = 6;
+      out.shared_bytes = variant_shared_bytes(out.variant, 6, out.stages);
+    }
   }
   out.cluster_merge = cluster_merge_enabled() && (splits == 2 || splits == 4);
   if (out.tasks > kMaxTicketTasks) {

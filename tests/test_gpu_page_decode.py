@@ -461,6 +461,34 @@ def test_tensor_core_variant_block_size_follows_the_wave_count(layout) -> None:
     _status_ok()
 
 
+@pytest.mark.parametrize("layout", ["fp8_kv", "int8_kv", "bf16_kv"])
+def test_tensor_core_variant_fills_the_device_with_resident_thirds(layout) -> None:
+    """8-bit pages, more than half and at most two thirds of the SMs with a task, long requests (by
+    the caller's hint): three 6-warp blocks per task, merged through the workspace. bf16 pages keep
+    one 12-warp block per task. The hint is an upper bound -- the requests here are short, so some
+    blocks get no unit at all -- and the result must not depend on it."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    kv_heads = 2
+    batch = (sms * 5 // 9) // kv_heads + 1  # tasks just above half of the SMs
+    tasks = batch * kv_heads
+    assert sms < 2 * tasks and 3 * tasks <= 2 * sms
+    generator = torch.Generator().manual_seed(tasks)
+    lens = torch.randint(1, 120, (batch,), generator=generator).tolist()
+    query, cache, plan = _random_problem(batch=batch, q_heads=8, kv_heads=kv_heads, head_dim=128, page_size=16,
+                                         lens=lens, layout=layout, rotated=True, seed=77)
+    dev = _device_case(query, cache, plan)
+    out = dev.forward(pdc, max_pages_hint=512)
+    info = pdc.describe_plan(dev.args(pdc, out, max_pages_hint=512))
+    if layout == "bf16_kv":
+        assert (info["splits"], info["warps"]) == ("1", "12"), info
+    else:
+        assert (info["splits"], info["warps"], info["merge"]) == ("3", "6", "global"), info
+    want = dev.oracle(oracle)
+    _assert_close_to_oracle(out, want, layout)
+    _assert_close_to_oracle(dev.forward(pdc, max_pages_hint=plan.max_pages), want, f"{layout}, true hint")
+    _status_ok()
+
+
 def test_group_tile_and_launch_overrides_keep_the_result() -> None:
     query, cache, plan = _random_problem(batch=2, q_heads=16, kv_heads=2, head_dim=128, page_size=16,
                                          lens=[333, 200], layout="bf16_kv", rotated=False, seed=2)
